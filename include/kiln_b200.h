@@ -1,0 +1,110 @@
+/*
+ * kiln_b200 — C ABI of the B200 (sm_100a) attention path for the kiln engine's Anima DiT.
+ *
+ * Conventions (all entry points):
+ *   - plain C, no exceptions; every function returns an int status (KB_OK = 0, negative = error,
+ *     kb_error_string() names it) unless stated otherwise;
+ *   - every buffer is owned by the caller and lives on the current CUDA device; nothing is
+ *     allocated per call, optional scratch is passed in as `workspace`;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns without
+ *     synchronising; no hidden streams, no device-wide syncs;
+ *   - activations are row-major [rows, ld] with head h at columns [h*128, (h+1)*128), the layout of
+ *     the engine's op set (reference: engine/src/gpu.h:149-156); `ld_*` are in ELEMENTS;
+ *   - head size is 128 (the only size the reference's fused kernels take: engine/src/tcflash.cuh:170-172);
+ *   - row pointers must be 16-byte aligned and ld a multiple of 8 (reference: engine/src/tcflash.cuh:169).
+ *
+ * `npad` has the reference's meaning (engine/src/gpu.h:149-151): npad extra keys that are exactly
+ * zero (K = 0, V = 0) join the softmax analytically. Reference semantics for a padded text context
+ * are (Tk = real, npad = len - real); masking the padding out instead is (Tk = real, npad = 0).
+ */
+#ifndef KILN_B200_H
+#define KILN_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of Q/K/V (`dtype`) and of the output (`out_dtype`: same as dtype, or KB_F32) */
+enum { KB_F16 = 0, KB_BF16 = 1, KB_F32 = 2 };
+
+enum {
+    KB_OK = 0,
+    KB_ERR_ARG = -1,        /* null pointer, non-positive size, unknown dtype */
+    KB_ERR_ALIGN = -2,      /* pointer not 16-byte aligned or ld not a multiple of 8 */
+    KB_ERR_SHAPE = -3,      /* unsupported shape (ld < H*128, H not a cluster size for NAG, ...) */
+    KB_ERR_WORKSPACE = -4,  /* workspace missing or too small */
+    KB_ERR_CUDA = -5,       /* a CUDA runtime/driver call failed; cudaGetLastError has the detail */
+    KB_ERR_DEVICE = -6,     /* not an sm_100 device, or no device */
+    KB_ERR_TIMEOUT = -7,    /* a kernel gave up on a bounded wait (reported by kb_status) */
+    KB_ERR_SELFCHECK = -8   /* kb_attn_selfcheck: error above tolerance */
+};
+
+const char* kb_error_string(int code);
+int kb_version(void);
+
+/* Prepare the current device (kernel attributes, status word). Idempotent and implied by every
+ * launch entry point; call it once up front to keep the first launch cheap. */
+int kb_init(void);
+
+/* Bytes of scratch the attention entry points need: room for the normalised/rotated 16-bit copies of
+ * Q (norm_q != 0) and K (norm_k != 0). rows_q = B*Tq, rows_k = B*Tk. */
+size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int H, int norm_q, int norm_k);
+
+/* Self-attention of B images, T tokens each (Tq = Tk = T), no padding.
+ * Replaces, per DiT block, the reference sequence rmsnorm(Q), rmsnorm(K), rope_half(Q), rope_half(K),
+ * attention16() (engine/src/dit.cu:464-470; ops at engine/src/kernels.cu:668-673, 773-777, 868-873).
+ *   qn_w / kn_w : bf16 RMSNorm weight[128] for Q / K, or NULL for "already normalised"
+ *   rope_cos / rope_sin : fp32 tables [T, 64] (engine/src/dit.cu:196-215), or NULL for no RoPE
+ * q, k, v: [B*T, ld_*]; out: [B*T, ld_o]. */
+int kb_attn_self(void* out, const void* q, const void* k, const void* v,
+                 const void* qn_w, const void* kn_w, const float* rope_cos, const float* rope_sin,
+                 int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
+                 int dtype, int out_dtype, float eps,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Cross-attention of Tq latent tokens to one text context of Tk real rows + npad zero rows.
+ * Replaces rmsnorm(Q) + attention16(..., Tk = real, npad) (engine/src/dit.cu:476-481). K is taken as
+ * already normalised, as the reference's per-image K/V cache holds it (engine/src/dit.cu:217-234). */
+int kb_attn_cross(void* out, const void* q, const void* qn_w, const void* k, const void* v,
+                  int Tq, int Tk, int npad, int H, int ld_q, int ld_k, int ld_v, int ld_o,
+                  int dtype, int out_dtype, float eps,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* NAG cross-attention: attention to the positive and the negative context from one Q, then
+ *   g = s*Z+ - (s-1)*Z-;  ratio = |g|_1 / max(|Z+|_1, 1e-12) per token over all H*128 channels;
+ *   out = alpha * g * (ratio > tau ? tau/ratio : 1) + (1 - alpha) * Z+
+ * in one kernel. Replaces attention16 x2 + k_nag (engine/src/dit.cu:482-487, 295-324).
+ * H must be 1, 2, 4, 8 or 16 (the heads of one query tile form one thread-block cluster). */
+int kb_attn_nag(void* out, const void* q, const void* qn_w,
+                const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
+                const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg,
+                float scale, float tau, float alpha,
+                int Tq, int H, int ld_q, int ld_kv, int ld_o,
+                int dtype, int out_dtype, float eps,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row pre-pass on its own: out[r, h*128..] = rope(rmsnorm(in[r, h*128..])) as 16-bit, or a plain
+ * conversion when w, cos and sin are NULL. in_dtype may be KB_F32 (the engine keeps Q/K/V in fp32:
+ * engine/src/dit.cu:429-430). Replaces rmsnorm + rope_half (engine/src/kernels.cu:668-673, 773-777)
+ * and the fp32 -> fp16 staging inside the reference kernel (engine/src/tcflash.cuh:56-64). */
+int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype,
+               int rows, int H, int T, const void* w_bf16, float eps,
+               const float* rope_cos, const float* rope_sin, void* stream);
+
+/* Read and clear the device status word of the current device (synchronises the device).
+ * *status_bits = 0 when every kernel since the last call finished normally; returns KB_ERR_TIMEOUT
+ * when a kernel gave up on a bounded wait. */
+int kb_status(unsigned* status_bits);
+
+/* Start-up known-answer test on the current device, in the spirit of the reference's start-up GEMM
+ * cross-check (engine/src/kernels.cu:106-151): runs each kernel family on a small seeded problem and
+ * compares with a one-thread-per-row fp32 kernel. workspace >= kb_selfcheck_workspace_bytes(). */
+size_t kb_selfcheck_workspace_bytes(void);
+int kb_attn_selfcheck(void* workspace, size_t workspace_bytes, float* max_abs_err_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KILN_B200_H */

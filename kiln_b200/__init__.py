@@ -1,0 +1,9 @@
+"""kiln_b200: B200 (sm_100a) attention path for the kiln engine's Anima DiT.
+
+The product is the CUDA library behind the C ABI in include/kiln_b200.h; this package holds its
+sources (csrc/), the C++ op-set shim the engine links (host/), and a ctypes binding used by the
+tests and the benchmark. There is no CPU fallback: every launch entry point fails when the library
+or an sm_100 device is missing.
+"""
+from .ops import (KB_BF16, KB_F16, KB_F32, KilnError, attn_cross, attn_nag, attn_self, check_status, lib, qk_prep,  # noqa: F401
+                  workspace_bytes)

@@ -1,0 +1,413 @@
+// C ABI of the sm_100a attention path (declarations and contracts: include/kiln_b200.h).
+// Host side only: argument validation, TMA tensor-map construction, kernel selection by dtype, launches.
+// There is no CPU fallback and no second backend: on anything but an sm_100 device the entry points fail.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <string.h>
+
+#include <mutex>
+
+#include "../../include/kiln_b200.h"
+#include "attn_sm100.cuh"
+#include "prep.cuh"
+#include "selfcheck.cuh"
+
+namespace {
+
+using namespace kb;
+
+// One word per device that kernels OR error bits into (ST_*). File-scope device memory: no allocation.
+__device__ unsigned int g_status_word;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+    bool ready = false;
+    int err = KB_OK;
+    unsigned int* status = nullptr;
+};
+
+constexpr int MAX_DEVICES = 64;
+DeviceState g_dev[MAX_DEVICES];
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mu;
+
+template <typename K>
+int set_smem(K kernel, bool nonportable_cluster) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) return KB_ERR_CUDA;
+    if (nonportable_cluster && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return KB_ERR_CUDA;
+    return KB_OK;
+}
+
+int init_device(DeviceState& st, int dev) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return KB_ERR_DEVICE;
+    if (prop.major != 10) return KB_ERR_DEVICE;  // tcgen05 / TMEM exist on sm_100 only
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || !fn)
+            return KB_ERR_CUDA;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    int rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_F16, __half>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_F16, float>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_BF16, __nv_bfloat16>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_BF16, float>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_F16, __half>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_F16, float>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_BF16, __nv_bfloat16>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_BF16, float>, true))) return rc;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return KB_ERR_CUDA;
+    st.status = static_cast<unsigned int*>(p);
+    if (cudaMemset(st.status, 0, sizeof(unsigned int)) != cudaSuccess) return KB_ERR_CUDA;
+    return KB_OK;
+}
+
+// state of the current device, initialised on first use
+int get_state(DeviceState** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return KB_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        st.err = init_device(st, dev);
+        st.ready = true;
+        if (st.err != KB_OK) cudaGetLastError();
+    }
+    *out = &st;
+    return st.err;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+// [batches][rows][H*128] view of a row-major 16-bit matrix with row stride ld; box = 64 columns x 128 rows
+int make_tmap(CUtensorMap* tm, const void* ptr, int dtype, int rows, int H, int batches, int ld) {
+    const cuuint64_t dims[3] = {(cuuint64_t)H * 128, (cuuint64_t)rows, (cuuint64_t)batches};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows * (cuuint64_t)ld * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(tm, dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                          const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KB_OK : KB_ERR_CUDA;
+}
+
+int check_mat(const void* p, int ld, int H) {
+    if (!p) return KB_ERR_ARG;
+    if (!aligned16(p) || (ld & 7)) return KB_ERR_ALIGN;
+    if (ld < H * 128) return KB_ERR_SHAPE;
+    return KB_OK;
+}
+
+int check_out(const void* p, int ld, int H, int dtype, int out_dtype) {
+    if (!p) return KB_ERR_ARG;
+    if (out_dtype != dtype && out_dtype != KB_F32) return KB_ERR_ARG;
+    if (!aligned16(p) || (ld & (out_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (ld < H * 128) return KB_ERR_SHAPE;
+    return KB_OK;
+}
+
+template <typename InT, typename OutT>
+void launch_prep_t(void* out, int ld_out, const void* in, int ld_in, int rows, int H, int T, const void* w, float eps,
+                   const float* c, const float* s, cudaStream_t stream) {
+    const long long items = (long long)rows * H;
+    const unsigned grid = (unsigned)((items + 7) / 8);
+    qk_prep_kernel<InT, OutT><<<grid, 256, 0, stream>>>(static_cast<OutT*>(out), ld_out, static_cast<const InT*>(in), ld_in, rows, H, T,
+                                                       static_cast<const __nv_bfloat16*>(w), eps, c, s);
+}
+
+int launch_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
+                const void* w, float eps, const float* c, const float* s, cudaStream_t stream) {
+    if (rows <= 0) return KB_OK;
+#define KB_PREP(IN, OUT) launch_prep_t<IN, OUT>(out, ld_out, in, ld_in, rows, H, T, w, eps, c, s, stream)
+    if (out_dtype == KB_F16) {
+        if (in_dtype == KB_F16) KB_PREP(__half, __half);
+        else if (in_dtype == KB_BF16) KB_PREP(__nv_bfloat16, __half);
+        else KB_PREP(float, __half);
+    } else {
+        if (in_dtype == KB_F16) KB_PREP(__half, __nv_bfloat16);
+        else if (in_dtype == KB_BF16) KB_PREP(__nv_bfloat16, __nv_bfloat16);
+        else KB_PREP(float, __nv_bfloat16);
+    }
+#undef KB_PREP
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+}
+
+template <int MODE, int DT, typename OutT>
+int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
+                  const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = ATTN_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (MODE == MODE_PAIR) {
+        cfg.gridDim = dim3((unsigned)((p.Tq + 2 * BM - 1) / (2 * BM)), (unsigned)p.H, (unsigned)p.B);
+        cfg.numAttrs = 0;
+    } else {
+        cfg.gridDim = dim3((unsigned)((p.Tq + BM - 1) / BM), (unsigned)p.H, 1);
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = (unsigned)p.H;   // all heads of one query tile: the NAG norm spans them
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, DT, OutT>, tq, tk0, tv0, tk1, tv1, p);
+    return e == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+}
+
+template <int MODE>
+int launch_attn(int dtype, int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0,
+                const CUtensorMap& tk1, const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
+    if (dtype == KB_F16) {
+        if (out_dtype == KB_F32) return launch_attn_t<MODE, DT_F16, float>(tq, tk0, tv0, tk1, tv1, p, stream);
+        return launch_attn_t<MODE, DT_F16, __half>(tq, tk0, tv0, tk1, tv1, p, stream);
+    }
+    if (out_dtype == KB_F32) return launch_attn_t<MODE, DT_BF16, float>(tq, tk0, tv0, tk1, tv1, p, stream);
+    return launch_attn_t<MODE, DT_BF16, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, p, stream);
+}
+
+#ifdef KB_DEBUG
+float* g_dbg = nullptr;
+#define KB_SET_DBG(p) (p).dbg = g_dbg
+#else
+#define KB_SET_DBG(p)
+#endif
+
+constexpr float SCALE_LOG2 = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+
+// shared body of self- and cross-attention: q [B*Tq], k/v [B*Tk]
+int attn_pair(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
+              const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk, int npad, int H, int ld_q, int ld_k,
+              int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes,
+              cudaStream_t stream) {
+    if (dtype != KB_F16 && dtype != KB_BF16) return KB_ERR_ARG;
+    if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || npad < 0) return KB_ERR_ARG;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
+    int rc;
+    if ((rc = check_mat(q, ld_q, H)) || (rc = check_mat(k, ld_k, H)) || (rc = check_mat(v, ld_v, H)) ||
+        (rc = check_out(out, ld_o, H, dtype, out_dtype)))
+        return rc;
+    DeviceState* st;
+    if ((rc = get_state(&st))) return rc;
+
+    const bool prep_q = qn_w || rope_cos, prep_k = kn_w || rope_cos;
+    const size_t need = kb_attn_workspace_bytes(B * Tq, B * Tk, H, prep_q, prep_k);
+    if (need && (!workspace || workspace_bytes < need || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    const void* qq = q; const void* kk = k;
+    int ldq = ld_q, ldk = ld_k;
+    char* ws = static_cast<char*>(workspace);
+    if (prep_q) {
+        if ((rc = launch_prep(ws, H * 128, dtype, q, ld_q, dtype, B * Tq, H, Tq, qn_w, eps, rope_cos, rope_sin, stream))) return rc;
+        qq = ws; ldq = H * 128;
+        ws += align256((size_t)B * Tq * H * 128 * 2);
+    }
+    if (prep_k) {
+        if ((rc = launch_prep(ws, H * 128, dtype, k, ld_k, dtype, B * Tk, H, Tk, kn_w, eps, rope_cos, rope_sin, stream))) return rc;
+        kk = ws; ldk = H * 128;
+    }
+    CUtensorMap tq, tk, tv;
+    if ((rc = make_tmap(&tq, qq, dtype, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, dtype, Tk, H, B, ldk)) ||
+        (rc = make_tmap(&tv, v, dtype, Tk, H, B, ld_v)))
+        return rc;
+    AttnParams p = {};
+    p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = B;
+    p.Tk[0] = Tk; p.Tk[1] = 0; p.npad[0] = npad; p.npad[1] = 0;
+    p.scale_log2 = SCALE_LOG2;
+    p.status = st->status;
+    KB_SET_DBG(p);
+    return launch_attn<MODE_PAIR>(dtype, out_dtype, tq, tk, tv, tk, tv, p, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* kb_error_string(int code) {
+    switch (code) {
+        case KB_OK: return "ok";
+        case KB_ERR_ARG: return "bad argument (null pointer, non-positive size or unknown dtype)";
+        case KB_ERR_ALIGN: return "pointer not 16-byte aligned or row stride not a multiple of 8 elements";
+        case KB_ERR_SHAPE: return "unsupported shape";
+        case KB_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case KB_ERR_CUDA: return "CUDA call failed";
+        case KB_ERR_DEVICE: return "no sm_100 device is current";
+        case KB_ERR_TIMEOUT: return "a kernel gave up on a bounded wait";
+        case KB_ERR_SELFCHECK: return "start-up self-check exceeded its tolerance";
+        default: return "unknown error";
+    }
+}
+
+int kb_version(void) { return 100; }
+
+#ifdef KB_DEBUG
+// debug builds only: device buffer of 66048 floats that CTA (0,0,0) of the next launches dumps into
+void kb_debug_set_buffer(float* p) { g_dbg = p; }
+#endif
+
+int kb_init(void) {
+    DeviceState* st;
+    return get_state(&st);
+}
+
+size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int H, int norm_q, int norm_k) {
+    size_t n = 0;
+    if (norm_q) n += align256((size_t)rows_q * H * 128 * 2);
+    if (norm_k) n += align256((size_t)rows_k * H * 128 * 2);
+    return n;
+}
+
+int kb_attn_self(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
+                 const float* rope_cos, const float* rope_sin, int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
+                 int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+    return attn_pair(out, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, T, T, 0, H, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype, eps,
+                     workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int kb_attn_cross(void* out, const void* q, const void* qn_w, const void* k, const void* v, int Tq, int Tk, int npad, int H,
+                  int ld_q, int ld_k, int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    return attn_pair(out, q, k, v, qn_w, nullptr, nullptr, nullptr, 1, Tq, Tk, npad, H, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype,
+                     eps, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
+                const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg, float scale, float tau, float alpha, int Tq,
+                int H, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
+                size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dtype != KB_F16 && dtype != KB_BF16) return KB_ERR_ARG;
+    if (Tq <= 0 || Tk_pos <= 0 || Tk_neg <= 0 || H <= 0 || npad_pos < 0 || npad_neg < 0) return KB_ERR_ARG;
+    if (H > 16 || (H & (H - 1))) return KB_ERR_SHAPE;  // the heads of a query tile are one cluster
+    int rc;
+    if ((rc = check_mat(q, ld_q, H)) || (rc = check_mat(k_pos, ld_kv, H)) || (rc = check_mat(v_pos, ld_kv, H)) ||
+        (rc = check_mat(k_neg, ld_kv, H)) || (rc = check_mat(v_neg, ld_kv, H)) || (rc = check_out(out, ld_o, H, dtype, out_dtype)))
+        return rc;
+    DeviceState* st;
+    if ((rc = get_state(&st))) return rc;
+    const size_t need = kb_attn_workspace_bytes(Tq, 0, H, qn_w != nullptr, 0);
+    if (need && (!workspace || workspace_bytes < need || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    const void* qq = q;
+    int ldq = ld_q;
+    if (qn_w) {
+        if ((rc = launch_prep(workspace, H * 128, dtype, q, ld_q, dtype, Tq, H, Tq, qn_w, eps, nullptr, nullptr, stream))) return rc;
+        qq = workspace; ldq = H * 128;
+    }
+    CUtensorMap tq, tk0, tv0, tk1, tv1;
+    if ((rc = make_tmap(&tq, qq, dtype, Tq, H, 1, ldq)) || (rc = make_tmap(&tk0, k_pos, dtype, Tk_pos, H, 1, ld_kv)) ||
+        (rc = make_tmap(&tv0, v_pos, dtype, Tk_pos, H, 1, ld_kv)) || (rc = make_tmap(&tk1, k_neg, dtype, Tk_neg, H, 1, ld_kv)) ||
+        (rc = make_tmap(&tv1, v_neg, dtype, Tk_neg, H, 1, ld_kv)))
+        return rc;
+    AttnParams p = {};
+    p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = 1;
+    p.Tk[0] = Tk_pos; p.Tk[1] = Tk_neg; p.npad[0] = npad_pos; p.npad[1] = npad_neg;
+    p.scale_log2 = SCALE_LOG2;
+    p.nag_s = scale; p.nag_tau = tau; p.nag_alpha = alpha;
+    p.status = st->status;
+    KB_SET_DBG(p);
+    return launch_attn<MODE_NAG>(dtype, out_dtype, tq, tk0, tv0, tk1, tv1, p, stream);
+}
+
+int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
+               const void* w_bf16, float eps, const float* rope_cos, const float* rope_sin, void* stream) {
+    if (!out || !in || rows < 0 || H <= 0 || T <= 0) return KB_ERR_ARG;
+    if (out_dtype != KB_F16 && out_dtype != KB_BF16) return KB_ERR_ARG;
+    if (in_dtype != KB_F16 && in_dtype != KB_BF16 && in_dtype != KB_F32) return KB_ERR_ARG;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
+    if (!aligned16(out) || !aligned16(in) || (ld_out & 7) || (ld_in & 7)) return KB_ERR_ALIGN;
+    if (ld_out < H * 128 || ld_in < H * 128) return KB_ERR_SHAPE;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    return launch_prep(out, ld_out, out_dtype, in, ld_in, in_dtype, rows, H, T, w_bf16, eps, rope_cos, rope_sin,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int kb_status(unsigned* status_bits) {
+    if (!status_bits) return KB_ERR_ARG;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    unsigned v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_CUDA;
+    if (cudaMemcpy(&v, st->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return KB_ERR_CUDA;
+    if (v && cudaMemset(st->status, 0, sizeof(v)) != cudaSuccess) return KB_ERR_CUDA;
+    *status_bits = v;
+    return (v & ST_TIMEOUT) ? KB_ERR_TIMEOUT : KB_OK;
+}
+
+size_t kb_selfcheck_workspace_bytes(void) { return (size_t)4 << 20; }
+
+int kb_attn_selfcheck(void* workspace, size_t workspace_bytes, float* max_abs_err_out, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!workspace || workspace_bytes < kb_selfcheck_workspace_bytes() || !aligned16(workspace)) return KB_ERR_WORKSPACE;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    // small ragged shapes: neither Tq nor Tk a multiple of the tile sizes
+    const int H = 2, ld = H * 128, Tq = 300, Tk = 200, Tc = 77, Tn = 26;
+    char* ws = static_cast<char*>(workspace);
+    auto take = [&](size_t bytes) { char* p = ws; ws += align256(bytes); return p; };
+    void* q = take((size_t)Tq * ld * 2); void* k = take((size_t)Tq * ld * 2); void* v = take((size_t)Tq * ld * 2);
+    void* k2 = take((size_t)Tq * ld * 2); void* v2 = take((size_t)Tq * ld * 2);
+    float* out = (float*)take((size_t)Tq * ld * 4); float* ref = (float*)take((size_t)Tq * ld * 4);
+    float* ref2 = (float*)take((size_t)Tq * ld * 4);
+    unsigned int* err = (unsigned int*)take(256);
+    const size_t n = (size_t)Tq * ld;
+    const unsigned fb = (unsigned)((n + 255) / 256), ab = (unsigned)((Tq * H + 127) / 128);
+    if (cudaMemsetAsync(err, 0, 4, stream) != cudaSuccess) return KB_ERR_CUDA;
+    for (int dtype = 0; dtype < 2; dtype++) {
+        if (dtype == KB_F16) {
+            sc_fill_kernel<__half><<<fb, 256, 0, stream>>>((__half*)q, n, 11u, 1.2f);
+            sc_fill_kernel<__half><<<fb, 256, 0, stream>>>((__half*)k, n, 12u, 1.2f);
+            sc_fill_kernel<__half><<<fb, 256, 0, stream>>>((__half*)v, n, 13u, 0.8f);
+            sc_fill_kernel<__half><<<fb, 256, 0, stream>>>((__half*)k2, n, 14u, 1.2f);
+            sc_fill_kernel<__half><<<fb, 256, 0, stream>>>((__half*)v2, n, 15u, 0.8f);
+        } else {
+            sc_fill_kernel<__nv_bfloat16><<<fb, 256, 0, stream>>>((__nv_bfloat16*)q, n, 21u, 1.2f);
+            sc_fill_kernel<__nv_bfloat16><<<fb, 256, 0, stream>>>((__nv_bfloat16*)k, n, 22u, 1.2f);
+            sc_fill_kernel<__nv_bfloat16><<<fb, 256, 0, stream>>>((__nv_bfloat16*)v, n, 23u, 0.8f);
+            sc_fill_kernel<__nv_bfloat16><<<fb, 256, 0, stream>>>((__nv_bfloat16*)k2, n, 24u, 1.2f);
+            sc_fill_kernel<__nv_bfloat16><<<fb, 256, 0, stream>>>((__nv_bfloat16*)v2, n, 25u, 0.8f);
+        }
+        auto naive = [&](float* o, const void* kk, const void* vv, int tk, int npad) {
+            if (dtype == KB_F16) sc_naive_attn_kernel<__half><<<ab, 128, 0, stream>>>(o, (const __half*)q, (const __half*)kk, (const __half*)vv, Tq, tk, H, ld, npad);
+            else sc_naive_attn_kernel<__nv_bfloat16><<<ab, 128, 0, stream>>>(o, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kk, (const __nv_bfloat16*)vv, Tq, tk, H, ld, npad);
+        };
+        // self-shaped (Tq x Tk keys, no padding)
+        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, 0, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, nullptr, 0, stream))) return rc;
+        naive(ref, k, v, Tk, 0);
+        sc_maxdiff_kernel<<<fb, 256, 0, stream>>>(out, ref, n, err);
+        // cross with analytic padding
+        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tc, 512 - Tc, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, nullptr, 0, stream))) return rc;
+        naive(ref, k, v, Tc, 512 - Tc);
+        sc_maxdiff_kernel<<<fb, 256, 0, stream>>>(out, ref, n, err);
+        // NAG: two contexts, reference defaults s=5 tau=2.5 alpha=0.25 (engine/src/models.h:80)
+        if ((rc = kb_attn_nag(out, q, nullptr, k, v, Tc, 512 - Tc, k2, v2, Tn, 512 - Tn, 5.f, 2.5f, 0.25f, Tq, H, ld, ld, ld, dtype, KB_F32,
+                              1e-6f, nullptr, 0, stream)))
+            return rc;
+        naive(ref2, k2, v2, Tn, 512 - Tn);
+        sc_naive_nag_kernel<<<(Tq + 127) / 128, 128, 0, stream>>>(ref, ref2, Tq, ld, 5.f, 2.5f, 0.25f);
+        sc_maxdiff_kernel<<<fb, 256, 0, stream>>>(out, ref, n, err);
+    }
+    unsigned int bits = 0;
+    if (cudaMemcpyAsync(&bits, err, 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return KB_ERR_CUDA;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return KB_ERR_CUDA;
+    float e;
+    memcpy(&e, &bits, 4);
+    if (max_abs_err_out) *max_abs_err_out = e;
+    unsigned sb = 0;
+    if ((rc = kb_status(&sb))) return rc;
+    return e <= 2e-3f ? KB_OK : KB_ERR_SELFCHECK;
+}
+
+}  // extern "C"

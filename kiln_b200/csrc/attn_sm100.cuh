@@ -1,0 +1,556 @@
+// Fused multi-head attention forward for head size 128 on sm_100a (B200):
+// TMA-staged Q/K/V tiles (128-byte swizzle), tcgen05 MMAs with the S and O accumulators in TMEM,
+// online softmax with one thread per query row, P handed to the second MMA through TMEM.
+//
+// It replaces the reference's mma.sync FlashAttention-2 kernel tfa::k_flash
+// (engine/src/tcflash.cuh:20-157) and keeps its contract: non-causal, keys >= Tk ignored, `npad`
+// all-zero keys joining the softmax analytically (engine/src/tcflash.cuh:136-147), fp32 statistics,
+// base-2 exponent with the scale log2(e)/sqrt(128) (engine/src/tcflash.cuh:164).
+//
+// One CTA runs TWO softmax streams that ping-pong on the tensor core:
+//   MODE_PAIR : two 128-row query tiles of one (batch, head) against one K/V sequence
+//               (self-attention and plain cross-attention);
+//   MODE_NAG  : one 128-row query tile against TWO K/V sequences (positive and negative context),
+//               followed by the NAG combine of engine/src/dit.cu:295-324 in the epilogue. The combine
+//               needs per-token L1 norms over ALL heads, so the CTAs of the 16 heads of one query tile
+//               form a thread-block cluster and exchange their partial norms through distributed
+//               shared memory; nothing but the blended result goes to HBM.
+//
+// Warp roles (384 threads): warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1 (warp w
+// owns TMEM lanes 32*(w%4)..+31, one query row per thread), warp 8 issues MMAs (one lane), warp 9
+// issues TMA loads (one lane), warps 10-11 idle.
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i overwrites the first
+// 64 columns of S_i as packed 16-bit pairs.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <type_traits>
+
+#include "ptx.cuh"
+
+namespace kb {
+
+constexpr int MODE_PAIR = 0, MODE_NAG = 1;
+constexpr int DT_F16 = 0, DT_BF16 = 1;
+
+constexpr int HD = 128;                 // head size
+constexpr int BM = 128;                 // query rows per stream tile
+constexpr int BN = 128;                 // keys per block
+constexpr int TILE_BYTES = BM * HD * 2; // 32 KiB: one Q, K or V tile (two 64-column swizzled halves)
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int NSTAGE = 4;               // K/V ring depth
+constexpr int ATTN_THREADS = 384;
+constexpr int CTRL_BYTES = 8192;
+constexpr int ATTN_SMEM = 2 * TILE_BYTES + NSTAGE * TILE_BYTES + CTRL_BYTES + 1024;  // + alignment slack
+
+// error bits written to the status word
+constexpr uint32_t ST_TIMEOUT = 1u;
+
+struct AttnParams {
+    void* out;          // [B*Tq, ldo]
+    int ldo;
+    int Tq, H, B;
+    int Tk[2];          // MODE_PAIR uses [0]; MODE_NAG: positive, negative context
+    int npad[2];
+    float scale_log2;   // log2(e) / sqrt(128)
+    float nag_s, nag_tau, nag_alpha;
+    uint32_t* status;   // device word, OR-ed with ST_* on failure
+#ifdef KB_DEBUG
+    float* dbg;         // debug builds only: CTA (0,0,0) dumps S(0), P(0) of stream 0 and the raw O, m, l of both streams
+#endif
+};
+
+// barrier slots inside the control block
+enum { BAR_QFULL = 0, BAR_SFULL = 2, BAR_PFULL = 4, BAR_ODONE = 6, BAR_KVFULL = 8, BAR_KVEMPTY = 8 + NSTAGE, BAR_COUNT = 8 + 2 * NSTAGE };
+
+// full-CTA barrier usable from divergent role branches (same id and count everywhere)
+__device__ __forceinline__ void cta_sync() { named_bar_sync(2, ATTN_THREADS); }
+
+template <int DT>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+    if constexpr (DT == DT_BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
+// store 32 consecutive output columns of one row
+template <typename OutT>
+__device__ __forceinline__ void store32(OutT* dst, const float (&v)[32]) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+        constexpr int DT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(pack16<DT>(v[8 * i], v[8 * i + 1]), pack16<DT>(v[8 * i + 2], v[8 * i + 3]),
+                                                          pack16<DT>(v[8 * i + 4], v[8 * i + 5]), pack16<DT>(v[8 * i + 6], v[8 * i + 7]));
+    }
+}
+
+template <int MODE, int DT, typename OutT>
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
+                const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
+                const __grid_constant__ CUtensorMap tmV1, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
+    uint8_t* const smem = smem_raw + (base - raw);
+    const uint32_t sQ = base;                                     // 2 tiles
+    const uint32_t sKV = base + 2 * TILE_BYTES;                   // NSTAGE tiles
+    uint8_t* const ctrl = smem + 2 * TILE_BYTES + NSTAGE * TILE_BYTES;
+    const uint32_t bars = sKV + NSTAGE * TILE_BYTES;              // BAR_COUNT x 8 bytes
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
+    volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
+    float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 7 x 128 floats
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int q0 = blockIdx.x * (MODE == MODE_PAIR ? 2 * BM : BM);
+
+    // per-stream shape: number of key blocks, and whether the stream exists
+    int nblk[2];
+    nblk[0] = (p.Tk[0] + BN - 1) / BN;
+    nblk[1] = MODE == MODE_NAG ? (p.Tk[1] + BN - 1) / BN : ((q0 + BM < p.Tq) ? nblk[0] : 0);
+
+    if (tid == 0) {
+        for (int i = 0; i < BAR_COUNT; i++) {
+            uint32_t count = 1;
+            if (i >= BAR_PFULL && i < BAR_PFULL + 2) count = 4;   // one arrival per softmax warp
+            mbar_init(bar(i), count);
+        }
+        *abort_flag = 0u;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK0); tma_prefetch_desc(&tmV0);
+        if (MODE == MODE_NAG) { tma_prefetch_desc(&tmK1); tma_prefetch_desc(&tmV1); }
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // state the softmax threads carry from the main loop into the epilogue
+    float row_m = -INFINITY, row_l = 0.f;
+    bool ok = true;
+
+    // 384 threads start with 168 registers each; the MMA/TMA warpgroup gives most of its share to the
+    // softmax ones. Everything a softmax thread runs from here on sits inside this branch so that the
+    // register budget of the branch is known at compile time; the full-CTA barriers below are therefore
+    // written as the same bar.sync id from both branches.
+    if (warp < 8) {
+        setmaxnreg_inc<224>();
+        // ------------------------------------------------------------------ softmax, one row per thread
+        const int i = warp >> 2;                                   // stream
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + (uint32_t)(i * 128);
+        const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(i * 128);
+        const int nb = nblk[i];
+        const int Tk = p.Tk[MODE == MODE_NAG ? i : 0];
+        const float c = p.scale_log2;
+        for (int j = 0; j < nb; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), (uint32_t)(j & 1), abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s[4][32];
+#pragma unroll
+            for (int q = 0; q < 4; q++) tmem_ld32(tS + 32u * q, s[q]);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 4; q++) reg_fence32(s[q]);
+            if (j == nb - 1 && (Tk & (BN - 1))) {                  // ragged last block: keys >= Tk score -inf
+                const int valid = Tk - j * BN;
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+#pragma unroll
+                    for (int e = 0; e < 32; e++)
+                        if (q * 32 + e >= valid) s[q][e] = 0xff800000u;
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 32; e++) {
+                mx0 = fmaxf(mx0, __uint_as_float(s[0][e]));
+                mx1 = fmaxf(mx1, __uint_as_float(s[1][e]));
+                mx2 = fmaxf(mx2, __uint_as_float(s[2][e]));
+                mx3 = fmaxf(mx3, __uint_as_float(s[3][e]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+#ifdef KB_DEBUG
+            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
+                float* d = p.dbg + (size_t)i * 16384 + (size_t)(tid & 127) * 128;
+                for (int q = 0; q < 4; q++)
+                    for (int e = 0; e < 32; e++) d[q * 32 + e] = __uint_as_float(s[q][e]);
+            }
+#endif
+            if (j == 0) {
+                row_m = mx;
+            } else {
+                // Keep a stale maximum while the new one is less than 2^8 above it: P stays <= 256, which
+                // fp16/bf16 and the fp32 sums hold exactly as well, and O needs no rescale.
+                const bool need = (mx - row_m) * c > 8.f;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float mn = fmaxf(row_m, mx);
+                    const float a = ex2((row_m - mn) * c);
+                    row_l *= a;
+                    row_m = mn;
+                    // The commit that completed S_i(j) was issued after PV_i(j-1), so O_i is quiescent here.
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + 32u * q, o);
+                        tmem_wait_ld();
+                        reg_fence32(o);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * a);
+                        tmem_st32(tO + 32u * q, o);
+                    }
+                }
+            }
+            const float mc = row_m * c;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int e = 0; e < 16; e++) {
+                    const float p0 = ex2(fmaf(__uint_as_float(s[2 * q][2 * e]), c, -mc));
+                    const float p1 = ex2(fmaf(__uint_as_float(s[2 * q][2 * e + 1]), c, -mc));
+                    const float p2 = ex2(fmaf(__uint_as_float(s[2 * q + 1][2 * e]), c, -mc));
+                    const float p3 = ex2(fmaf(__uint_as_float(s[2 * q + 1][2 * e + 1]), c, -mc));
+                    sum0 += p0 + p1;
+                    sum1 += p2 + p3;
+                    pk[e] = pack16<DT>(p0, p1);
+                    pk[16 + e] = pack16<DT>(p2, p3);
+                }
+                tmem_st32(tS + 32u * q, pk);                       // P: key pair (2c, 2c+1) in column c
+            }
+            row_l += sum0 + sum1;
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_PFULL + i));
+        }
+        if (ok && nb > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), 0u, abort_flag));
+            tc_fence_after();
+        }
+#ifdef KB_DEBUG
+        if (p.dbg && ok && nb > 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            float* d = p.dbg + 32768 + (size_t)i * 16384 + (size_t)(tid & 127) * 128;
+            for (int q = 0; q < 4; q++) {
+                uint32_t o[32];
+                tmem_ld32(tO + 32u * q, o);
+                tmem_wait_ld();
+                reg_fence32(o);
+                for (int e = 0; e < 32; e++) d[q * 32 + e] = __uint_as_float(o[e]);
+            }
+            p.dbg[65536 + i * 256 + (tid & 127)] = row_m;
+            p.dbg[65536 + i * 256 + 128 + (tid & 127)] = row_l;
+        }
+#endif
+        // -------------------------------------------------------------------- epilogue (softmax warps)
+        if (MODE == MODE_PAIR) {
+            if (ok && nblk[warp >> 2] > 0) {
+                const int i = warp >> 2;
+                const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+                const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(i * 128);
+                const float mc = row_m * p.scale_log2;
+                float scale = 1.f, l = row_l;
+                if (p.npad[0]) {                                         // engine/src/tcflash.cuh:140-144
+                    const float mn = fmaxf(mc, 0.f);
+                    scale = exp2f(mc - mn);
+                    l = l * scale + (float)p.npad[0] * exp2f(-mn);
+                }
+                const float inv = scale / l;
+                const int row = q0 + i * BM + (tid & 127);
+                OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    uint32_t o[32];
+                    float v[32];
+                    tmem_ld32(tO + 32u * q, o);
+                    tmem_wait_ld();
+                    reg_fence32(o);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
+                    if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                }
+            }
+            tc_fence_before();
+            cta_sync();
+        } else {
+            // NAG combine (engine/src/dit.cu:295-324) on Z+ = O0/l0 and Z- = O1/l1 without leaving the chip.
+            float* const f_inv = fbuf;             // [2][128]  1/l per stream
+            float* const f_part = fbuf + 256;      // [2 column halves][2 norms][128]
+            float* const f_hsum = fbuf + 768;      // [2 norms][128]  this head's |Z+|_1 and |g|_1
+            const int t = tid & 127, w = warp >> 2;
+            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+            const uint32_t tOp = tmem_base + lane_base + 256u + (uint32_t)(w * 64);
+            const uint32_t tOn = tmem_base + lane_base + 384u + (uint32_t)(w * 64);
+            const float s = p.nag_s, sm1 = p.nag_s - 1.f;
+            {
+                const float mc = row_m * p.scale_log2;
+                float scale = 1.f, l = row_l;
+                if (p.npad[w]) {
+                    const float mn = fmaxf(mc, 0.f);
+                    scale = exp2f(mc - mn);
+                    l = l * scale + (float)p.npad[w] * exp2f(-mn);
+                }
+                f_inv[w * 128 + t] = scale / l;
+            }
+            tc_fence_before();
+            named_bar_sync(1, 256);                                       // both streams' O and 1/l are final
+            const float ip = f_inv[t], in = f_inv[128 + t];
+            float lp = 0.f, lg = 0.f;
+            // warpgroup w takes head columns [64w, 64w+64) of both outputs
+            if (__all_sync(0xffffffffu, ok)) {
+                tc_fence_after();
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    uint32_t a[32], n[32];
+                    tmem_ld32(tOp + 32u * q, a);
+                    tmem_ld32(tOn + 32u * q, n);
+                    tmem_wait_ld();
+                    reg_fence32(a);
+                    reg_fence32(n);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const float pv = __uint_as_float(a[e]) * ip;
+                        const float nv = __uint_as_float(n[e]) * in;
+                        lp += fabsf(pv);
+                        lg += fabsf(pv * s - nv * sm1);
+                    }
+                }
+            }
+            f_part[(w * 2 + 0) * 128 + t] = lp;
+            f_part[(w * 2 + 1) * 128 + t] = lg;
+            named_bar_sync(1, 256);
+            // warpgroup 0 finishes |Z+|_1, warpgroup 1 finishes |g|_1 (fixed order: deterministic)
+            f_hsum[w * 128 + t] = f_part[(0 * 2 + w) * 128 + t] + f_part[(1 * 2 + w) * 128 + t];
+            cta_sync();
+            cluster_arrive();
+            cluster_wait();
+            float tot = 0.f;
+            {
+                const uint32_t nrank = cluster_nctarank();
+                const uint32_t my = smem_u32(&f_hsum[w * 128 + t]);
+                for (uint32_t r = 0; r < nrank; r++) tot += dsmem_ld_f32(my, r);   // rank order: same sum in every CTA
+            }
+            cluster_arrive();                                             // our reads of the peers are done
+            float* const f_tot = f_part;                                  // reuse: [2 norms][128]
+            f_tot[w * 128 + t] = tot;
+            named_bar_sync(1, 256);
+            const float ratio = f_tot[128 + t] / fmaxf(f_tot[t], 1e-12f);
+            const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
+            const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
+            const int row = q0 + t;
+            OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD + w * 64;
+            if (__all_sync(0xffffffffu, ok)) {
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    uint32_t a[32], n[32];
+                    float v[32];
+                    tmem_ld32(tOp + 32u * q, a);
+                    tmem_ld32(tOn + 32u * q, n);
+                    tmem_wait_ld();
+                    reg_fence32(a);
+                    reg_fence32(n);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const float pv = __uint_as_float(a[e]) * ip;
+                        const float nv = __uint_as_float(n[e]) * in;
+                        v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                    }
+                    if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                }
+            }
+            tc_fence_before();
+            cta_sync();
+            cluster_wait();                                               // peers are done reading our f_hsum
+        }
+    } else {
+        setmaxnreg_dec<56>();
+        if (warp == 8) {
+        // ------------------------------------------------------------------ MMA issue (one lane)
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(DT, 0, 0, BM, BN);    // S = Q K^T, both K-major
+            constexpr uint32_t IDESC_PV = idesc_f16(DT, 0, 1, BM, HD);   // O += P V, V is MN-major (rows = keys)
+            uint32_t n = 0;                                              // ring slot being consumed
+            bool good = true;
+            auto kv_wait = [&](uint32_t idx) { return mbar_wait(bar(BAR_KVFULL + idx % NSTAGE), (idx / NSTAGE) & 1u, abort_flag); };
+            auto kv_addr = [&](uint32_t idx) { return sKV + (idx % NSTAGE) * TILE_BYTES; };
+            auto kv_release = [&](uint32_t idx) { tc_commit(bar(BAR_KVEMPTY + idx % NSTAGE)); };
+            auto issue_S = [&](int i, uint32_t k_saddr) {
+                const uint32_t q_saddr = sQ + (MODE == MODE_NAG ? 0 : i) * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint32_t off = (uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u;
+                    mma_ss(tmem_base + (uint32_t)(i * 128), smem_desc_sw128(q_saddr + off, 16, 1024),
+                           smem_desc_sw128(k_saddr + off, 16, 1024), IDESC_S, kk > 0);
+                }
+                tc_commit(bar(BAR_SFULL + i));
+            };
+            auto issue_PV = [&](int i, uint32_t v_saddr, int j, int Tk) {
+                const int valid = min(BN, Tk - j * BN);
+                const int nkk = (valid + 15) >> 4;                       // 16 keys per MMA; P is 0 past `valid`
+                for (int kk = 0; kk < nkk; kk++)
+                    mma_ts(tmem_base + 256u + (uint32_t)(i * 128), tmem_base + (uint32_t)(i * 128) + (uint32_t)(kk * 8),
+                           smem_desc_sw128(v_saddr + (uint32_t)kk * 2048u, HALF_BYTES, 1024), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+            };
+            if (MODE == MODE_PAIR) {
+                const int nb = nblk[0];
+                const bool two = nblk[1] > 0;
+                good = mbar_wait(bar(BAR_QFULL + 0), 0u, abort_flag) && kv_wait(n);
+                if (good) {
+                    issue_S(0, kv_addr(n));
+                    if (two) {
+                        good = mbar_wait(bar(BAR_QFULL + 1), 0u, abort_flag);
+                        if (good) issue_S(1, kv_addr(n));
+                    }
+                    kv_release(n);
+                    ++n;
+                }
+                for (int j = 0; j < nb && good; ++j) {
+                    const uint32_t nv = n, nk = n + 1;
+                    const bool more = j + 1 < nb;
+                    good = kv_wait(nv) && mbar_wait(bar(BAR_PFULL + 0), (uint32_t)(j & 1), abort_flag);
+                    if (!good) break;
+                    tc_fence_after();
+                    issue_PV(0, kv_addr(nv), j, p.Tk[0]);
+                    if (!more) tc_commit(bar(BAR_ODONE + 0));
+                    if (more) {
+                        good = kv_wait(nk);
+                        if (!good) break;
+                        issue_S(0, kv_addr(nk));
+                    }
+                    if (two) {
+                        good = mbar_wait(bar(BAR_PFULL + 1), (uint32_t)(j & 1), abort_flag);
+                        if (!good) break;
+                        tc_fence_after();
+                        issue_PV(1, kv_addr(nv), j, p.Tk[0]);
+                        if (!more) tc_commit(bar(BAR_ODONE + 1));
+                    }
+                    kv_release(nv);
+                    ++n;
+                    if (more) {
+                        if (two) issue_S(1, kv_addr(nk));
+                        kv_release(nk);
+                        ++n;
+                    }
+                }
+            } else {
+                good = mbar_wait(bar(BAR_QFULL + 0), 0u, abort_flag);
+                for (int i = 0; i < 2 && good; i++) {
+                    good = kv_wait(n);
+                    if (good) { issue_S(i, kv_addr(n)); kv_release(n); ++n; }
+                }
+                const int nmax = max(nblk[0], nblk[1]);
+                for (int j = 0; j < nmax && good; ++j) {
+                    for (int i = 0; i < 2 && good; i++) {
+                        if (j >= nblk[i]) continue;
+                        good = kv_wait(n) && mbar_wait(bar(BAR_PFULL + i), (uint32_t)(j & 1), abort_flag);
+                        if (!good) break;
+                        tc_fence_after();
+                        issue_PV(i, kv_addr(n), j, p.Tk[i]);
+                        if (j + 1 == nblk[i]) tc_commit(bar(BAR_ODONE + i));
+                        kv_release(n);
+                        ++n;
+                        if (j + 1 < nblk[i]) {
+                            good = kv_wait(n);
+                            if (!good) break;
+                            issue_S(i, kv_addr(n));
+                            kv_release(n);
+                            ++n;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        } else if (warp == 9) {
+        // ------------------------------------------------------------------ TMA loads (one lane)
+        if (lane == 0) {
+            uint32_t n = 0;
+            bool good = true;
+            // one 128x128 tile = two 64-column boxes, each landing as a 128-byte-swizzled [128][64] half
+            auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0, int bb) {
+                tma_load_3d(dst, tm, mbar, h * HD, row0, bb);
+                tma_load_3d(dst + HALF_BYTES, tm, mbar, h * HD + 64, row0, bb);
+            };
+            auto load_kv = [&](const CUtensorMap* tm, int row0) {
+                const uint32_t st = n % NSTAGE;
+                good = mbar_wait(bar(BAR_KVEMPTY + st), ((n / NSTAGE) & 1u) ^ 1u, abort_flag);
+                if (!good) return;
+                mbar_expect_tx(bar(BAR_KVFULL + st), TILE_BYTES);
+                load_tile(sKV + st * TILE_BYTES, tm, bar(BAR_KVFULL + st), row0, MODE == MODE_NAG ? 0 : b);
+                ++n;
+            };
+            mbar_expect_tx(bar(BAR_QFULL + 0), TILE_BYTES);
+            load_tile(sQ, &tmQ, bar(BAR_QFULL + 0), q0, b);
+            if (MODE == MODE_PAIR) {
+                const int nb = nblk[0];
+                if (nb > 0) load_kv(&tmK0, 0);
+                if (nblk[1] > 0) {
+                    mbar_expect_tx(bar(BAR_QFULL + 1), TILE_BYTES);
+                    load_tile(sQ + TILE_BYTES, &tmQ, bar(BAR_QFULL + 1), q0 + BM, b);
+                }
+                for (int j = 0; j < nb && good; ++j) {
+                    load_kv(&tmV0, j * BN);
+                    if (good && j + 1 < nb) load_kv(&tmK0, (j + 1) * BN);
+                }
+            } else {
+                if (nblk[0] > 0) load_kv(&tmK0, 0);
+                if (good && nblk[1] > 0) load_kv(&tmK1, 0);
+                const int nmax = max(nblk[0], nblk[1]);
+                for (int j = 0; j < nmax && good; ++j) {
+                    for (int i = 0; i < 2 && good; i++) {
+                        if (j >= nblk[i]) continue;
+                        load_kv(i ? &tmV1 : &tmV0, j * BN);
+                        if (good && j + 1 < nblk[i]) load_kv(i ? &tmK1 : &tmK0, (j + 1) * BN);
+                    }
+                }
+            }
+            // on failure, let the copies already in flight land before the CTA's shared memory goes away
+            if (!good || *abort_flag) {
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 20000ull) {}
+            }
+        }
+        __syncwarp();
+    }
+
+        // the same full-CTA and cluster barriers the softmax branch runs
+        if (MODE == MODE_PAIR) {
+            cta_sync();
+        } else {
+            cta_sync();
+            cluster_arrive();
+            cluster_wait();
+            cluster_arrive();
+            cta_sync();
+            cluster_wait();
+        }
+        if (warp == 8) {
+            if (lane == 0 && *abort_flag) atomicOr(p.status, ST_TIMEOUT);
+            tc_fence_after();
+            tmem_dealloc(tmem_base, 512);
+        }
+    }
+}
+
+}  // namespace kb

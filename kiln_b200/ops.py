@@ -1,0 +1,129 @@
+"""ctypes binding of the C ABI (include/kiln_b200.h) plus thin torch-tensor helpers.
+
+The helpers take torch CUDA tensors only to get device pointers, strides and the current stream;
+all arithmetic happens in the library's kernels. Argument names and meaning follow the engine's
+op set (reference: engine/src/gpu.h:149-156): row-major [rows, ld] activations, head h at columns
+[h*128, (h+1)*128), `npad` zero keys joining the softmax.
+"""
+import ctypes
+import os
+
+KB_F16, KB_BF16, KB_F32 = 0, 1, 2
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_PKG, "lib", "libkiln_b200.so")
+_lib = None
+
+
+class KilnError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the engine's shim throws std::runtime_error here)."""
+
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__(f"{what}: {lib().kb_error_string(code).decode()} ({code})")
+
+
+def lib():
+    """Load the in-tree library; fails loudly when it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise FileNotFoundError(f"{_LIB_PATH} is missing: run `python -m kiln_b200.build` (nvcc, sm_100a)")
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i, f, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+        L.kb_error_string.restype = ctypes.c_char_p
+        L.kb_error_string.argtypes = [i]
+        L.kb_version.restype = i
+        L.kb_init.restype = i
+        L.kb_attn_workspace_bytes.restype = sz
+        L.kb_attn_workspace_bytes.argtypes = [i, i, i, i, i]
+        L.kb_attn_self.restype = i
+        L.kb_attn_self.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_attn_cross.restype = i
+        L.kb_attn_cross.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_attn_nag.restype = i
+        L.kb_attn_nag.argtypes = [vp, vp, vp, vp, vp, i, i, vp, vp, i, i, f, f, f, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_qk_prep.restype = i
+        L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
+        L.kb_status.restype = i
+        L.kb_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        L.kb_selfcheck_workspace_bytes.restype = sz
+        L.kb_attn_selfcheck.restype = i
+        L.kb_attn_selfcheck.argtypes = [vp, sz, ctypes.POINTER(ctypes.c_float), vp]
+        _lib = L
+    return _lib
+
+
+def _dt(t):
+    import torch
+    return {torch.float16: KB_F16, torch.bfloat16: KB_BF16, torch.float32: KB_F32}[t.dtype]
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _ld(t):
+    assert t.dim() == 2 and t.stride(1) == 1, "activations are row-major [rows, ld]"
+    return t.stride(0)
+
+
+def _stream():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code, what):
+    if code != 0:
+        raise KilnError(code, what)
+
+
+def workspace_bytes(rows_q, rows_k, H, norm_q, norm_k):
+    return lib().kb_attn_workspace_bytes(rows_q, rows_k, H, int(bool(norm_q)), int(bool(norm_k)))
+
+
+def _ws(workspace):
+    if workspace is None:
+        return None, 0
+    return _ptr(workspace), workspace.numel() * workspace.element_size()
+
+
+def attn_self(out, q, k, v, B, T, H, qn_w=None, kn_w=None, rope_cos=None, rope_sin=None, eps=1e-6, workspace=None):
+    """Self-attention of B images of T tokens; q, k, v, out are [B*T, ld] tensors (out may be fp32)."""
+    wp, wb = _ws(workspace)
+    _check(lib().kb_attn_self(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(qn_w), _ptr(kn_w), _ptr(rope_cos), _ptr(rope_sin),
+                              B, T, H, _ld(q), _ld(k), _ld(v), _ld(out), _dt(q), _dt(out), eps, wp, wb, _stream()), "kb_attn_self")
+    return out
+
+
+def attn_cross(out, q, k, v, Tq, Tk, npad, H, qn_w=None, eps=1e-6, workspace=None):
+    """Cross-attention to one context: the first Tk rows of k, v are real, npad zero keys join the softmax."""
+    wp, wb = _ws(workspace)
+    _check(lib().kb_attn_cross(_ptr(out), _ptr(q), _ptr(qn_w), _ptr(k), _ptr(v), Tq, Tk, npad, H, _ld(q), _ld(k), _ld(v),
+                               _ld(out), _dt(q), _dt(out), eps, wp, wb, _stream()), "kb_attn_cross")
+    return out
+
+
+def attn_nag(out, q, k_pos, v_pos, Tk_pos, npad_pos, k_neg, v_neg, Tk_neg, npad_neg, scale, tau, alpha, Tq, H,
+             qn_w=None, eps=1e-6, workspace=None):
+    """Cross-attention to a positive and a negative context followed by the NAG combine, in one kernel."""
+    assert _ld(k_pos) == _ld(v_pos) == _ld(k_neg) == _ld(v_neg)
+    wp, wb = _ws(workspace)
+    _check(lib().kb_attn_nag(_ptr(out), _ptr(q), _ptr(qn_w), _ptr(k_pos), _ptr(v_pos), Tk_pos, npad_pos, _ptr(k_neg),
+                             _ptr(v_neg), Tk_neg, npad_neg, scale, tau, alpha, Tq, H, _ld(q), _ld(k_pos), _ld(out), _dt(q),
+                             _dt(out), eps, wp, wb, _stream()), "kb_attn_nag")
+    return out
+
+
+def qk_prep(out, x, rows, H, T, w=None, rope_cos=None, rope_sin=None, eps=1e-6):
+    """out = rope(rmsnorm(x)) per (row, head) as 16-bit; a plain conversion when w and the tables are None."""
+    _check(lib().kb_qk_prep(_ptr(out), _ld(out), _dt(out), _ptr(x), _ld(x), _dt(x), rows, H, T, _ptr(w), eps, _ptr(rope_cos),
+                            _ptr(rope_sin), _stream()), "kb_qk_prep")
+    return out
+
+
+def check_status():
+    """Synchronise and raise if any kernel since the last call gave up on a bounded wait."""
+    bits = ctypes.c_uint(0)
+    _check(lib().kb_status(ctypes.byref(bits)), "kb_status")
+    return bits.value

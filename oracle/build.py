@@ -1,0 +1,61 @@
+"""Build recipe for the test oracle (TEST INFRASTRUCTURE; the shipped library never uses it).
+
+    python oracle/build.py            # oracle/libkiln_oracle.so  (CPU restatement, gcc + OpenMP)
+    python oracle/build.py --ref DIR  # oracle/_ref/libkiln_ref.so (the reference's own CUDA kernels,
+                                      # compiled for sm_100a from the sources where they lie under DIR)
+
+Nothing from the reference tree is copied: ref_wrap.cu only #includes its files by path, and the
+output goes to oracle/_ref/, which is kept out of version control.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libkiln_oracle.so")
+REF_DIR = os.path.join(HERE, "_ref")
+REF_SO = os.path.join(REF_DIR, "libkiln_ref.so")
+GCC_B = "/usr/lib/gcc/x86_64-linux-gnu/13/"   # where libgomp.spec lives on images whose gcc wrapper hides it
+
+
+def _newer(target, *deps):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(d) <= t for d in deps)
+
+
+def build_oracle(force=False):
+    src = os.path.join(HERE, "kiln_oracle.c")
+    if not force and _newer(ORACLE_SO, src):
+        return ORACLE_SO
+    base = ["gcc", "-O3", "-fopenmp", "-fPIC", "-mavx2", "-mfma", "-fno-math-errno", "-shared", "-o", ORACLE_SO, src, "-lm"]
+    r = subprocess.run(base, capture_output=True, text=True)
+    if r.returncode != 0 and os.path.isdir(GCC_B):
+        r = subprocess.run(base[:1] + ["-B" + GCC_B] + base[1:], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + r.stderr)
+    return ORACLE_SO
+
+
+def build_ref(ref_root, force=False):
+    """Compile the reference's attention / norm / rope / NAG kernels for sm_100a (GPU-side oracle)."""
+    src = os.path.join(HERE, "ref_wrap.cu")
+    if not os.path.isdir(os.path.join(ref_root, "engine", "src")):
+        raise FileNotFoundError(ref_root)
+    if not force and _newer(REF_SO, src):
+        return REF_SO
+    os.makedirs(REF_DIR, exist_ok=True)
+    cmd = ["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-Xcompiler", "-fPIC", "-shared", "-I" + os.path.join(ref_root, "engine", "src"),
+           "-I" + os.path.join(ref_root, "bench"), "-o", REF_SO, src, "-lcublas", "-Xlinker", "--no-undefined"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("reference kernel build failed:\n" + r.stderr[-4000:])
+    return REF_SO
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="--force" in sys.argv))
+    if "--ref" in sys.argv:
+        print(build_ref(sys.argv[sys.argv.index("--ref") + 1], force=True))

@@ -1,0 +1,108 @@
+"""ctypes wrapper of the CPU oracle (oracle/kiln_oracle.c). TEST INFRASTRUCTURE ONLY:
+imported by tests/, the smoke check and the benchmark's CPU baseline, never by the library."""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "libkiln_oracle.so")
+        if not os.path.exists(path):
+            import importlib.util
+            spec = importlib.util.spec_from_file_location("_kiln_oracle_build", os.path.join(_HERE, "build.py"))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            mod.build_oracle()
+        L = ctypes.CDLL(path)
+        vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        L.ko_max_threads.restype = i
+        for name in ("ko_attention_f32", "ko_attention_f64"):
+            getattr(L, name).argtypes = [vp, i, vp, i, vp, i, vp, i, i, i, i, i]
+            getattr(L, name).restype = None
+        L.ko_rmsnorm.argtypes = [vp, vp, vp, ctypes.c_size_t, i, f]
+        L.ko_rope_half.argtypes = [vp, i, i, i, vp, vp]
+        L.ko_cosmos_rope.argtypes = [vp, vp, i, i]
+        L.ko_nag.argtypes = [vp, vp, i, i, f, f, f, i]
+        L.ko_torch_randn.argtypes = [ctypes.c_uint64, ctypes.c_size_t, vp]
+        L.ko_torch_randn.restype = i
+        L.ko_round16.argtypes = [vp, ctypes.c_size_t, i]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a
+
+
+def max_threads():
+    return lib().ko_max_threads()
+
+
+def randn(seed, n):
+    """torch.manual_seed(seed); torch.randn(n) on CPU, restated (reference: engine/src/pipeline.cu:16-64)."""
+    out = np.empty(n, np.float32)
+    if lib().ko_torch_randn(seed, n, _p(out)) != 0:
+        raise ValueError("n must be >= 16")
+    return out
+
+
+def round16(x, kind):
+    """Round an fp32 array through fp16 (kind 0) or bf16 (kind 1), returning fp32."""
+    x = _f32(x).copy()
+    lib().ko_round16(_p(x), x.size, kind)
+    return x
+
+
+def attention(q, k, v, H, npad=0, acc64=True):
+    """q [Tq, >=H*128], k/v [Tk, >=H*128] fp32 -> out [Tq, H*128] (reference: bench/tfa_test.cu:11-33)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    Tq, Tk = q.shape[0], k.shape[0]
+    out = np.zeros((Tq, H * 128), np.float32)
+    fn = lib().ko_attention_f64 if acc64 else lib().ko_attention_f32
+    fn(_p(out), out.shape[1], _p(q), q.shape[1], _p(k), k.shape[1], _p(v), v.shape[1], Tq, Tk, H, npad)
+    return out
+
+
+def rmsnorm(x, w_bf16_bits, H, eps=1e-6):
+    """x [rows, H*128] -> per (row, head) RMSNorm with bf16 weight bits [128] (reference: engine/src/kernels.cu:656-666)."""
+    x = _f32(x)
+    assert x.shape[1] == H * 128
+    y = np.empty_like(x)
+    w = None if w_bf16_bits is None else np.ascontiguousarray(w_bf16_bits, dtype=np.uint16)
+    lib().ko_rmsnorm(_p(y), _p(x), None if w is None else _p(w), x.shape[0] * H, 128, eps)
+    return y
+
+
+def rope_half(x, T, H, cos_t, sin_t):
+    """In-place rotate-half RoPE on a copy of x [T, H*128] (reference: engine/src/kernels.cu:759-772)."""
+    x = _f32(x).copy()
+    assert x.shape == (T, H * 128)
+    lib().ko_rope_half(_p(x), T, H, 128, _p(_f32(cos_t)), _p(_f32(sin_t)))
+    return x
+
+
+def cosmos_rope(Hp, Wp):
+    """cos, sin tables [Hp*Wp, 64] (reference: engine/src/dit.cu:196-215)."""
+    c = np.empty((Hp * Wp, 64), np.float32)
+    s = np.empty_like(c)
+    lib().ko_cosmos_rope(_p(c), _p(s), Hp, Wp)
+    return c, s
+
+
+def nag(zp, zn, s, tau, alpha, acc64=True):
+    """NAG combine of Z+ and Z- [T, dim] -> [T, dim] (reference: engine/src/dit.cu:295-324)."""
+    a = _f32(zp).copy()
+    n = _f32(zn)
+    lib().ko_nag(_p(a), _p(n), a.shape[0], a.shape[1], s, tau, alpha, int(acc64))
+    return a
