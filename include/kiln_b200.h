@@ -11,7 +11,8 @@
  *   - activations are row-major [rows, ld] with head h at columns [h*128, (h+1)*128), the layout of
  *     the engine's op set (reference: engine/src/gpu.h:149-156); `ld_*` are in ELEMENTS;
  *   - head size is 128 (the only size the reference's fused kernels take: engine/src/tcflash.cuh:170-172);
- *   - row pointers must be 16-byte aligned and ld a multiple of 8 (reference: engine/src/tcflash.cuh:169).
+ *   - row pointers must be 16-byte aligned and ld a multiple of 8 elements, 4 for fp32 (reference:
+ *     engine/src/tcflash.cuh:169); the workspace must be 16-byte aligned.
  *
  * `npad` has the reference's meaning (engine/src/gpu.h:149-151): npad extra keys that are exactly
  * zero (K = 0, V = 0) join the softmax analytically. Reference semantics for a padded text context
@@ -26,7 +27,12 @@
 extern "C" {
 #endif
 
-/* element types of Q/K/V (`dtype`) and of the output (`out_dtype`: same as dtype, or KB_F32) */
+/* Element types of Q/K/V (`dtype`) and of the output (`out_dtype`), chosen independently.
+ * The tensor-core operands are always fp16 with fp32 accumulation, as in the reference kernel, which
+ * converts its fp32 inputs to fp16 while staging (engine/src/tcflash.cuh:56-64): KB_F16 inputs that need
+ * neither norm nor RoPE are read in place; KB_BF16 / KB_F32 inputs, and any tensor that gets RMSNorm or
+ * RoPE, are staged once as fp16 in the caller's workspace by a fused pre-pass. KB_F32 inputs are what the
+ * engine holds today (engine/src/dit.cu:429-430). */
 enum { KB_F16 = 0, KB_BF16 = 1, KB_F32 = 2 };
 
 enum {
@@ -48,9 +54,11 @@ int kb_version(void);
  * launch entry point; call it once up front to keep the first launch cheap. */
 int kb_init(void);
 
-/* Bytes of scratch the attention entry points need: room for the normalised/rotated 16-bit copies of
- * Q (norm_q != 0) and K (norm_k != 0). rows_q = B*Tq, rows_k = B*Tk. */
-size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int H, int norm_q, int norm_k);
+/* Bytes of scratch an attention call needs: room for the fp16 staging copies of Q (when dtype is not
+ * KB_F16 or norm_q != 0), of K per context (dtype not KB_F16 or norm_k != 0) and of V per context
+ * (dtype not KB_F16). rows_q = B*Tq, rows_k = B*Tk (the largest context for NAG), n_ctx = 1, or 2 for
+ * kb_attn_nag. norm_q / norm_k: that tensor gets RMSNorm and/or RoPE. */
+size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int n_ctx, int H, int dtype, int norm_q, int norm_k);
 
 /* Self-attention of B images, T tokens each (Tq = Tk = T), no padding.
  * Replaces, per DiT block, the reference sequence rmsnorm(Q), rmsnorm(K), rope_half(Q), rope_half(K),

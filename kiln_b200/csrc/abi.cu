@@ -55,14 +55,12 @@ int init_device(DeviceState& st, int dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     int rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_F16, __half>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_F16, float>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_BF16, __nv_bfloat16>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, DT_BF16, float>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_F16, __half>, true))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_F16, float>, true))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_BF16, __nv_bfloat16>, true))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, DT_BF16, float>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>, false))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>, true))) return rc;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return KB_ERR_CUDA;
     st.status = static_cast<unsigned int*>(p);
@@ -88,46 +86,49 @@ int get_state(DeviceState** out) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
-// [batches][rows][H*128] view of a row-major 16-bit matrix with row stride ld; box = 64 columns x 128 rows
-int make_tmap(CUtensorMap* tm, const void* ptr, int dtype, int rows, int H, int batches, int ld) {
+// [batches][rows][H*128] view of a row-major fp16 matrix with row stride ld; box = 64 columns x 128 rows
+int make_tmap(CUtensorMap* tm, const void* ptr, int rows, int H, int batches, int ld) {
     const cuuint64_t dims[3] = {(cuuint64_t)H * 128, (cuuint64_t)rows, (cuuint64_t)batches};
     const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows * (cuuint64_t)ld * 2};
     const cuuint32_t box[3] = {64, 128, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(tm, dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                           const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? KB_OK : KB_ERR_CUDA;
 }
 
-int check_mat(const void* p, int ld, int H) {
+int check_mat(const void* p, int ld, int H, int dtype) {
     if (!p) return KB_ERR_ARG;
-    if (!aligned16(p) || (ld & 7)) return KB_ERR_ALIGN;
+    if (!aligned16(p) || (ld & (dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
     if (ld < H * 128) return KB_ERR_SHAPE;
     return KB_OK;
 }
 
-int check_out(const void* p, int ld, int H, int dtype, int out_dtype) {
+int check_out(const void* p, int ld, int H, int out_dtype) {
     if (!p) return KB_ERR_ARG;
-    if (out_dtype != dtype && out_dtype != KB_F32) return KB_ERR_ARG;
+    if (out_dtype != KB_F16 && out_dtype != KB_BF16 && out_dtype != KB_F32) return KB_ERR_ARG;
     if (!aligned16(p) || (ld & (out_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
     if (ld < H * 128) return KB_ERR_SHAPE;
     return KB_OK;
 }
 
-template <typename InT, typename OutT>
-void launch_prep_t(void* out, int ld_out, const void* in, int ld_in, int rows, int H, int T, const void* w, float eps,
-                   const float* c, const float* s, cudaStream_t stream) {
-    const long long items = (long long)rows * H;
-    const unsigned grid = (unsigned)((items + 7) / 8);
-    qk_prep_kernel<InT, OutT><<<grid, 256, 0, stream>>>(static_cast<OutT*>(out), ld_out, static_cast<const InT*>(in), ld_in, rows, H, T,
-                                                       static_cast<const __nv_bfloat16*>(w), eps, c, s);
-}
+// Collects the tensors one launch of the pre-pass stages.
+struct PrepBatch {
+    PrepParams pp = {};
+    void add(void* out, int ld_out, const void* in, int ld_in, int rows, int T, const void* w, const float* c, const float* s) {
+        PrepSeg& sg = pp.seg[pp.nseg++];
+        sg.in = in; sg.out = out; sg.w = static_cast<const __nv_bfloat16*>(w); sg.cos_t = c; sg.sin_t = s;
+        sg.rows = rows; sg.ld_in = ld_in; sg.ld_out = ld_out; sg.T = T > 0 ? T : 1;
+        sg.item0 = pp.items;
+        pp.items += (long long)rows * pp.H;
+    }
+};
 
-int launch_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
-                const void* w, float eps, const float* c, const float* s, cudaStream_t stream) {
-    if (rows <= 0) return KB_OK;
-#define KB_PREP(IN, OUT) launch_prep_t<IN, OUT>(out, ld_out, in, ld_in, rows, H, T, w, eps, c, s, stream)
+int launch_prep(const PrepBatch& pb, int in_dtype, int out_dtype, cudaStream_t stream) {
+    if (pb.pp.items <= 0) return KB_OK;
+    const unsigned grid = (unsigned)((pb.pp.items + 7) / 8);
+#define KB_PREP(IN, OUT) qk_prep_kernel<IN, OUT><<<grid, 256, 0, stream>>>(pb.pp)
     if (out_dtype == KB_F16) {
         if (in_dtype == KB_F16) KB_PREP(__half, __half);
         else if (in_dtype == KB_BF16) KB_PREP(__nv_bfloat16, __half);
@@ -141,7 +142,7 @@ int launch_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in,
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
-template <int MODE, int DT, typename OutT>
+template <int MODE, typename OutT>
 int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
                   const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
@@ -161,19 +162,16 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, DT, OutT>, tq, tk0, tv0, tk1, tv1, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, OutT>, tq, tk0, tv0, tk1, tv1, p);
     return e == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 template <int MODE>
-int launch_attn(int dtype, int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0,
-                const CUtensorMap& tk1, const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
-    if (dtype == KB_F16) {
-        if (out_dtype == KB_F32) return launch_attn_t<MODE, DT_F16, float>(tq, tk0, tv0, tk1, tv1, p, stream);
-        return launch_attn_t<MODE, DT_F16, __half>(tq, tk0, tv0, tk1, tv1, p, stream);
-    }
-    if (out_dtype == KB_F32) return launch_attn_t<MODE, DT_BF16, float>(tq, tk0, tv0, tk1, tv1, p, stream);
-    return launch_attn_t<MODE, DT_BF16, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, p, stream);
+int launch_attn(int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
+                const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
+    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, p, stream);
+    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, p, stream);
+    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, p, stream);
 }
 
 #ifdef KB_DEBUG
@@ -185,39 +183,52 @@ float* g_dbg = nullptr;
 
 constexpr float SCALE_LOG2 = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
 
+inline bool valid_in_dtype(int d) { return d == KB_F16 || d == KB_BF16 || d == KB_F32; }
+
+// A tensor is staged (copied as fp16 into the workspace) when it is not fp16 already or needs norm/RoPE.
+struct Stage {
+    char* ws;
+    size_t left;
+    bool overflow = false;
+    void* take(size_t rows, int H) {
+        const size_t n = align256(rows * (size_t)H * 128 * 2);
+        if (!ws || n > left) { overflow = true; return nullptr; }
+        void* p = ws;
+        ws += n; left -= n;
+        return p;
+    }
+};
+
 // shared body of self- and cross-attention: q [B*Tq], k/v [B*Tk]
 int attn_pair(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
               const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk, int npad, int H, int ld_q, int ld_k,
               int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes,
               cudaStream_t stream) {
-    if (dtype != KB_F16 && dtype != KB_BF16) return KB_ERR_ARG;
+    if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || npad < 0) return KB_ERR_ARG;
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
     int rc;
-    if ((rc = check_mat(q, ld_q, H)) || (rc = check_mat(k, ld_k, H)) || (rc = check_mat(v, ld_v, H)) ||
-        (rc = check_out(out, ld_o, H, dtype, out_dtype)))
+    if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k, ld_k, H, dtype)) || (rc = check_mat(v, ld_v, H, dtype)) ||
+        (rc = check_out(out, ld_o, H, out_dtype)))
         return rc;
     DeviceState* st;
     if ((rc = get_state(&st))) return rc;
 
-    const bool prep_q = qn_w || rope_cos, prep_k = kn_w || rope_cos;
-    const size_t need = kb_attn_workspace_bytes(B * Tq, B * Tk, H, prep_q, prep_k);
-    if (need && (!workspace || workspace_bytes < need || !aligned16(workspace))) return KB_ERR_WORKSPACE;
-    const void* qq = q; const void* kk = k;
-    int ldq = ld_q, ldk = ld_k;
-    char* ws = static_cast<char*>(workspace);
-    if (prep_q) {
-        if ((rc = launch_prep(ws, H * 128, dtype, q, ld_q, dtype, B * Tq, H, Tq, qn_w, eps, rope_cos, rope_sin, stream))) return rc;
-        qq = ws; ldq = H * 128;
-        ws += align256((size_t)B * Tq * H * 128 * 2);
-    }
-    if (prep_k) {
-        if ((rc = launch_prep(ws, H * 128, dtype, k, ld_k, dtype, B * Tk, H, Tk, kn_w, eps, rope_cos, rope_sin, stream))) return rc;
-        kk = ws; ldk = H * 128;
-    }
+    const bool conv = dtype != KB_F16;
+    const bool stage_q = conv || qn_w || rope_cos, stage_k = conv || kn_w || rope_cos, stage_v = conv;
+    if ((stage_q || stage_k || stage_v) && (!workspace || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    Stage sg{static_cast<char*>(workspace), workspace_bytes};
+    PrepBatch pb;
+    pb.pp.H = H; pb.pp.eps = eps;
+    const void *qq = q, *kk = k, *vv = v;
+    int ldq = ld_q, ldk = ld_k, ldv = ld_v;
+    if (stage_q) { void* d = sg.take((size_t)B * Tq, H); if (d) pb.add(d, H * 128, q, ld_q, B * Tq, Tq, qn_w, rope_cos, rope_sin); qq = d; ldq = H * 128; }
+    if (stage_k) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, k, ld_k, B * Tk, Tk, kn_w, rope_cos, rope_sin); kk = d; ldk = H * 128; }
+    if (stage_v) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, v, ld_v, B * Tk, Tk, nullptr, nullptr, nullptr); vv = d; ldv = H * 128; }
+    if (sg.overflow) return KB_ERR_WORKSPACE;
+    if ((rc = launch_prep(pb, dtype, KB_F16, stream))) return rc;
     CUtensorMap tq, tk, tv;
-    if ((rc = make_tmap(&tq, qq, dtype, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, dtype, Tk, H, B, ldk)) ||
-        (rc = make_tmap(&tv, v, dtype, Tk, H, B, ld_v)))
+    if ((rc = make_tmap(&tq, qq, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, Tk, H, B, ldk)) || (rc = make_tmap(&tv, vv, Tk, H, B, ldv)))
         return rc;
     AttnParams p = {};
     p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = B;
@@ -225,7 +236,7 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
     KB_SET_DBG(p);
-    return launch_attn<MODE_PAIR>(dtype, out_dtype, tq, tk, tv, tk, tv, p, stream);
+    return launch_attn<MODE_PAIR>(out_dtype, tq, tk, tv, tk, tv, p, stream);
 }
 
 }  // namespace
@@ -259,10 +270,12 @@ int kb_init(void) {
     return get_state(&st);
 }
 
-size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int H, int norm_q, int norm_k) {
+size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int n_ctx, int H, int dtype, int norm_q, int norm_k) {
+    const bool conv = dtype != KB_F16;
     size_t n = 0;
-    if (norm_q) n += align256((size_t)rows_q * H * 128 * 2);
-    if (norm_k) n += align256((size_t)rows_k * H * 128 * 2);
+    if (conv || norm_q) n += align256((size_t)rows_q * H * 128 * 2);
+    if (conv || norm_k) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);   // K of every context
+    if (conv) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);             // V of every context
     return n;
 }
 
@@ -285,27 +298,39 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
                 int H, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
                 size_t workspace_bytes, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (dtype != KB_F16 && dtype != KB_BF16) return KB_ERR_ARG;
+    if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (Tq <= 0 || Tk_pos <= 0 || Tk_neg <= 0 || H <= 0 || npad_pos < 0 || npad_neg < 0) return KB_ERR_ARG;
     if (H > 16 || (H & (H - 1))) return KB_ERR_SHAPE;  // the heads of a query tile are one cluster
     int rc;
-    if ((rc = check_mat(q, ld_q, H)) || (rc = check_mat(k_pos, ld_kv, H)) || (rc = check_mat(v_pos, ld_kv, H)) ||
-        (rc = check_mat(k_neg, ld_kv, H)) || (rc = check_mat(v_neg, ld_kv, H)) || (rc = check_out(out, ld_o, H, dtype, out_dtype)))
+    if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k_pos, ld_kv, H, dtype)) || (rc = check_mat(v_pos, ld_kv, H, dtype)) ||
+        (rc = check_mat(k_neg, ld_kv, H, dtype)) || (rc = check_mat(v_neg, ld_kv, H, dtype)) || (rc = check_out(out, ld_o, H, out_dtype)))
         return rc;
     DeviceState* st;
     if ((rc = get_state(&st))) return rc;
-    const size_t need = kb_attn_workspace_bytes(Tq, 0, H, qn_w != nullptr, 0);
-    if (need && (!workspace || workspace_bytes < need || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    const bool conv = dtype != KB_F16;
+    if ((conv || qn_w) && (!workspace || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    Stage sg{static_cast<char*>(workspace), workspace_bytes};
+    PrepBatch pb;
+    pb.pp.H = H; pb.pp.eps = eps;
     const void* qq = q;
-    int ldq = ld_q;
-    if (qn_w) {
-        if ((rc = launch_prep(workspace, H * 128, dtype, q, ld_q, dtype, Tq, H, Tq, qn_w, eps, nullptr, nullptr, stream))) return rc;
-        qq = workspace; ldq = H * 128;
+    const void* kv[4] = {k_pos, v_pos, k_neg, v_neg};
+    const int kv_rows[4] = {Tk_pos, Tk_pos, Tk_neg, Tk_neg};
+    int ldq = ld_q, ldkv = ld_kv;
+    if (conv || qn_w) { void* d = sg.take((size_t)Tq, H); if (d) pb.add(d, H * 128, q, ld_q, Tq, Tq, qn_w, nullptr, nullptr); qq = d; ldq = H * 128; }
+    if (conv) {
+        for (int i = 0; i < 4; i++) {
+            void* d = sg.take((size_t)kv_rows[i], H);
+            if (d) pb.add(d, H * 128, kv[i], ld_kv, kv_rows[i], kv_rows[i], nullptr, nullptr, nullptr);
+            kv[i] = d;
+        }
+        ldkv = H * 128;
     }
+    if (sg.overflow) return KB_ERR_WORKSPACE;
+    if ((rc = launch_prep(pb, dtype, KB_F16, stream))) return rc;
     CUtensorMap tq, tk0, tv0, tk1, tv1;
-    if ((rc = make_tmap(&tq, qq, dtype, Tq, H, 1, ldq)) || (rc = make_tmap(&tk0, k_pos, dtype, Tk_pos, H, 1, ld_kv)) ||
-        (rc = make_tmap(&tv0, v_pos, dtype, Tk_pos, H, 1, ld_kv)) || (rc = make_tmap(&tk1, k_neg, dtype, Tk_neg, H, 1, ld_kv)) ||
-        (rc = make_tmap(&tv1, v_neg, dtype, Tk_neg, H, 1, ld_kv)))
+    if ((rc = make_tmap(&tq, qq, Tq, H, 1, ldq)) || (rc = make_tmap(&tk0, kv[0], Tk_pos, H, 1, ldkv)) ||
+        (rc = make_tmap(&tv0, kv[1], Tk_pos, H, 1, ldkv)) || (rc = make_tmap(&tk1, kv[2], Tk_neg, H, 1, ldkv)) ||
+        (rc = make_tmap(&tv1, kv[3], Tk_neg, H, 1, ldkv)))
         return rc;
     AttnParams p = {};
     p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = 1;
@@ -314,7 +339,7 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     p.nag_s = scale; p.nag_tau = tau; p.nag_alpha = alpha;
     p.status = st->status;
     KB_SET_DBG(p);
-    return launch_attn<MODE_NAG>(dtype, out_dtype, tq, tk0, tv0, tk1, tv1, p, stream);
+    return launch_attn<MODE_NAG>(out_dtype, tq, tk0, tv0, tk1, tv1, p, stream);
 }
 
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
@@ -323,13 +348,15 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
     if (out_dtype != KB_F16 && out_dtype != KB_BF16) return KB_ERR_ARG;
     if (in_dtype != KB_F16 && in_dtype != KB_BF16 && in_dtype != KB_F32) return KB_ERR_ARG;
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
-    if (!aligned16(out) || !aligned16(in) || (ld_out & 7) || (ld_in & 7)) return KB_ERR_ALIGN;
+    if (!aligned16(out) || !aligned16(in) || (ld_out & 7) || (ld_in & (in_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
     if (ld_out < H * 128 || ld_in < H * 128) return KB_ERR_SHAPE;
     DeviceState* st;
     int rc;
     if ((rc = get_state(&st))) return rc;
-    return launch_prep(out, ld_out, out_dtype, in, ld_in, in_dtype, rows, H, T, w_bf16, eps, rope_cos, rope_sin,
-                       static_cast<cudaStream_t>(stream));
+    PrepBatch pb;
+    pb.pp.H = H; pb.pp.eps = eps;
+    pb.add(out, ld_out, in, ld_in, rows, T, w_bf16, rope_cos, rope_sin);
+    return launch_prep(pb, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int kb_status(unsigned* status_bits) {
@@ -362,6 +389,8 @@ int kb_attn_selfcheck(void* workspace, size_t workspace_bytes, float* max_abs_er
     float* out = (float*)take((size_t)Tq * ld * 4); float* ref = (float*)take((size_t)Tq * ld * 4);
     float* ref2 = (float*)take((size_t)Tq * ld * 4);
     unsigned int* err = (unsigned int*)take(256);
+    void* stage = take(5 * align256((size_t)Tq * ld * 2));          // fp16 staging of bf16 inputs
+    const size_t stage_bytes = 5 * align256((size_t)Tq * ld * 2);
     const size_t n = (size_t)Tq * ld;
     const unsigned fb = (unsigned)((n + 255) / 256), ab = (unsigned)((Tq * H + 127) / 128);
     if (cudaMemsetAsync(err, 0, 4, stream) != cudaSuccess) return KB_ERR_CUDA;
@@ -384,16 +413,16 @@ int kb_attn_selfcheck(void* workspace, size_t workspace_bytes, float* max_abs_er
             else sc_naive_attn_kernel<__nv_bfloat16><<<ab, 128, 0, stream>>>(o, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kk, (const __nv_bfloat16*)vv, Tq, tk, H, ld, npad);
         };
         // self-shaped (Tq x Tk keys, no padding)
-        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, 0, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, nullptr, 0, stream))) return rc;
+        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, 0, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, stage, stage_bytes, stream))) return rc;
         naive(ref, k, v, Tk, 0);
         sc_maxdiff_kernel<<<fb, 256, 0, stream>>>(out, ref, n, err);
         // cross with analytic padding
-        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tc, 512 - Tc, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, nullptr, 0, stream))) return rc;
+        if ((rc = kb_attn_cross(out, q, nullptr, k, v, Tq, Tc, 512 - Tc, H, ld, ld, ld, ld, dtype, KB_F32, 1e-6f, stage, stage_bytes, stream))) return rc;
         naive(ref, k, v, Tc, 512 - Tc);
         sc_maxdiff_kernel<<<fb, 256, 0, stream>>>(out, ref, n, err);
         // NAG: two contexts, reference defaults s=5 tau=2.5 alpha=0.25 (engine/src/models.h:80)
         if ((rc = kb_attn_nag(out, q, nullptr, k, v, Tc, 512 - Tc, k2, v2, Tn, 512 - Tn, 5.f, 2.5f, 0.25f, Tq, H, ld, ld, ld, dtype, KB_F32,
-                              1e-6f, nullptr, 0, stream)))
+                              1e-6f, stage, stage_bytes, stream)))
             return rc;
         naive(ref2, k2, v2, Tn, 512 - Tn);
         sc_naive_nag_kernel<<<(Tq + 127) / 128, 128, 0, stream>>>(ref, ref2, Tq, ld, 5.f, 2.5f, 0.25f);

@@ -1,5 +1,5 @@
 // Fused multi-head attention forward for head size 128 on sm_100a (B200):
-// TMA-staged Q/K/V tiles (128-byte swizzle), tcgen05 MMAs with the S and O accumulators in TMEM,
+// TMA-staged fp16 Q/K/V tiles (128-byte swizzle), tcgen05 MMAs with the S and O accumulators in TMEM,
 // online softmax with one thread per query row, P handed to the second MMA through TMEM.
 //
 // It replaces the reference's mma.sync FlashAttention-2 kernel tfa::k_flash
@@ -20,7 +20,7 @@
 // owns TMEM lanes 32*(w%4)..+31, one query row per thread), warp 8 issues MMAs (one lane), warp 9
 // issues TMA loads (one lane), warps 10-11 idle.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i overwrites the first
-// 64 columns of S_i as packed 16-bit pairs.
+// 64 columns of S_i as packed fp16 pairs.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -95,7 +95,7 @@ __device__ __forceinline__ void store32(OutT* dst, const float (&v)[32]) {
     }
 }
 
-template <int MODE, int DT, typename OutT>
+template <int MODE, typename OutT>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
@@ -234,8 +234,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const float p3 = ex2(fmaf(__uint_as_float(s[2 * q + 1][2 * e + 1]), c, -mc));
                     sum0 += p0 + p1;
                     sum1 += p2 + p3;
-                    pk[e] = pack16<DT>(p0, p1);
-                    pk[16 + e] = pack16<DT>(p2, p3);
+                    pk[e] = pack16<DT_F16>(p0, p1);
+                    pk[16 + e] = pack16<DT_F16>(p2, p3);
                 }
                 tmem_st32(tS + 32u * q, pk);                       // P: key pair (2c, 2c+1) in column c
             }
@@ -388,8 +388,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (warp == 8) {
         // ------------------------------------------------------------------ MMA issue (one lane)
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(DT, 0, 0, BM, BN);    // S = Q K^T, both K-major
-            constexpr uint32_t IDESC_PV = idesc_f16(DT, 0, 1, BM, HD);   // O += P V, V is MN-major (rows = keys)
+            // Operands are fp16 throughout (bf16/fp32 inputs are staged as fp16 by the pre-pass): with bf16
+            // P the 2^-9 rounding of each weight alone costs ~1e-3 relative error on outputs that are sums
+            // of random-sign terms, and tcgen05 does not take an fp16 A with a bf16 B.
+            constexpr uint32_t IDESC_S = idesc_f16(0, 0, 0, 0, BM, BN);   // S = Q K^T, both K-major
+            constexpr uint32_t IDESC_PV = idesc_f16(0, 0, 0, 1, BM, HD);  // O += P V, V is MN-major (rows = keys)
             uint32_t n = 0;                                              // ring slot being consumed
             bool good = true;
             auto kv_wait = [&](uint32_t idx) { return mbar_wait(bar(BAR_KVFULL + idx % NSTAGE), (idx / NSTAGE) & 1u, abort_flag); };

@@ -112,8 +112,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 }
 // Instruction descriptor for kind::f16: D format fp32 (bit 4), A/B format in [7,10)/[10,13)
 // (0 = fp16, 1 = bf16), A/B major in bits 15/16 (0 = K-major, 1 = MN-major), N>>3 in [17,23), M>>4 in [24,29).
-__host__ __device__ constexpr uint32_t idesc_f16(int bf16, int a_mn_major, int b_mn_major, int M, int N) {
-    return (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | ((uint32_t)a_mn_major << 15) |
+__host__ __device__ constexpr uint32_t idesc_f16(int a_bf16, int b_bf16, int a_mn_major, int b_mn_major, int M, int N) {
+    return (1u << 4) | ((uint32_t)a_bf16 << 7) | ((uint32_t)b_bf16 << 10) | ((uint32_t)a_mn_major << 15) |
            ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 // D[tmem] (+)= A[smem] * B[smem]

@@ -36,7 +36,7 @@ def lib():
         L.kb_version.restype = i
         L.kb_init.restype = i
         L.kb_attn_workspace_bytes.restype = sz
-        L.kb_attn_workspace_bytes.argtypes = [i, i, i, i, i]
+        L.kb_attn_workspace_bytes.argtypes = [i, i, i, i, i, i, i]
         L.kb_attn_self.restype = i
         L.kb_attn_self.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
         L.kb_attn_cross.restype = i
@@ -78,8 +78,12 @@ def _check(code, what):
         raise KilnError(code, what)
 
 
-def workspace_bytes(rows_q, rows_k, H, norm_q, norm_k):
-    return lib().kb_attn_workspace_bytes(rows_q, rows_k, H, int(bool(norm_q)), int(bool(norm_k)))
+def workspace_bytes(rows_q, rows_k, H, dtype, norm_q=False, norm_k=False, n_ctx=1):
+    """Scratch bytes for one attention call; dtype is a KB_* code or a torch dtype."""
+    if not isinstance(dtype, int):
+        import torch
+        dtype = {torch.float16: KB_F16, torch.bfloat16: KB_BF16, torch.float32: KB_F32}[dtype]
+    return lib().kb_attn_workspace_bytes(rows_q, rows_k, n_ctx, H, dtype, int(bool(norm_q)), int(bool(norm_k)))
 
 
 def _ws(workspace):
