@@ -1,0 +1,327 @@
+#!/usr/bin/env python
+"""Benchmark of the DiT attention path: one "step" = the attention calls of one DiT forward of one image.
+
+Workload (fixed): 1024x1024 image -> 4096 tokens, 16 heads x 128, 28 blocks; per block
+  * self-attention with per-head Q/K RMSNorm and 3D RoPE          (kb_attn_self,  137.44 GFLOP)
+  * NAG cross-attention to a positive and a negative 512-token context with Q RMSNorm
+    (kb_attn_nag: both cross-attentions and the combine in one kernel, 34.36 GFLOP)
+bf16 activations in HBM, fp16 tensor-core operands, fp32 accumulation; seeded synthetic N(0,1) inputs.
+FLOPs are algorithmic: 4*Tq*Tk*128*H per attention, the count the reference's own harness uses.
+Every block has its own buffers (28 x 109 MB), so consecutive launches never find their inputs in L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 (under torchrun): one image per GPU, no communication on the data path ("weak" scaling).
+--impl reference: the reference has no CPU implementation of this path, so the arm times the CPU
+restatement of its arithmetic (oracle/, OpenMP over all host cores) on a bounded sample of the
+same workload. One JSON line goes to stdout.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+T, H, L, BLOCKS, D = 4096, 16, 512, 28, 2048
+FLOP_SELF = 4.0 * T * T * 128 * H
+FLOP_CROSS = 4.0 * T * L * 128 * H
+FLOP_STEP = BLOCKS * (FLOP_SELF + 2 * FLOP_CROSS)
+WORKLOAD = "anima-dit attention step: 1024x1024 -> 4096 tokens, 16x128 heads, 28 blocks x (self-attn + Q/K RMSNorm + 3D RoPE, NAG cross-attn to 2x512-token contexts), bf16"
+METRIC = "attention TFLOP/s per DiT step (4096 tokens)"
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops_sustained"), d.get("bf16_tflops"), d.get("hbm_gbs"), "measured"
+    return 1400.0, 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples while the timed region runs (read-only queries)."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = self.proc.communicate()[0]
+        rows, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                rows.append((float(f[0]), float(f[2])))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load = those drawing at least 60 % of the highest power seen
+        pmax = max((p for _, p in rows), default=0.0)
+        load = [c for c, p in rows if p >= 0.6 * pmax]
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(rows), "samples_under_load": len(load), "power_w_max": pmax}
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def cpu_sample(seconds_target=12.0):
+    """Times the CPU restatement of the reference arithmetic on a slice of the workload: self-attention of the
+    first `rows` query tokens of one block against all 4096 keys, all 16 heads. Returns (TFLOP/s, cores, rows, secs)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import oracle
+    k = oracle.round16(oracle.randn(2, T * D), 1).reshape(T, D)
+    v = oracle.round16(oracle.randn(3, T * D), 1).reshape(T, D)
+    q = oracle.round16(oracle.randn(1, T * D), 1).reshape(T, D)
+    rows = 64
+    t0 = time.perf_counter()
+    oracle.attention(q[:rows], k, v, H, acc64=False)
+    dt = time.perf_counter() - t0
+    rows = int(min(T, max(64, rows * seconds_target / max(dt, 1e-3))))
+    t0 = time.perf_counter()
+    oracle.attention(q[:rows], k, v, H, acc64=False)
+    dt = time.perf_counter() - t0
+    return 4.0 * rows * T * 128 * H / dt / 1e12, oracle.max_threads(), rows, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    k = oracle.round16(oracle.randn(2, T * D), 1).reshape(T, D)
+    v = oracle.round16(oracle.randn(3, T * D), 1).reshape(T, D)
+    q = oracle.round16(oracle.randn(1, T * D), 1).reshape(T, D)
+    # size one step's sample for ~2 s so that K + W steps end within a few minutes
+    t0 = time.perf_counter()
+    oracle.attention(q[:32], k, v, H, acc64=False)
+    rows = int(min(T, max(32, 32 * 2.0 / max(time.perf_counter() - t0, 1e-3))))
+    for _ in range(args.warmup):
+        oracle.attention(q[:rows], k, v, H, acc64=False)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.attention(q[:rows], k, v, H, acc64=False)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 4.0 * rows * T * 128 * H / dt / 1e12
+    sample = f"per step: self-attention of {rows} of 4096 query tokens x 4096 keys x 16 heads of one block (fp32, two-pass, OpenMP); ms_per_step extrapolates to the full 4.81 TFLOP step"
+    line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": FLOP_STEP / (tflops * 1e12) * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": oracle.max_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import kiln_b200 as kb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rc = kb.lib().kb_init()
+    if rc != 0:
+        raise kb.KilnError(rc, "kb_init")
+    dev = torch.device("cuda", local)
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+
+    def randn(*shape):
+        return torch.randn(*shape, device=dev, generator=g, dtype=torch.float32).to(bf)
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    cos, sin = (torch.from_numpy(a).to(dev) for a in oracle.cosmos_rope(64, 64))
+    blocks = []
+    for _ in range(BLOCKS):
+        qkv = randn(T, 3 * D)                       # Q, K, V as thirds of one buffer, like the engine's [R, 4D] scratch
+        blk = {"q": qkv[:, :D], "k": qkv[:, D:2 * D], "v": qkv[:, 2 * D:], "a": torch.empty(T, D, device=dev, dtype=bf),
+               "q2": randn(T, D), "a2": torch.empty(T, D, device=dev, dtype=bf),
+               "kp": randn(L, D), "vp": randn(L, D), "kn": randn(L, D), "vn": randn(L, D),
+               "wq": (1 + 0.02 * torch.randn(128, device=dev, generator=g)).to(bf), "wk": (1 + 0.02 * torch.randn(128, device=dev, generator=g)).to(bf),
+               "wq2": (1 + 0.02 * torch.randn(128, device=dev, generator=g)).to(bf)}
+        blocks.append(blk)
+    ws_bytes = max(kb.workspace_bytes(T, T, H, bf, True, True), kb.workspace_bytes(T, L, H, bf, True, False, n_ctx=2))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+
+    def block_calls(b):
+        kb.attn_self(b["a"], b["q"], b["k"], b["v"], 1, T, H, qn_w=b["wq"], kn_w=b["wk"], rope_cos=cos, rope_sin=sin, workspace=ws)
+        kb.attn_nag(b["a2"], b["q2"], b["kp"], b["vp"], L, 0, b["kn"], b["vn"], L, 0, 5.0, 2.5, 0.25, T, H, qn_w=b["wq2"], workspace=ws)
+
+    def step():
+        for b in blocks:
+            block_calls(b)
+    LAUNCHES_PER_STEP = BLOCKS * 4                  # (staging pre-pass + attention kernel) x (self, NAG)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None   # samples from warm-up to the end of the per-kernel pass
+    for _ in range(max(args.warmup, 3)):
+        step()
+    assert kb.check_status() == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    assert kb.check_status() == 0
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * FLOP_STEP / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel: per-launch CUDA events on the launch stream (library's ProfScope hooks),
+    # taken over a second pass of the same K steps so the event records do not perturb `value`
+    kb.prof_enable(True)
+    for _ in range(min(args.steps, 8192 // LAUNCHES_PER_STEP)):
+        step()
+    attn_ms, attn_n = kb.prof_read(kb.PROF_ATTENTION)
+    nag_ms, nag_n = kb.prof_read(kb.PROF_NAG)
+    prep_ms, prep_n = kb.prof_read(kb.PROF_NORM_ROPE)
+    kb.prof_enable(False)
+    clocks = sampler.stop() if sampler else None
+    sustained, burst, hbm, src = read_peaks()
+    achieved = FLOP_SELF / (attn_ms / attn_n * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "attn_fwd_kernel<MODE_PAIR> (self-attention, 4096x4096x16 heads)", "achieved": achieved,
+                "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained, "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside a long step)",
+                "traffic": None, "avg_launch_us": attn_ms / attn_n * 1e3,
+                "other_kernels": {"nag_attn_us": nag_ms / nag_n * 1e3, "nag_tflops": 2 * FLOP_CROSS / (nag_ms / nag_n * 1e-3) / 1e12,
+                                  "staging_prepass_us": prep_ms / prep_n * 1e3}}
+    traffic_file = os.path.join(ROOT, "profiles", "attn_pair_traffic.json")
+    if os.path.exists(traffic_file):
+        roofline["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch_T4096")
+
+    # ---- end to end through the C ABI with HOST buffers: every block's inputs come from pinned host memory and
+    # both attention outputs go back to the host, inside the timed region; copies overlap compute on side streams
+    NSLOT = 2
+    pin_in = [{k2: torch.empty_like(blocks[i][k2], device="cpu").pin_memory() for k2 in ("q2", "kp", "vp", "kn", "vn")} for i in range(NSLOT)]
+    pin_qkv = [torch.empty(T, 3 * D, dtype=bf).pin_memory() for _ in range(NSLOT)]
+    pin_out = [(torch.empty(T, D, dtype=bf).pin_memory(), torch.empty(T, D, dtype=bf).pin_memory()) for _ in range(NSLOT)]
+    for i in range(NSLOT):
+        pin_qkv[i].copy_(torch.cat([blocks[i]["q"], blocks[i]["k"], blocks[i]["v"]], 1))
+        for k2 in pin_in[i]:
+            pin_in[i][k2].copy_(blocks[i][k2])
+    slots = []
+    for i in range(NSLOT):
+        qkv = torch.empty(T, 3 * D, device=dev, dtype=bf)
+        s = dict(blocks[i])
+        s.update({"qkv": qkv, "q": qkv[:, :D], "k": qkv[:, D:2 * D], "v": qkv[:, 2 * D:], "a": torch.empty(T, D, device=dev, dtype=bf),
+                  "a2": torch.empty(T, D, device=dev, dtype=bf)})
+        for k2 in ("q2", "kp", "vp", "kn", "vn"):
+            s[k2] = torch.empty_like(blocks[i][k2])
+        slots.append(s)
+    h2d_bytes = BLOCKS * (pin_qkv[0].numel() + sum(t_.numel() for t_ in pin_in[0].values())) * 2
+    d2h_bytes = BLOCKS * 2 * T * D * 2
+    s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
+    ev_done = [torch.cuda.Event() for _ in range(NSLOT)]
+    ev_out = [torch.cuda.Event() for _ in range(NSLOT)]
+
+    def e2e_step():
+        for i in range(BLOCKS):
+            sl = i % NSLOT
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_done[sl])                      # the slot's previous compute has read its inputs
+                slots[sl]["qkv"].copy_(pin_qkv[sl], non_blocking=True)
+                for k2 in pin_in[sl]:
+                    slots[sl][k2].copy_(pin_in[sl][k2], non_blocking=True)
+                ev_in[sl].record(s_in)
+            s_main.wait_event(ev_in[sl])
+            s_main.wait_event(ev_out[sl])                         # the slot's previous outputs have left
+            block_calls(slots[sl])
+            ev_done[sl].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[sl])
+                pin_out[sl][0].copy_(slots[sl]["a"], non_blocking=True)
+                pin_out[sl][1].copy_(slots[sl]["a2"], non_blocking=True)
+                ev_out[sl].record(s_out)
+        s_main.wait_stream(s_out)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    assert kb.check_status() == 0
+    e2e = {"value": world * FLOP_STEP / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
+           "note": "all 28 blocks' Q/K/V, cross Q and contexts copied from pinned host memory and both outputs copied back every step; PCIe-bound"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f16 tensor-core operands, f32 accumulate (bf16 in HBM)", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "images_per_gpu": 1, "flop_per_step_per_gpu": FLOP_STEP,
+                           "l2": "28 distinct per-block buffer sets (3 GB) cycle through: inputs larger than L2"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * LAUNCHES_PER_STEP, "roofline": roofline}
+        if world == 1:
+            tf, cores, rows, secs = cpu_sample()
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"self-attention of {rows} of 4096 query tokens x 4096 keys x 16 heads (fp32 two-pass CPU restatement, OpenMP), {secs:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -106,6 +106,15 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
  * when a kernel gave up on a bounded wait. */
 int kb_status(unsigned* status_bits);
 
+/* Per-category kernel timing, the counterpart of the engine's ProfScope / prof_report
+ * (engine/src/kernels.cu:18-58; categories "norm"+"rope" and "attention" there). kb_prof_enable(1)
+ * (re)starts recording one CUDA event pair per kernel launch on the launch's stream, up to 8192 launches;
+ * the event pool is created on the first enable, never per call. kb_prof_read synchronises the device
+ * and returns the summed kernel time and launch count of one category since the last enable. */
+enum { KB_PROF_NORM_ROPE = 0, KB_PROF_ATTENTION = 1, KB_PROF_NAG = 2, KB_PROF_CATEGORIES = 3 };
+int kb_prof_enable(int on);
+int kb_prof_read(int category, double* total_ms, int* launches);
+
 /* Start-up known-answer test on the current device, in the spirit of the reference's start-up GEMM
  * cross-check (engine/src/kernels.cu:106-151): runs each kernel family on a small seeded problem and
  * compares with a one-thread-per-row fp32 kernel. workspace >= kb_selfcheck_workspace_bytes(). */

@@ -5,5 +5,5 @@ sources (csrc/), the C++ op-set shim the engine links (host/), and a ctypes bind
 tests and the benchmark. There is no CPU fallback: every launch entry point fails when the library
 or an sm_100 device is missing.
 """
-from .ops import (KB_BF16, KB_F16, KB_F32, KilnError, attn_cross, attn_nag, attn_self, check_status, lib, qk_prep,  # noqa: F401
-                  workspace_bytes)
+from .ops import (KB_BF16, KB_F16, KB_F32, PROF_ATTENTION, PROF_NAG, PROF_NORM_ROPE, KilnError, attn_cross, attn_nag,  # noqa: F401
+                  attn_self, check_status, lib, prof_enable, prof_read, qk_prep, workspace_bytes)

@@ -24,10 +24,36 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Optional per-category kernel timing, the counterpart of the reference's ProfScope / prof_report
+// (engine/src/kernels.cu:18-58): an event pair around every launch while enabled, summed on read.
+constexpr int PROF_POOL = 8192;
+struct Prof {
+    bool on = false;
+    int used = 0;
+    cudaEvent_t* ev = nullptr;      // 2 * PROF_POOL events, created when profiling is first enabled
+    unsigned char* cat = nullptr;   // category of each pair
+};
+
 struct DeviceState {
     bool ready = false;
     int err = KB_OK;
     unsigned int* status = nullptr;
+    Prof prof;
+};
+
+struct ProfScope {
+    Prof* p = nullptr;
+    int slot = -1;
+    cudaStream_t stream;
+    ProfScope(DeviceState* st, int category, cudaStream_t s) : stream(s) {
+        if (st && st->prof.on && st->prof.used < PROF_POOL) {
+            p = &st->prof;
+            slot = p->used++;
+            p->cat[slot] = (unsigned char)category;
+            cudaEventRecord(p->ev[2 * slot], stream);
+        }
+    }
+    ~ProfScope() { if (p) cudaEventRecord(p->ev[2 * slot + 1], stream); }
 };
 
 constexpr int MAX_DEVICES = 64;
@@ -125,8 +151,9 @@ struct PrepBatch {
     }
 };
 
-int launch_prep(const PrepBatch& pb, int in_dtype, int out_dtype, cudaStream_t stream) {
+int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtype, cudaStream_t stream) {
     if (pb.pp.items <= 0) return KB_OK;
+    ProfScope ps(st, KB_PROF_NORM_ROPE, stream);
     const unsigned grid = (unsigned)((pb.pp.items + 7) / 8);
 #define KB_PREP(IN, OUT) qk_prep_kernel<IN, OUT><<<grid, 256, 0, stream>>>(pb.pp)
     if (out_dtype == KB_F16) {
@@ -226,7 +253,7 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     if (stage_k) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, k, ld_k, B * Tk, Tk, kn_w, rope_cos, rope_sin); kk = d; ldk = H * 128; }
     if (stage_v) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, v, ld_v, B * Tk, Tk, nullptr, nullptr, nullptr); vv = d; ldv = H * 128; }
     if (sg.overflow) return KB_ERR_WORKSPACE;
-    if ((rc = launch_prep(pb, dtype, KB_F16, stream))) return rc;
+    if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
     CUtensorMap tq, tk, tv;
     if ((rc = make_tmap(&tq, qq, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, Tk, H, B, ldk)) || (rc = make_tmap(&tv, vv, Tk, H, B, ldv)))
         return rc;
@@ -236,6 +263,7 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
     KB_SET_DBG(p);
+    ProfScope ps(st, KB_PROF_ATTENTION, stream);
     return launch_attn<MODE_PAIR>(out_dtype, tq, tk, tv, tk, tv, p, stream);
 }
 
@@ -326,7 +354,7 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
         ldkv = H * 128;
     }
     if (sg.overflow) return KB_ERR_WORKSPACE;
-    if ((rc = launch_prep(pb, dtype, KB_F16, stream))) return rc;
+    if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
     CUtensorMap tq, tk0, tv0, tk1, tv1;
     if ((rc = make_tmap(&tq, qq, Tq, H, 1, ldq)) || (rc = make_tmap(&tk0, kv[0], Tk_pos, H, 1, ldkv)) ||
         (rc = make_tmap(&tv0, kv[1], Tk_pos, H, 1, ldkv)) || (rc = make_tmap(&tk1, kv[2], Tk_neg, H, 1, ldkv)) ||
@@ -339,6 +367,7 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     p.nag_s = scale; p.nag_tau = tau; p.nag_alpha = alpha;
     p.status = st->status;
     KB_SET_DBG(p);
+    ProfScope ps(st, KB_PROF_NAG, stream);
     return launch_attn<MODE_NAG>(out_dtype, tq, tk0, tv0, tk1, tv1, p, stream);
 }
 
@@ -356,7 +385,7 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
     PrepBatch pb;
     pb.pp.H = H; pb.pp.eps = eps;
     pb.add(out, ld_out, in, ld_in, rows, T, w_bf16, rope_cos, rope_sin);
-    return launch_prep(pb, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+    return launch_prep(st, pb, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int kb_status(unsigned* status_bits) {
@@ -370,6 +399,43 @@ int kb_status(unsigned* status_bits) {
     if (v && cudaMemset(st->status, 0, sizeof(v)) != cudaSuccess) return KB_ERR_CUDA;
     *status_bits = v;
     return (v & ST_TIMEOUT) ? KB_ERR_TIMEOUT : KB_OK;
+}
+
+int kb_prof_enable(int on) {
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    Prof& pf = st->prof;
+    if (on && !pf.ev) {
+        pf.ev = new cudaEvent_t[2 * PROF_POOL];
+        pf.cat = new unsigned char[PROF_POOL];
+        for (int i = 0; i < 2 * PROF_POOL; i++)
+            if (cudaEventCreate(&pf.ev[i]) != cudaSuccess) return KB_ERR_CUDA;
+    }
+    pf.on = on != 0;
+    pf.used = 0;
+    return KB_OK;
+}
+
+int kb_prof_read(int category, double* total_ms, int* launches) {
+    if (!total_ms || !launches || category < 0 || category >= KB_PROF_CATEGORIES) return KB_ERR_ARG;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    Prof& pf = st->prof;
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_CUDA;
+    double sum = 0;
+    int n = 0;
+    for (int i = 0; i < pf.used; i++) {
+        if (pf.cat[i] != category) continue;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, pf.ev[2 * i], pf.ev[2 * i + 1]) != cudaSuccess) return KB_ERR_CUDA;
+        sum += ms;
+        n++;
+    }
+    *total_ms = sum;
+    *launches = n;
+    return KB_OK;
 }
 
 size_t kb_selfcheck_workspace_bytes(void) { return (size_t)4 << 20; }

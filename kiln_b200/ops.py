@@ -47,6 +47,10 @@ def lib():
         L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
         L.kb_status.restype = i
         L.kb_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        L.kb_prof_enable.restype = i
+        L.kb_prof_enable.argtypes = [i]
+        L.kb_prof_read.restype = i
+        L.kb_prof_read.argtypes = [i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(i)]
         L.kb_selfcheck_workspace_bytes.restype = sz
         L.kb_attn_selfcheck.restype = i
         L.kb_attn_selfcheck.argtypes = [vp, sz, ctypes.POINTER(ctypes.c_float), vp]
@@ -131,3 +135,18 @@ def check_status():
     bits = ctypes.c_uint(0)
     _check(lib().kb_status(ctypes.byref(bits)), "kb_status")
     return bits.value
+
+
+PROF_NORM_ROPE, PROF_ATTENTION, PROF_NAG = 0, 1, 2
+
+
+def prof_enable(on=True):
+    """Start (or stop) recording one event pair per kernel launch (engine counterpart: ProfScope)."""
+    _check(lib().kb_prof_enable(int(on)), "kb_prof_enable")
+
+
+def prof_read(category):
+    """(total kernel milliseconds, launches) of one category since prof_enable; synchronises the device."""
+    ms, n = ctypes.c_double(0), ctypes.c_int(0)
+    _check(lib().kb_prof_read(category, ctypes.byref(ms), ctypes.byref(n)), "kb_prof_read")
+    return ms.value, n.value
