@@ -95,7 +95,8 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w,
 
 /* Row pre-pass on its own: out[r, h*128..] = rope(rmsnorm(in[r, h*128..])) as 16-bit, or a plain
  * conversion when w, cos and sin are NULL. in_dtype may be KB_F32 (the engine keeps Q/K/V in fp32:
- * engine/src/dit.cu:429-430). Replaces rmsnorm + rope_half (engine/src/kernels.cu:668-673, 773-777)
+ * engine/src/dit.cu:429-430); with in_dtype = out_dtype = KB_F32 it is the engine's in-place fp32
+ * rmsnorm / rope_half (out may equal in: every element is read before it is written by the same lane). Replaces rmsnorm + rope_half (engine/src/kernels.cu:668-673, 773-777)
  * and the fp32 -> fp16 staging inside the reference kernel (engine/src/tcflash.cuh:56-64). */
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype,
                int rows, int H, int T, const void* w_bf16, float eps,

@@ -156,7 +156,9 @@ int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtyp
     ProfScope ps(st, KB_PROF_NORM_ROPE, stream);
     const unsigned grid = (unsigned)((pb.pp.items + 7) / 8);
 #define KB_PREP(IN, OUT) qk_prep_kernel<IN, OUT><<<grid, 256, 0, stream>>>(pb.pp)
-    if (out_dtype == KB_F16) {
+    if (out_dtype == KB_F32) {
+        KB_PREP(float, float);        // in-place fp32 norm / RoPE as the engine's own ops do (validated by the caller)
+    } else if (out_dtype == KB_F16) {
         if (in_dtype == KB_F16) KB_PREP(__half, __half);
         else if (in_dtype == KB_BF16) KB_PREP(__nv_bfloat16, __half);
         else KB_PREP(float, __half);
@@ -374,10 +376,11 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
                const void* w_bf16, float eps, const float* rope_cos, const float* rope_sin, void* stream) {
     if (!out || !in || rows < 0 || H <= 0 || T <= 0) return KB_ERR_ARG;
-    if (out_dtype != KB_F16 && out_dtype != KB_BF16) return KB_ERR_ARG;
+    if (out_dtype != KB_F16 && out_dtype != KB_BF16 && out_dtype != KB_F32) return KB_ERR_ARG;
     if (in_dtype != KB_F16 && in_dtype != KB_BF16 && in_dtype != KB_F32) return KB_ERR_ARG;
+    if (out_dtype == KB_F32 && in_dtype != KB_F32) return KB_ERR_ARG;
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
-    if (!aligned16(out) || !aligned16(in) || (ld_out & 7) || (ld_in & (in_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (!aligned16(out) || !aligned16(in) || (ld_out & (out_dtype == KB_F32 ? 3 : 7)) || (ld_in & (in_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
     if (ld_out < H * 128 || ld_in < H * 128) return KB_ERR_SHAPE;
     DeviceState* st;
     int rc;

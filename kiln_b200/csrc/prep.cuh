@@ -19,6 +19,7 @@ namespace kb {
 template <typename T> struct Io;
 template <> struct Io<float> {
     static __device__ __forceinline__ float2 ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void st2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 };
 template <> struct Io<__half> {
     static __device__ __forceinline__ float2 ld2(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }

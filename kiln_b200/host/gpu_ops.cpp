@@ -1,0 +1,101 @@
+// Implementation of the engine-facing op set over the C ABI (see gpu_ops.h for the reference citations).
+#include "gpu_ops.h"
+
+#include <stdexcept>
+#include <string>
+
+#include "kiln_b200.h"
+
+namespace kiln_b200 {
+
+namespace {
+OpContext g_ctx;
+
+void check(int rc, const char* what) {
+    if (rc != KB_OK) throw std::runtime_error(std::string(what) + ": " + kb_error_string(rc));
+}
+void need_d128(int Dh, const char* what) {
+    // same wording as the reference's attention16 (engine/src/kernels.cu:870)
+    if (Dh != 128) throw std::runtime_error(std::string(what) + ": unsupported head size or row stride");
+}
+}  // namespace
+
+void set_context(const OpContext& ctx) { g_ctx = ctx; }
+const OpContext& context() { return g_ctx; }
+
+void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, int Tq, int Tk,
+               int H, int Dh, bool causal, int npad) {
+    need_d128(Dh, "attention");
+    if (causal) throw std::runtime_error("attention: causal attention is not on the fused path");
+    check(kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, npad, H, ldq, ldk, ldv, ldo, KB_F32, KB_F32, 1e-6f, g_ctx.workspace,
+                        g_ctx.workspace_bytes, g_ctx.stream),
+          "attention");
+}
+
+void attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, int Tq, int Tk,
+                 int H, int Dh, int npad) {
+    need_d128(Dh, "attention16");
+    check(kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, npad, H, ldq, ldk, ldv, ldo, KB_F32, KB_F16, 1e-6f, g_ctx.workspace,
+                        g_ctx.workspace_bytes, g_ctx.stream),
+          "attention16");
+}
+
+void rmsnorm(float* y, const float* x, const uint16_t* w_bf16, int rows, int dim, float eps) {
+    if (dim != 128) throw std::runtime_error("rmsnorm: only the per-head rows of 128 are on this path");
+    // rows of 128 are (token, head) pairs: one "head" per row
+    check(kb_qk_prep(y, 128, KB_F32, x, 128, KB_F32, rows, 1, 1, w_bf16, eps, nullptr, nullptr, g_ctx.stream), "rmsnorm");
+}
+
+void rope_half(float* x, int T, int H, int Dh, const float* cos_t, const float* sin_t) {
+    need_d128(Dh, "rope_half");
+    check(kb_qk_prep(x, H * 128, KB_F32, x, H * 128, KB_F32, T, H, T, nullptr, 0.f, cos_t, sin_t, g_ctx.stream), "rope_half");
+}
+
+void self_attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, int B, int T,
+                      int H, const uint16_t* qn_w, const uint16_t* kn_w, const float* rope_cos, const float* rope_sin, float eps) {
+    check(kb_attn_self(out, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, T, H, ldq, ldk, ldv, ldo, KB_F32, KB_F16, eps,
+                       g_ctx.workspace, g_ctx.workspace_bytes, g_ctx.stream),
+          "self_attention16");
+}
+
+void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16_t* qn_w, const float* k_pos, const float* v_pos,
+                     int Tk_pos, int npad_pos, const float* k_neg, const float* v_neg, int Tk_neg, int npad_neg, int ld_kv,
+                     float scale, float tau, float alpha, int Tq, int H, float eps) {
+    check(kb_attn_nag(out, q, qn_w, k_pos, v_pos, Tk_pos, npad_pos, k_neg, v_neg, Tk_neg, npad_neg, scale, tau, alpha, Tq, H, ldq,
+                      ld_kv, ldo, KB_F32, KB_F16, eps, g_ctx.workspace, g_ctx.workspace_bytes, g_ctx.stream),
+          "nag_attention16");
+}
+
+}  // namespace kiln_b200
+
+// C trampolines so the shim can be exercised from the test-suite without a C++ test runner:
+// each returns 0, or -1 after copying the exception text into `err`.
+extern "C" {
+static int guard(char* err, int n, void (*fn)(void*), void* arg) {
+    try { fn(arg); return 0; }
+    catch (const std::exception& e) { if (err && n > 0) { snprintf(err, n, "%s", e.what()); } return -1; }
+}
+void kbh_set_context(void* stream, void* workspace, size_t bytes) {
+    kiln_b200::OpContext c; c.stream = (cudaStream_t)stream; c.workspace = workspace; c.workspace_bytes = bytes;
+    kiln_b200::set_context(c);
+}
+struct A16 { void* out; int ldo; const float *q; int ldq; const float* k; int ldk; const float* v; int ldv; int Tq, Tk, H, Dh, npad; int causal; int f32out; };
+int kbh_attention(void* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, int Tq, int Tk, int H,
+                  int Dh, int causal, int npad, int f32out, char* err, int n) {
+    A16 a{out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, npad, causal, f32out};
+    return guard(err, n, [](void* p) {
+        A16& a = *(A16*)p;
+        if (a.f32out) kiln_b200::attention((float*)a.out, a.ldo, a.q, a.ldq, a.k, a.ldk, a.v, a.ldv, a.Tq, a.Tk, a.H, a.Dh, a.causal != 0, a.npad);
+        else kiln_b200::attention16((__half*)a.out, a.ldo, a.q, a.ldq, a.k, a.ldk, a.v, a.ldv, a.Tq, a.Tk, a.H, a.Dh, a.npad);
+    }, &a);
+}
+struct NR { float* x; const uint16_t* w; int rows, T, H; float eps; const float *c, *s; };
+int kbh_rmsnorm_rope(float* x, const uint16_t* w, int T, int H, float eps, const float* c, const float* s, char* err, int n) {
+    NR a{x, w, T * H, T, H, eps, c, s};
+    return guard(err, n, [](void* p) {
+        NR& a = *(NR*)p;
+        kiln_b200::rmsnorm(a.x, a.x, a.w, a.rows, 128, a.eps);
+        kiln_b200::rope_half(a.x, a.T, a.H, 128, a.c, a.s);
+    }, &a);
+}
+}

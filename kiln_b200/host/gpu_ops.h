@@ -1,0 +1,53 @@
+// Engine-facing op set: the attention entry points of the reference's gpu.h with the same names,
+// argument order and meaning, implemented over the C ABI of include/kiln_b200.h.
+//
+//   attention()    engine/src/gpu.h:152-153, engine/src/kernels.cu:828-866
+//   attention16()  engine/src/gpu.h:155-156, engine/src/kernels.cu:868-873
+//   rmsnorm()      engine/src/gpu.h:133,     engine/src/kernels.cu:668-673   (rows of 128: the per-head Q/K norm)
+//   rope_half()    engine/src/gpu.h:145,     engine/src/kernels.cu:773-777
+//   nag_combine is the k_nag launch of engine/src/dit.cu:486 (fp16 rows) / :524 (fp32 rows)
+//
+// Like the reference ops they run on one stream, take device pointers the caller owns, and throw
+// std::runtime_error on failure (the reference's CK/CB macros, engine/src/gpu.h:15-16); the engine's job
+// wrapper turns that into an {"ev":"error"} event (engine/src/engine.h:785-791).
+// The reference keeps stream and scratch arena in a global `Gpu G` (engine/src/gpu.h:63-90); the
+// equivalent here is OpContext, set once by the engine with G.stream and a slice of G.arena.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace kiln_b200 {
+
+struct OpContext {
+    cudaStream_t stream = nullptr;
+    void* workspace = nullptr;       // fp16 staging of Q/K/V: kb_attn_workspace_bytes(...) for the largest call
+    size_t workspace_bytes = 0;
+};
+void set_context(const OpContext& ctx);
+const OpContext& context();
+
+// q [Tq, ldq], k/v [Tk, ld*], out [Tq, ldo] fp32; head h at column h*Dh; npad zero keys join the softmax.
+// Dh must be 128 and causal false: the reference sends everything else to its cuBLAS path, which is not part of this library.
+void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+               int Tq, int Tk, int H, int Dh, bool causal, int npad = 0);
+void attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                 int Tq, int Tk, int H, int Dh, int npad = 0);
+
+// In-place fp32 RMSNorm over rows of 128 with a bf16 weight (the reference passes a Weight*; its ->p is this pointer).
+void rmsnorm(float* y, const float* x, const uint16_t* w_bf16, int rows, int dim, float eps);
+void rope_half(float* x, int T, int H, int Dh, const float* cos_t, const float* sin_t);
+
+// Fused forms the DiT block driver can call instead of the unfused sequences:
+// rmsnorm(Q) + rmsnorm(K) + rope_half(Q) + rope_half(K) + attention16 per batch element -> one call for the whole batch
+void self_attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                      int B, int T, int H, const uint16_t* qn_w, const uint16_t* kn_w, const float* rope_cos,
+                      const float* rope_sin, float eps);
+// rmsnorm(Q) + attention16(pos) + attention16(neg) + k_nag -> one call
+void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16_t* qn_w, const float* k_pos, const float* v_pos,
+                     int Tk_pos, int npad_pos, const float* k_neg, const float* v_neg, int Tk_neg, int npad_neg, int ld_kv,
+                     float scale, float tau, float alpha, int Tq, int H, float eps);
+
+}  // namespace kiln_b200
