@@ -44,7 +44,8 @@ enum {
     KB_ERR_CUDA = -5,       /* a CUDA runtime/driver call failed; cudaGetLastError has the detail */
     KB_ERR_DEVICE = -6,     /* not an sm_100 device, or no device */
     KB_ERR_TIMEOUT = -7,    /* a kernel gave up on a bounded wait (reported by kb_status) */
-    KB_ERR_SELFCHECK = -8   /* kb_attn_selfcheck: error above tolerance */
+    KB_ERR_SELFCHECK = -8,  /* kb_attn_selfcheck: error above tolerance */
+    KB_ERR_STATIC_SCRATCH = -9  /* kb_attn_self_static: the problem does not fit the built-in scratch */
 };
 
 const char* kb_error_string(int code);
@@ -71,6 +72,32 @@ int kb_attn_self(void* out, const void* q, const void* k, const void* v,
                  int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
                  int dtype, int out_dtype, float eps,
                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* kb_attn_self for callers that can neither pass a workspace nor allocate one. (No counterpart in the
+ * reference: its ops bump-allocate scratch from the engine's arena.)
+ *
+ * Who needs it: code that runs with the GPU memory already carved up and no allocator to ask — an engine
+ * whose arena was sized to the user's VRAM budget at start-up and is full, a plugin or callback that is
+ * only given input and output buffers, a latency-sensitive loop where cudaMalloc (which synchronises the
+ * device and can fail once another application has taken the remaining memory) is not acceptable.
+ *
+ * Same arguments and results as kb_attn_self, minus the workspace: the fp16 staging copies of Q, K and V
+ * live in a fixed KB_STATIC_SCRATCH_BYTES array inside the library's device image. Consequences:
+ *   - every GPU on which the library is loaded holds those 32 MiB until the process exits;
+ *   - a problem whose staging (kb_attn_workspace_bytes(B*T, B*T, 1, H, dtype, norm_q, norm_k)) exceeds
+ *     KB_STATIC_SCRATCH_BYTES is refused with KB_ERR_STATIC_SCRATCH and nothing is launched
+ *     (e.g. bf16 or fp32 inputs: B*T*H <= 43690 rows-times-heads; 1536 tokens x 16 heads fit, 4096 x 16 do not);
+ *   - the array is shared by every call on that GPU and keeps the previous call's contents (nothing in it
+ *     needs clearing: each call overwrites what it later reads); two calls whose kernels overlap on the GPU
+ *     (different streams, or different host threads) race on it — keep such calls on one stream;
+ *   - the first call on each device looks up the array's device address (and, like every entry point,
+ *     prepares the device); make that first call before any stream capture begins.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define KB_STATIC_SCRATCH_BYTES (32u << 20)
+int kb_attn_self_static(void* out, const void* q, const void* k, const void* v,
+                        const void* qn_w, const void* kn_w, const float* rope_cos, const float* rope_sin,
+                        int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
+                        int dtype, int out_dtype, float eps, void* stream);
 
 /* Cross-attention of Tq latent tokens to one text context of Tk real rows + npad zero rows.
  * Replaces rmsnorm(Q) + attention16(..., Tk = real, npad) (engine/src/dit.cu:476-481). K is taken as

@@ -284,6 +284,7 @@ const char* kb_error_string(int code) {
         case KB_ERR_DEVICE: return "no sm_100 device is current";
         case KB_ERR_TIMEOUT: return "a kernel gave up on a bounded wait";
         case KB_ERR_SELFCHECK: return "start-up self-check exceeded its tolerance";
+        case KB_ERR_STATIC_SCRATCH: return "problem needs more staging scratch than the library's built-in buffer (KB_STATIC_SCRATCH_BYTES); use kb_attn_self with a workspace";
         default: return "unknown error";
     }
 }
@@ -439,6 +440,53 @@ int kb_prof_read(int category, double* total_ms, int* launches) {
     *total_ms = sum;
     *launches = n;
     return KB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-attention for callers that cannot hand over scratch memory and must not allocate any.
+// The fp16 staging copies of Q, K and V go to a fixed array that is part of the library's device
+// image, so the call makes no cudaMalloc / cudaFree and needs no caller workspace. The price: every
+// GPU that loads the library carries the array until the process exits, problems whose staging
+// does not fit are refused, and the array is shared by all calls on that GPU.
+static __device__ __align__(256) unsigned char g_static_scratch[KB_STATIC_SCRATCH_BYTES];
+
+namespace {
+void* g_static_scratch_addr[MAX_DEVICES] = {};   // device address of the array, per device
+std::mutex g_static_mu;
+
+// The array's name is only a host-side handle here; kernels need its device address, looked up once
+// per device while that device is current.
+int static_scratch_addr(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return KB_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return KB_ERR_CUDA;
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return KB_OK;
+}
+}  // namespace
+
+int kb_attn_self_static(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
+                        const float* rope_cos, const float* rope_sin, int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
+                        int dtype, int out_dtype, float eps, void* stream) {
+    if (!valid_in_dtype(dtype) || B <= 0 || T <= 0 || H <= 0) return KB_ERR_ARG;
+    if ((long long)B * T > (long long)KB_STATIC_SCRATCH_BYTES) return KB_ERR_STATIC_SCRATCH;   // keeps the size arithmetic in range
+    const size_t need = kb_attn_workspace_bytes(B * T, B * T, 1, H, dtype, qn_w || rope_cos, kn_w || rope_cos);
+    if (need > (size_t)KB_STATIC_SCRATCH_BYTES) return KB_ERR_STATIC_SCRATCH;
+    void* scratch = nullptr;
+    int rc;
+    if ((rc = static_scratch_addr(&scratch))) return rc;
+    // Nothing in the array has to start at zero: the pre-pass overwrites every staged row before the
+    // attention kernel's TMA loads read it, and rows past the end are never read (the tensor maps bound them).
+    return attn_pair(out, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, T, T, 0, H, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype, eps, scratch,
+                     (size_t)KB_STATIC_SCRATCH_BYTES, static_cast<cudaStream_t>(stream));
 }
 
 size_t kb_selfcheck_workspace_bytes(void) { return (size_t)4 << 20; }

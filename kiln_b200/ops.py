@@ -39,6 +39,8 @@ def lib():
         L.kb_attn_workspace_bytes.argtypes = [i, i, i, i, i, i, i]
         L.kb_attn_self.restype = i
         L.kb_attn_self.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_attn_self_static.restype = i
+        L.kb_attn_self_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, f, vp]
         L.kb_attn_cross.restype = i
         L.kb_attn_cross.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
         L.kb_attn_nag.restype = i
