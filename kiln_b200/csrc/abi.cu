@@ -38,6 +38,7 @@ struct DeviceState {
     bool ready = false;
     int err = KB_OK;
     unsigned int* status = nullptr;
+    int sm_count = 148;
     Prof prof;
 };
 
@@ -72,6 +73,7 @@ int init_device(DeviceState& st, int dev) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return KB_ERR_DEVICE;
     if (prop.major != 10) return KB_ERR_DEVICE;  // tcgen05 / TMEM exist on sm_100 only
+    st.sm_count = prop.multiProcessorCount;
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -146,15 +148,15 @@ struct PrepBatch {
         PrepSeg& sg = pp.seg[pp.nseg++];
         sg.in = in; sg.out = out; sg.w = static_cast<const __nv_bfloat16*>(w); sg.cos_t = c; sg.sin_t = s;
         sg.rows = rows; sg.ld_in = ld_in; sg.ld_out = ld_out; sg.T = T > 0 ? T : 1;
-        sg.item0 = pp.items;
-        pp.items += (long long)rows * pp.H;
+        sg.block0 = pp.blocks;
+        pp.blocks += (unsigned)(((long long)rows * pp.H + PREP_ITEMS_PER_BLOCK - 1) / PREP_ITEMS_PER_BLOCK);
     }
 };
 
 int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtype, cudaStream_t stream) {
-    if (pb.pp.items <= 0) return KB_OK;
+    if (pb.pp.blocks == 0) return KB_OK;
     ProfScope ps(st, KB_PROF_NORM_ROPE, stream);
-    const unsigned grid = (unsigned)((pb.pp.items + 7) / 8);
+    const unsigned grid = pb.pp.blocks;
 #define KB_PREP(IN, OUT) qk_prep_kernel<IN, OUT><<<grid, 256, 0, stream>>>(pb.pp)
     if (out_dtype == KB_F32) {
         KB_PREP(float, float);        // in-place fp32 norm / RoPE as the engine's own ops do (validated by the caller)
