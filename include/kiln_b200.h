@@ -120,6 +120,37 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w,
                 int dtype, int out_dtype, float eps,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* The NAG combine on its own, in place on `a` (Z+) with `an` (Z-): the engine's k_nag launch
+ * (engine/src/dit.cu:486, 524; kernel :295-324). Rows of `dim` channels (all heads together, dim % 8 == 0,
+ * dim <= 8192), row strides lda / ldn in elements, dtype KB_F16 / KB_BF16 / KB_F32 for both. One pass:
+ * the row stays in registers between the norm and the blend. kb_attn_nag fuses this into the attention
+ * kernel; this entry point serves callers that already hold Z+ and Z- (head-split runs, the unfused engine path). */
+int kb_nag_combine(void* a, const void* an, int T, int dim, int lda, int ldn,
+                   float scale, float tau, float alpha, int dtype, void* stream);
+
+/* ---- Head split at batch 1 (no counterpart in the reference, which is single-GPU: one cudaSetDevice at
+ * engine/src/kernels.cu:207, no peer access, no collective). Each of G GPUs owns H/G heads: its Q/K/V are
+ * [rows, (H/G)*128] slices, and every GPU needs the full [Tq, H*128] output for the following projection.
+ * kb_attn_push is kb_attn_self / kb_attn_cross over the local heads whose epilogue writes each finished
+ * 128-row tile into the output buffer of EVERY GPU (peer-mapped pointers, plain stores over NVLink) at
+ * column col0 = rank*(H/G)*128, then bumps every GPU's arrival counter (system-scope fence + atomic).
+ * kb_wait_arrivals enqueues a one-thread kernel that waits, bounded, until this GPU's counter reaches
+ * `target`; work enqueued after it on the stream may read the gathered rows. Counters only grow: after
+ * the n-th call target = n * kb_push_arrivals_per_call(...). Buffers for peers come from kb_peer_alloc
+ * (cudaMalloc + zero fill, at set-up time) and travel between processes as 64-byte IPC handles. */
+int kb_peer_alloc(size_t bytes, void** ptr);
+int kb_peer_free(void* ptr);
+int kb_ipc_export(void* ptr, unsigned char* handle64);
+int kb_ipc_import(const unsigned char* handle64, void** ptr);
+int kb_ipc_close(void* ptr);
+int kb_attn_push(void* const* out_peers, unsigned long long* const* ctr_peers, int n_peers, int col0,
+                 const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
+                 const float* rope_cos, const float* rope_sin,
+                 int B, int Tq, int Tk, int npad, int H_local, int ld_q, int ld_k, int ld_v, int ld_o,
+                 int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes, void* stream);
+unsigned long long kb_push_arrivals_per_call(int B, int Tq, int H_local, int n_peers);
+int kb_wait_arrivals(const unsigned long long* ctr, unsigned long long target, void* stream);
+
 /* Row pre-pass on its own: out[r, h*128..] = rope(rmsnorm(in[r, h*128..])) as 16-bit, or a plain
  * conversion when w, cos and sin are NULL. in_dtype may be KB_F32 (the engine keeps Q/K/V in fp32:
  * engine/src/dit.cu:429-430); with in_dtype = out_dtype = KB_F32 it is the engine's in-place fp32

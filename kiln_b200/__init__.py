@@ -6,4 +6,4 @@ tests and the benchmark. There is no CPU fallback: every launch entry point fail
 or an sm_100 device is missing.
 """
 from .ops import (KB_BF16, KB_F16, KB_F32, PROF_ATTENTION, PROF_NAG, PROF_NORM_ROPE, KilnError, attn_cross, attn_nag,  # noqa: F401
-                  attn_self, check_status, lib, prof_enable, prof_read, qk_prep, workspace_bytes)
+                  attn_push, attn_self, check_status, lib, nag_combine, prof_enable, prof_read, qk_prep, wait_arrivals, workspace_bytes)

@@ -11,6 +11,7 @@
 #include "../../include/kiln_b200.h"
 #include "attn_sm100.cuh"
 #include "prep.cuh"
+#include "combine.cuh"
 #include "selfcheck.cuh"
 
 namespace {
@@ -230,13 +231,29 @@ struct Stage {
     }
 };
 
+// where a head-split run stores its output: every GPU's [B*Tq, ld_o] buffer (own included) and arrival counter
+struct PeerSpec {
+    void* const* out_peers;
+    unsigned long long* const* ctr_peers;
+    int n_peers, col0;
+};
+
 // shared body of self- and cross-attention: q [B*Tq], k/v [B*Tk]
 int attn_pair(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
               const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk, int npad, int H, int ld_q, int ld_k,
               int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes,
-              cudaStream_t stream) {
+              cudaStream_t stream, const PeerSpec* peers = nullptr) {
     if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || npad < 0) return KB_ERR_ARG;
+    if (peers) {
+        if (peers->n_peers < 1 || peers->n_peers > MAX_PEERS || peers->col0 < 0 || (peers->col0 & 7) || out_dtype == KB_F32) return KB_ERR_ARG;
+        if (ld_o < peers->col0 + H * 128) return KB_ERR_SHAPE;
+        for (int i = 0; i < peers->n_peers; i++) {
+            if (!peers->out_peers[i] || !peers->ctr_peers[i]) return KB_ERR_ARG;
+            if (!aligned16(peers->out_peers[i])) return KB_ERR_ALIGN;
+        }
+        out = peers->out_peers[0];
+    }
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
     int rc;
     if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k, ld_k, H, dtype)) || (rc = check_mat(v, ld_v, H, dtype)) ||
@@ -266,6 +283,11 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     p.Tk[0] = Tk; p.Tk[1] = 0; p.npad[0] = npad; p.npad[1] = 0;
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
+    if (peers) {
+        p.n_peers = peers->n_peers;
+        p.col0 = peers->col0;
+        for (int i = 0; i < peers->n_peers; i++) { p.out_peers[i] = peers->out_peers[i]; p.ctr_peers[i] = peers->ctr_peers[i]; }
+    }
     KB_SET_DBG(p);
     ProfScope ps(st, KB_PROF_ATTENTION, stream);
     return launch_attn<MODE_PAIR>(out_dtype, tq, tk, tv, tk, tv, p, stream);
@@ -442,6 +464,71 @@ int kb_prof_read(int category, double* total_ms, int* launches) {
     *total_ms = sum;
     *launches = n;
     return KB_OK;
+}
+
+int kb_nag_combine(void* a, const void* an, int T, int dim, int lda, int ldn, float scale, float tau, float alpha, int dtype, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!a || !an || T < 0 || dim <= 0 || !valid_in_dtype(dtype)) return KB_ERR_ARG;
+    if ((dim & 7) || dim > 256 * 8 * NAG_MAX_CHUNKS || lda < dim || ldn < dim) return KB_ERR_SHAPE;
+    const int m = dtype == KB_F32 ? 3 : 7;
+    if (!aligned16(a) || !aligned16(an) || (lda & m) || (ldn & m)) return KB_ERR_ALIGN;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    if (T == 0) return KB_OK;
+    ProfScope ps(st, KB_PROF_NAG, stream);
+    if (dtype == KB_F16) nag_combine_kernel<__half><<<T, 256, 0, stream>>>((__half*)a, (const __half*)an, dim, lda, ldn, scale, tau, alpha);
+    else if (dtype == KB_BF16) nag_combine_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)an, dim, lda, ldn, scale, tau, alpha);
+    else nag_combine_kernel<float><<<T, 256, 0, stream>>>((float*)a, (const float*)an, dim, lda, ldn, scale, tau, alpha);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------------------------- head split
+int kb_peer_alloc(size_t bytes, void** ptr) {
+    if (!ptr || !bytes) return KB_ERR_ARG;
+    if (cudaMalloc(ptr, bytes) != cudaSuccess) { cudaGetLastError(); return KB_ERR_CUDA; }
+    if (cudaMemset(*ptr, 0, bytes) != cudaSuccess) return KB_ERR_CUDA;
+    return KB_OK;
+}
+int kb_peer_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? KB_OK : KB_ERR_CUDA; }
+int kb_ipc_export(void* ptr, unsigned char* handle64) {
+    if (!ptr || !handle64) return KB_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) { cudaGetLastError(); return KB_ERR_CUDA; }
+    memcpy(handle64, &h, 64);
+    return KB_OK;
+}
+int kb_ipc_import(const unsigned char* handle64, void** ptr) {
+    if (!ptr || !handle64) return KB_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return KB_ERR_CUDA; }
+    return KB_OK;
+}
+int kb_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? KB_OK : KB_ERR_CUDA; }
+
+int kb_attn_push(void* const* out_peers, unsigned long long* const* ctr_peers, int n_peers, int col0, const void* q, const void* k,
+                 const void* v, const void* qn_w, const void* kn_w, const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk,
+                 int npad, int H_local, int ld_q, int ld_k, int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+    if (!out_peers || !ctr_peers) return KB_ERR_ARG;
+    PeerSpec ps{out_peers, ctr_peers, n_peers, col0};
+    return attn_pair(nullptr, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, Tq, Tk, npad, H_local, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype, eps,
+                     workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &ps);
+}
+
+unsigned long long kb_push_arrivals_per_call(int B, int Tq, int H_local, int n_peers) {
+    return (unsigned long long)n_peers * (unsigned long long)B * (unsigned long long)H_local * (unsigned long long)((Tq + 127) / 128);
+}
+
+int kb_wait_arrivals(const unsigned long long* ctr, unsigned long long target, void* stream) {
+    if (!ctr) return KB_ERR_ARG;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    wait_arrivals_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(ctr, target, st->status, ST_TIMEOUT);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 // ---------------------------------------------------------------------------------------------

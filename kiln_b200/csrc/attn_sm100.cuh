@@ -49,9 +49,17 @@ constexpr int ATTN_SMEM = 2 * TILE_BYTES + NSTAGE * TILE_BYTES + CTRL_BYTES + 10
 // error bits written to the status word
 constexpr uint32_t ST_TIMEOUT = 1u;
 
+constexpr int MAX_PEERS = 8;
+
 struct AttnParams {
     void* out;          // [B*Tq, ldo]
     int ldo;
+    // Head-split runs (MODE_PAIR, 16-bit output): the output tile is stored into the [B*Tq, ldo] buffer of every
+    // GPU in `out_peers` (this GPU's own buffer included) at column offset col0, and each finished 128-row tile
+    // bumps the arrival counter of every peer. n_peers = 0 on the ordinary single-buffer path.
+    void* out_peers[MAX_PEERS];
+    unsigned long long* ctr_peers[MAX_PEERS];
+    int n_peers, col0;
     int Tq, H, B;
     int Tk[2];          // MODE_PAIR uses [0]; MODE_NAG: positive, negative context
     int npad[2];
@@ -110,6 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t bars = sKV + NSTAGE * TILE_BYTES;              // BAR_COUNT x 8 bytes
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
+    volatile uint32_t* const warp_ok = reinterpret_cast<volatile uint32_t*>(ctrl + 264);   // [8] per softmax warp
     float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 7 x 128 floats
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
@@ -265,6 +274,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #endif
         // -------------------------------------------------------------------- epilogue (softmax warps)
         if (MODE == MODE_PAIR) {
+            // Make `ok` uniform over the stream's four warps before any barrier that only they take part in:
+            // this barrier is reached unconditionally, so a warp that gave up cannot leave the others waiting.
+            if (nblk[warp >> 2] > 0) {
+                if (lane == 0) warp_ok[warp] = ok ? 1u : 0u;
+                named_bar_sync(3 + (warp >> 2), 128);
+                const int w0 = warp & 4;
+                ok = (warp_ok[w0] & warp_ok[w0 + 1] & warp_ok[w0 + 2] & warp_ok[w0 + 3]) != 0u;
+            }
             if (ok && nblk[warp >> 2] > 0) {
                 const int i = warp >> 2;
                 const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -277,18 +294,60 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     l = l * scale + (float)p.npad[0] * exp2f(-mn);
                 }
                 const float inv = scale / l;
-                const int row = q0 + i * BM + (tid & 127);
-                OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD;
+                const int t = tid & 127;
+                if constexpr (sizeof(OutT) == 2) {
+                    // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream has
+                    // completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
+                    constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+                    uint8_t* const stage = smem + i * TILE_BYTES;
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    uint32_t o[32];
-                    float v[32];
-                    tmem_ld32(tO + 32u * q, o);
-                    tmem_wait_ld();
-                    reg_fence32(o);
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + 32u * q, o);
+                        tmem_wait_ld();
+                        reg_fence32(o);
 #pragma unroll
-                    for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
-                    if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                        for (int c = 0; c < 4; c++) {                    // 16-byte chunk 4q + c of the row, XOR-swizzled against bank conflicts
+                            uint4 pk;
+                            pk.x = pack16<ODT>(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+                            pk.y = pack16<ODT>(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+                            pk.z = pack16<ODT>(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+                            pk.w = pack16<ODT>(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+                            *reinterpret_cast<uint4*>(stage + t * 256 + (((4 * q + c) ^ (t & 15)) << 4)) = pk;
+                        }
+                    }
+                    named_bar_sync(3 + i, 128);                          // this stream's four warps
+                    const int np = p.n_peers > 0 ? p.n_peers : 1;
+                    const int wq = warp & 3;
+                    for (int rr = 0; rr < 32; rr++) {
+                        const int lr = 32 * wq + rr, row = q0 + i * BM + lr;
+                        if (row >= p.Tq) break;                          // warp-uniform
+                        const uint2 val = *reinterpret_cast<const uint2*>(stage + lr * 256 + (((lane >> 1) ^ (lr & 15)) << 4) + (lane & 1) * 8);
+                        const size_t off = ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)(p.col0 + h * HD) + (size_t)lane * 4;
+                        for (int pe = 0; pe < np; pe++) {
+                            OutT* base_out = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out);
+                            *reinterpret_cast<uint2*>(base_out + off) = val;
+                        }
+                    }
+                    if (p.n_peers > 0) {
+                        __threadfence_system();                          // the tile is visible to every GPU before the arrival
+                        named_bar_sync(3 + i, 128);
+                        if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
+                    }
+                } else {
+                    const int row = q0 + i * BM + t;
+                    OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t o[32];
+                        float v[32];
+                        tmem_ld32(tO + 32u * q, o);
+                        tmem_wait_ld();
+                        reg_fence32(o);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
+                        if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                    }
                 }
             }
             tc_fence_before();

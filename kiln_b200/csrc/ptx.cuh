@@ -67,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
-// 3-D tiled load global -> this CTA's shared memory, completion counted on an mbarrier (no multicast).
+// 3-D tiled load global -> this CTA's shared memory, completion counted on an mbarrier.
 // Coordinates are (column, row, batch); the column must be a multiple of 8 elements (16 bytes).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
     asm volatile(

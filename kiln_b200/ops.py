@@ -49,6 +49,25 @@ def lib():
         L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
         L.kb_status.restype = i
         L.kb_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        ull = ctypes.c_ulonglong
+        L.kb_nag_combine.restype = i
+        L.kb_nag_combine.argtypes = [vp, vp, i, i, i, i, f, f, f, i, vp]
+        L.kb_peer_alloc.restype = i
+        L.kb_peer_alloc.argtypes = [sz, ctypes.POINTER(vp)]
+        L.kb_peer_free.restype = i
+        L.kb_peer_free.argtypes = [vp]
+        L.kb_ipc_export.restype = i
+        L.kb_ipc_export.argtypes = [vp, ctypes.c_char_p]
+        L.kb_ipc_import.restype = i
+        L.kb_ipc_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.kb_ipc_close.restype = i
+        L.kb_ipc_close.argtypes = [vp]
+        L.kb_attn_push.restype = i
+        L.kb_attn_push.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i, i, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_push_arrivals_per_call.restype = ull
+        L.kb_push_arrivals_per_call.argtypes = [i, i, i, i]
+        L.kb_wait_arrivals.restype = i
+        L.kb_wait_arrivals.argtypes = [vp, ull, vp]
         L.kb_prof_enable.restype = i
         L.kb_prof_enable.argtypes = [i]
         L.kb_prof_read.restype = i
@@ -123,6 +142,30 @@ def attn_nag(out, q, k_pos, v_pos, Tk_pos, npad_pos, k_neg, v_neg, Tk_neg, npad_
                              _ptr(v_neg), Tk_neg, npad_neg, scale, tau, alpha, Tq, H, _ld(q), _ld(k_pos), _ld(out), _dt(q),
                              _dt(out), eps, wp, wb, _stream()), "kb_attn_nag")
     return out
+
+
+def nag_combine(a, an, scale, tau, alpha):
+    """In-place NAG combine of a (Z+) with an (Z-), rows of all heads together (engine counterpart: k_nag)."""
+    assert a.dtype == an.dtype and a.shape == an.shape
+    _check(lib().kb_nag_combine(_ptr(a), _ptr(an), a.shape[0], a.shape[1], _ld(a), _ld(an), scale, tau, alpha, _dt(a), _stream()), "kb_nag_combine")
+    return a
+
+
+def attn_push(out_ptrs, ctr_ptrs, col0, q, k, v, B, Tq, Tk, npad, H_local, ld_o, out_dtype, qn_w=None, kn_w=None, rope_cos=None,
+              rope_sin=None, eps=1e-6, workspace=None):
+    """Attention over the local heads whose output tiles are stored into every peer buffer (device addresses in
+    out_ptrs, this GPU's own included) at column col0, bumping the counters at ctr_ptrs. out_dtype: KB_F16 / KB_BF16."""
+    n = len(out_ptrs)
+    outs = (ctypes.c_void_p * n)(*out_ptrs)
+    ctrs = (ctypes.c_void_p * n)(*ctr_ptrs)
+    wp, wb = _ws(workspace)
+    _check(lib().kb_attn_push(outs, ctrs, n, col0, _ptr(q), _ptr(k), _ptr(v), _ptr(qn_w), _ptr(kn_w), _ptr(rope_cos), _ptr(rope_sin),
+                              B, Tq, Tk, npad, H_local, _ld(q), _ld(k), _ld(v), ld_o, _dt(q), out_dtype, eps, wp, wb, _stream()), "kb_attn_push")
+
+
+def wait_arrivals(ctr_ptr, target):
+    """Enqueue the bounded wait for `target` tile arrivals on this GPU's counter (device address ctr_ptr)."""
+    _check(lib().kb_wait_arrivals(ctypes.c_void_p(ctr_ptr), target, _stream()), "kb_wait_arrivals")
 
 
 def qk_prep(out, x, rows, H, T, w=None, rope_cos=None, rope_sin=None, eps=1e-6):
