@@ -42,6 +42,10 @@ constexpr int BN = 128;                 // keys per block
 constexpr int TILE_BYTES = BM * HD * 2; // 32 KiB: one Q, K or V tile (two 64-column swizzled halves)
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int NSTAGE = 4;               // K/V ring depth
+#ifndef KB_POLY_PAIRS
+#define KB_POLY_PAIRS 0
+#endif
+constexpr int POLY_PAIRS = KB_POLY_PAIRS; // of every 8 score pairs, this many take 2^x on the FMA pipe instead of MUFU
 constexpr int ATTN_THREADS = 384;
 constexpr int CTRL_BYTES = 8192;
 constexpr int ATTN_SMEM = 2 * TILE_BYTES + NSTAGE * TILE_BYTES + CTRL_BYTES + 1024;  // + alignment slack
@@ -192,11 +196,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 32; e++) {
-                mx0 = fmaxf(mx0, __uint_as_float(s[0][e]));
-                mx1 = fmaxf(mx1, __uint_as_float(s[1][e]));
-                mx2 = fmaxf(mx2, __uint_as_float(s[2][e]));
-                mx3 = fmaxf(mx3, __uint_as_float(s[3][e]));
+            for (int e = 0; e < 32; e += 2) {                      // 3-input max: two scores per instruction
+                mx0 = max3(mx0, __uint_as_float(s[0][e]), __uint_as_float(s[0][e + 1]));
+                mx1 = max3(mx1, __uint_as_float(s[1][e]), __uint_as_float(s[1][e + 1]));
+                mx2 = max3(mx2, __uint_as_float(s[2][e]), __uint_as_float(s[2][e + 1]));
+                mx3 = max3(mx3, __uint_as_float(s[3][e]), __uint_as_float(s[3][e + 1]));
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 #ifdef KB_DEBUG
@@ -230,24 +234,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                 }
             }
-            const float mc = row_m * c;
-            float sum0 = 0.f, sum1 = 0.f;
+            // p = 2^(s*c - m*c) on packed pairs: one FFMA2 per two scores, then MUFU ex2 for most pairs and the
+            // FMA-pipe polynomial for POLY_PAIRS of every 8 pairs (the MUFU unit is the co-bottleneck of this
+            // kernel: 128 ex2 per thread and block take as long as the two MMAs they overlap with).
+            const uint64_t c2 = pack2(c, c), nmc2 = pack2(-row_m * c, -row_m * c);
+            uint64_t sum2a = pack2(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
             for (int q = 0; q < 2; q++) {
                 uint32_t pk[32];
 #pragma unroll
-                for (int e = 0; e < 16; e++) {
-                    const float p0 = ex2(fmaf(__uint_as_float(s[2 * q][2 * e]), c, -mc));
-                    const float p1 = ex2(fmaf(__uint_as_float(s[2 * q][2 * e + 1]), c, -mc));
-                    const float p2 = ex2(fmaf(__uint_as_float(s[2 * q + 1][2 * e]), c, -mc));
-                    const float p3 = ex2(fmaf(__uint_as_float(s[2 * q + 1][2 * e + 1]), c, -mc));
-                    sum0 += p0 + p1;
-                    sum1 += p2 + p3;
+                for (int e = 0; e < 32; e++) {                     // pair e of this half: scores 2e, 2e+1 of chunk 2q + e/16
+                    const int ch = 2 * q + (e >> 4), ee = (e & 15) * 2;
+                    const uint64_t x2 = fma2(pack2u(s[ch][ee], s[ch][ee + 1]), c2, nmc2);
+                    uint64_t p2;
+                    if ((e & 7) >= 8 - POLY_PAIRS) {
+                        p2 = ex2_poly2(x2);
+                    } else {
+                        float x0, x1;
+                        unpack2(x2, x0, x1);
+                        p2 = pack2(ex2(x0), ex2(x1));
+                    }
+                    if (e & 1) sum2b = add2(sum2b, p2); else sum2a = add2(sum2a, p2);
+                    float p0, p1;
+                    unpack2(p2, p0, p1);
                     pk[e] = pack16<DT_F16>(p0, p1);
-                    pk[16 + e] = pack16<DT_F16>(p2, p3);
                 }
                 tmem_st32(tS + 32u * q, pk);                       // P: key pair (2c, 2c+1) in column c
             }
+            float sum0, sum1, sum2, sum3;
+            unpack2(sum2a, sum0, sum1);
+            unpack2(sum2b, sum2, sum3);
+            sum0 += sum2; sum1 += sum3;
             row_l += sum0 + sum1;
             tmem_wait_st();
             tc_fence_before();

@@ -194,6 +194,65 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t local_saddr, uint32_t ran
 template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
+// ---------------------------------------------------------------- packed fp32 pairs (f32x2) and 3-input max
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ void unpack2u(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {   // round toward -inf
+    uint64_t r;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// 2^x for a pair on the FMA pipe: x = floor(x) + f, 2^f by a degree-3 polynomial (max relative error
+// 7.5e-5, below half an fp16 ulp of the result), floor(x) added into the exponent field. Takes the load off
+// the 16-per-clock MUFU unit, which the attention softmax otherwise saturates. Inputs are clamped to
+// >= -126 (a masked -inf score comes out as 2^-126, which is zero in fp16 and in the row sums).
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const uint64_t magic = pack2(12582912.f, 12582912.f);                 // 1.5 * 2^23: low mantissa bits of x + magic hold floor(x)
+    const uint64_t t2 = add2_rm(x2, magic);
+    const uint64_t f2 = sub2(x2, sub2(t2, magic));                        // x - floor(x) in [0, 1)
+    uint64_t p2 = fma2(pack2(0.07802422344684601f, 0.07802422344684601f), f2, pack2(0.22606723010540009f, 0.22606723010540009f));
+    p2 = fma2(p2, f2, pack2(0.695833683013916f, 0.695833683013916f));
+    p2 = fma2(p2, f2, pack2(0.9999251961708069f, 0.9999251961708069f));
+    uint32_t t0, t1, p0, p1;
+    unpack2u(t2, t0, t1);
+    unpack2u(p2, p0, p1);
+    return pack2u(p0 + (t0 << 23), p1 + (t1 << 23));
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

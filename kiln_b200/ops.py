@@ -11,7 +11,7 @@ import os
 KB_F16, KB_BF16, KB_F32 = 0, 1, 2
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_PKG, "lib", "libkiln_b200.so")
+_LIB_PATH = os.environ.get("KILN_B200_LIB") or os.path.join(_PKG, "lib", "libkiln_b200.so")   # override: an alternative build of the same ABI
 _lib = None
 
 
