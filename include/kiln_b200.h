@@ -111,7 +111,10 @@ int kb_attn_cross(void* out, const void* q, const void* qn_w, const void* k, con
  *   g = s*Z+ - (s-1)*Z-;  ratio = |g|_1 / max(|Z+|_1, 1e-12) per token over all H*128 channels;
  *   out = alpha * g * (ratio > tau ? tau/ratio : 1) + (1 - alpha) * Z+
  * in one kernel. Replaces attention16 x2 + k_nag (engine/src/dit.cu:482-487, 295-324).
- * H must be 1, 2, 4, 8 or 16 (the heads of one query tile form one thread-block cluster). */
+ * The per-token norms span all heads: the thread blocks holding the heads of one query tile exchange
+ * their partial norms through a few KB of the workspace, so a workspace is ALWAYS required here
+ * (kb_attn_workspace_bytes(Tq, max(Tk_pos, Tk_neg), 2, H, dtype, norm_q, 0)), H <= 64, and the launch is
+ * cooperative (all its thread blocks are resident at once). */
 int kb_attn_nag(void* out, const void* q, const void* qn_w,
                 const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
                 const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg,

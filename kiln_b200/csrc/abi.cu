@@ -64,9 +64,8 @@ EncodeTiledFn g_encode = nullptr;
 std::mutex g_mu;
 
 template <typename K>
-int set_smem(K kernel, bool nonportable_cluster) {
+int set_smem(K kernel) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) return KB_ERR_CUDA;
-    if (nonportable_cluster && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return KB_ERR_CUDA;
     return KB_OK;
 }
 
@@ -84,12 +83,12 @@ int init_device(DeviceState& st, int dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     int rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>, false))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>, true))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>, true))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>, true))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>))) return rc;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return KB_ERR_CUDA;
     st.status = static_cast<unsigned int*>(p);
@@ -176,21 +175,19 @@ int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtyp
 
 template <int MODE, typename OutT>
 int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
-                  const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
+                  const CUtensorMap& tv1, const AttnParams& p, int sm_count, cudaStream_t stream) {
+    // persistent kernel: one CTA per SM (its shared memory and TMEM fill an SM) walks the work items
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
+    cfg.gridDim = dim3((unsigned)(p.n_items < sm_count ? p.n_items : sm_count), 1, 1);
     cfg.dynamicSmemBytes = ATTN_SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    if (MODE == MODE_PAIR) {
-        cfg.gridDim = dim3((unsigned)((p.Tq + 2 * BM - 1) / (2 * BM)), (unsigned)p.H, (unsigned)p.B);
-        cfg.numAttrs = 0;
-    } else {
-        cfg.gridDim = dim3((unsigned)((p.Tq + BM - 1) / BM), (unsigned)p.H, 1);
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = (unsigned)p.H;   // all heads of one query tile: the NAG norm spans them
-        attr[0].val.clusterDim.z = 1;
+    cfg.numAttrs = 0;
+    if (MODE == MODE_NAG) {
+        // the CTAs holding the heads of one query tile wait for each other: all CTAs must be resident at once
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
@@ -200,18 +197,11 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
 
 template <int MODE>
 int launch_attn(int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
-                const CUtensorMap& tv1, const AttnParams& p, cudaStream_t stream) {
-    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, p, stream);
-    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, p, stream);
-    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, p, stream);
+                const CUtensorMap& tv1, const AttnParams& p, int sm_count, cudaStream_t stream) {
+    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, p, sm_count, stream);
+    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, p, sm_count, stream);
+    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, p, sm_count, stream);
 }
-
-#ifdef KB_DEBUG
-float* g_dbg = nullptr;
-#define KB_SET_DBG(p) (p).dbg = g_dbg
-#else
-#define KB_SET_DBG(p)
-#endif
 
 constexpr float SCALE_LOG2 = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
 
@@ -222,8 +212,9 @@ struct Stage {
     char* ws;
     size_t left;
     bool overflow = false;
-    void* take(size_t rows, int H) {
-        const size_t n = align256(rows * (size_t)H * 128 * 2);
+    void* take(size_t rows, int H) { return take_bytes(rows * (size_t)H * 128 * 2); }
+    void* take_bytes(size_t bytes) {
+        const size_t n = align256(bytes);
         if (!ws || n > left) { overflow = true; return nullptr; }
         void* p = ws;
         ws += n; left -= n;
@@ -281,6 +272,7 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     AttnParams p = {};
     p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = B;
     p.Tk[0] = Tk; p.Tk[1] = 0; p.npad[0] = npad; p.npad[1] = 0;
+    p.n_items = ((Tq + 2 * BM - 1) / (2 * BM)) * H * B;
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
     if (peers) {
@@ -288,9 +280,8 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
         p.col0 = peers->col0;
         for (int i = 0; i < peers->n_peers; i++) { p.out_peers[i] = peers->out_peers[i]; p.ctr_peers[i] = peers->ctr_peers[i]; }
     }
-    KB_SET_DBG(p);
     ProfScope ps(st, KB_PROF_ATTENTION, stream);
-    return launch_attn<MODE_PAIR>(out_dtype, tq, tk, tv, tk, tv, p, stream);
+    return launch_attn<MODE_PAIR>(out_dtype, tq, tk, tv, tk, tv, p, st->sm_count, stream);
 }
 
 }  // namespace
@@ -315,10 +306,7 @@ const char* kb_error_string(int code) {
 
 int kb_version(void) { return 100; }
 
-#ifdef KB_DEBUG
-// debug builds only: device buffer of 66048 floats that CTA (0,0,0) of the next launches dumps into
-void kb_debug_set_buffer(float* p) { g_dbg = p; }
-#endif
+
 
 int kb_init(void) {
     DeviceState* st;
@@ -331,6 +319,10 @@ size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int n_ctx, int H, int dty
     if (conv || norm_q) n += align256((size_t)rows_q * H * 128 * 2);
     if (conv || norm_k) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);   // K of every context
     if (conv) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);             // V of every context
+    if (n_ctx == 2) {                                                                  // NAG: per-head norm partials and arrival counters
+        const size_t n_qt = ((size_t)rows_q + 127) / 128;
+        n += align256(n_qt * H * 256 * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+    }
     return n;
 }
 
@@ -355,7 +347,7 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (Tq <= 0 || Tk_pos <= 0 || Tk_neg <= 0 || H <= 0 || npad_pos < 0 || npad_neg < 0) return KB_ERR_ARG;
-    if (H > 16 || (H & (H - 1))) return KB_ERR_SHAPE;  // the heads of a query tile are one cluster
+    if (H > 64) return KB_ERR_SHAPE;                   // the heads of a query tile run on H different SMs at once
     int rc;
     if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k_pos, ld_kv, H, dtype)) || (rc = check_mat(v_pos, ld_kv, H, dtype)) ||
         (rc = check_mat(k_neg, ld_kv, H, dtype)) || (rc = check_mat(v_neg, ld_kv, H, dtype)) || (rc = check_out(out, ld_o, H, out_dtype)))
@@ -363,8 +355,13 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     DeviceState* st;
     if ((rc = get_state(&st))) return rc;
     const bool conv = dtype != KB_F16;
-    if ((conv || qn_w) && (!workspace || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+    if (!workspace || !aligned16(workspace)) return KB_ERR_WORKSPACE;   // always: the cross-head norm exchange lives there
     Stage sg{static_cast<char*>(workspace), workspace_bytes};
+    const int n_qt = (Tq + BM - 1) / BM;
+    float* nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * 256 * sizeof(float)));
+    unsigned int* nag_flag = static_cast<unsigned int*>(sg.take_bytes((size_t)n_qt * sizeof(unsigned int)));
+    if (sg.overflow) return KB_ERR_WORKSPACE;
+    if (cudaMemsetAsync(nag_flag, 0, (size_t)n_qt * sizeof(unsigned int), stream) != cudaSuccess) return KB_ERR_CUDA;
     PrepBatch pb;
     pb.pp.H = H; pb.pp.eps = eps;
     const void* qq = q;
@@ -390,12 +387,13 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     AttnParams p = {};
     p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = 1;
     p.Tk[0] = Tk_pos; p.Tk[1] = Tk_neg; p.npad[0] = npad_pos; p.npad[1] = npad_neg;
+    p.n_items = n_qt * H;
+    p.nag_part = nag_part; p.nag_flag = nag_flag;
     p.scale_log2 = SCALE_LOG2;
     p.nag_s = scale; p.nag_tau = tau; p.nag_alpha = alpha;
     p.status = st->status;
-    KB_SET_DBG(p);
     ProfScope ps(st, KB_PROF_NAG, stream);
-    return launch_attn<MODE_NAG>(out_dtype, tq, tk0, tv0, tk1, tv1, p, stream);
+    return launch_attn<MODE_NAG>(out_dtype, tq, tk0, tv0, tk1, tv1, p, st->sm_count, stream);
 }
 
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
@@ -595,8 +593,8 @@ int kb_attn_selfcheck(void* workspace, size_t workspace_bytes, float* max_abs_er
     float* out = (float*)take((size_t)Tq * ld * 4); float* ref = (float*)take((size_t)Tq * ld * 4);
     float* ref2 = (float*)take((size_t)Tq * ld * 4);
     unsigned int* err = (unsigned int*)take(256);
-    void* stage = take(5 * align256((size_t)Tq * ld * 2));          // fp16 staging of bf16 inputs
-    const size_t stage_bytes = 5 * align256((size_t)Tq * ld * 2);
+    const size_t stage_bytes = kb_attn_workspace_bytes(Tq, Tq, 2, H, KB_BF16, 1, 1);   // fp16 staging of bf16 inputs + NAG scratch
+    void* stage = take(stage_bytes);
     const size_t n = (size_t)Tq * ld;
     const unsigned fb = (unsigned)((n + 255) / 256), ab = (unsigned)((Tq * H + 127) / 128);
     if (cudaMemsetAsync(err, 0, 4, stream) != cudaSuccess) return KB_ERR_CUDA;

@@ -7,20 +7,26 @@
 // all-zero keys joining the softmax analytically (engine/src/tcflash.cuh:136-147), fp32 statistics,
 // base-2 exponent with the scale log2(e)/sqrt(128) (engine/src/tcflash.cuh:164).
 //
-// One CTA runs TWO softmax streams that ping-pong on the tensor core:
-//   MODE_PAIR : two 128-row query tiles of one (batch, head) against one K/V sequence
+// The kernel is PERSISTENT: one CTA per SM walks a list of work items, so TMEM allocation, barrier
+// set-up and the TMA/MMA pipeline fill are paid once, and the loads of the next item run under the
+// epilogue of the current one. One item runs TWO softmax streams that ping-pong on the tensor core:
+//   MODE_PAIR : item = two 128-row query tiles of one (batch, head) against one K/V sequence
 //               (self-attention and plain cross-attention);
-//   MODE_NAG  : one 128-row query tile against TWO K/V sequences (positive and negative context),
-//               followed by the NAG combine of engine/src/dit.cu:295-324 in the epilogue. The combine
-//               needs per-token L1 norms over ALL heads, so the CTAs of the 16 heads of one query tile
-//               form a thread-block cluster and exchange their partial norms through distributed
-//               shared memory; nothing but the blended result goes to HBM.
+//   MODE_NAG  : item = one 128-row query tile of one head against TWO K/V sequences (positive and
+//               negative context), followed by the NAG combine of engine/src/dit.cu:295-324 in the
+//               epilogue. The combine needs per-token L1 norms over ALL heads: the CTAs that hold the
+//               heads of one query tile (adjacent items, so they run at the same time) publish their
+//               partial norms in a small global scratch, bump a per-tile counter and wait, bounded,
+//               for the other heads. Nothing but the blended result is written as output.
 //
 // Warp roles (384 threads): warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1 (warp w
 // owns TMEM lanes 32*(w%4)..+31, one query row per thread), warp 8 issues MMAs (one lane), warp 9
 // issues TMA loads (one lane), warps 10-11 idle.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i overwrites the first
 // 64 columns of S_i as packed fp16 pairs.
+// (Tried and dropped: 64-key half blocks with two S buffers per stream to decouple softmax and MMA
+// latency. An S MMA with N = 64 reads as many shared-memory bytes per FLOP for its A operand as it
+// saves on B, runs at half rate, and the kernel got 1.5x slower.)
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -65,18 +71,19 @@ struct AttnParams {
     unsigned long long* ctr_peers[MAX_PEERS];
     int n_peers, col0;
     int Tq, H, B;
+    int n_items;        // MODE_PAIR: ceil(Tq/256) * H * B; MODE_NAG: ceil(Tq/128) * H
     int Tk[2];          // MODE_PAIR uses [0]; MODE_NAG: positive, negative context
     int npad[2];
     float scale_log2;   // log2(e) / sqrt(128)
     float nag_s, nag_tau, nag_alpha;
+    float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][H][2][128]: per head |Z+|_1 and |g|_1 of each row
+    unsigned int* nag_flag;  // MODE_NAG [ceil(Tq/128)] arrival counters, zero before the launch
     uint32_t* status;   // device word, OR-ed with ST_* on failure
-#ifdef KB_DEBUG
-    float* dbg;         // debug builds only: CTA (0,0,0) dumps S(0), P(0) of stream 0 and the raw O, m, l of both streams
-#endif
 };
 
 // barrier slots inside the control block
-enum { BAR_QFULL = 0, BAR_SFULL = 2, BAR_PFULL = 4, BAR_ODONE = 6, BAR_KVFULL = 8, BAR_KVEMPTY = 8 + NSTAGE, BAR_COUNT = 8 + 2 * NSTAGE };
+enum { BAR_QFULL = 0, BAR_QEMPTY = 2, BAR_SFULL = 4, BAR_PFULL = 6, BAR_ODONE = 8, BAR_OFREE = 10, BAR_KVFULL = 12,
+       BAR_KVEMPTY = 12 + NSTAGE, BAR_COUNT = 12 + 2 * NSTAGE };
 
 // full-CTA barrier usable from divergent role branches (same id and count everywhere)
 __device__ __forceinline__ void cta_sync() { named_bar_sync(2, ATTN_THREADS); }
@@ -107,6 +114,36 @@ __device__ __forceinline__ void store32(OutT* dst, const float (&v)[32]) {
     }
 }
 
+// One work item: which rows, head and batch element, and how many 128-key blocks each stream runs
+// (0 = the stream does not exist in this item).
+struct Item {
+    int q0, h, b, qt;
+    int nblk[2];
+};
+
+template <int MODE>
+__device__ __forceinline__ Item decode_item(int w, const AttnParams& p) {
+    Item it;
+    if (MODE == MODE_PAIR) {
+        const int nqp = (p.Tq + 2 * BM - 1) / (2 * BM);       // query-tile pairs per (batch, head), fastest: K/V reuse in L2
+        const int qp = w % nqp, hb = w / nqp;
+        it.h = hb % p.H;
+        it.b = hb / p.H;
+        it.q0 = qp * 2 * BM;
+        it.qt = qp;
+        it.nblk[0] = (p.Tk[0] + BN - 1) / BN;
+        it.nblk[1] = (it.q0 + BM < p.Tq) ? it.nblk[0] : 0;
+    } else {
+        it.h = w % p.H;                                       // heads fastest: the heads of a query tile run side by side
+        it.qt = w / p.H;
+        it.b = 0;
+        it.q0 = it.qt * BM;
+        it.nblk[0] = (p.Tk[0] + BN - 1) / BN;
+        it.nblk[1] = (p.Tk[1] + BN - 1) / BN;
+    }
+    return it;
+}
+
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
@@ -123,22 +160,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
     volatile uint32_t* const warp_ok = reinterpret_cast<volatile uint32_t*>(ctrl + 264);   // [8] per softmax warp
-    float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 7 x 128 floats
+    volatile uint32_t* const wg_stop = reinterpret_cast<volatile uint32_t*>(ctrl + 296);   // [2] per softmax warpgroup
+    float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 5 x 128 floats x 2
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int q0 = blockIdx.x * (MODE == MODE_PAIR ? 2 * BM : BM);
-
-    // per-stream shape: number of key blocks, and whether the stream exists
-    int nblk[2];
-    nblk[0] = (p.Tk[0] + BN - 1) / BN;
-    nblk[1] = MODE == MODE_NAG ? (p.Tk[1] + BN - 1) / BN : ((q0 + BM < p.Tq) ? nblk[0] : 0);
 
     if (tid == 0) {
         for (int i = 0; i < BAR_COUNT; i++) {
             uint32_t count = 1;
-            if (i >= BAR_PFULL && i < BAR_PFULL + 2) count = 4;   // one arrival per softmax warp
+            if (i >= BAR_PFULL && i < BAR_PFULL + 2) count = 4;             // one arrival per softmax warp
+            if (i >= BAR_OFREE && i < BAR_OFREE + 2) count = MODE == MODE_NAG ? 8 : 4;   // NAG: both warpgroups read both O
             mbar_init(bar(i), count);
         }
         *abort_flag = 0u;
@@ -158,472 +190,487 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // state the softmax threads carry from the main loop into the epilogue
-    float row_m = -INFINITY, row_l = 0.f;
-    bool ok = true;
-
     // 384 threads start with 168 registers each; the MMA/TMA warpgroup gives most of its share to the
     // softmax ones. Everything a softmax thread runs from here on sits inside this branch so that the
-    // register budget of the branch is known at compile time; the full-CTA barriers below are therefore
+    // register budget of the branch is known at compile time; the final full-CTA barrier is therefore
     // written as the same bar.sync id from both branches.
     if (warp < 8) {
-        setmaxnreg_inc<224>();
+        setmaxnreg_inc<208>();
         // ------------------------------------------------------------------ softmax, one row per thread
-        const int i = warp >> 2;                                   // stream
+        const int i = warp >> 2;                                   // stream = warpgroup
+        const int t = tid & 127;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tS = tmem_base + lane_base + (uint32_t)(i * 128);
         const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(i * 128);
-        const int nb = nblk[i];
-        const int Tk = p.Tk[MODE == MODE_NAG ? i : 0];
         const float c = p.scale_log2;
-        for (int j = 0; j < nb; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), (uint32_t)(j & 1), abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t s[4][32];
+        uint32_t sf_cnt = 0, od_cnt = 0;                           // uses of s_full[i] / o_done[i] so far (phase parity)
+
+        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x) {
+            const Item it = decode_item<MODE>(w, p);
+            const int nb = it.nblk[i];
+            const int Tk = p.Tk[MODE == MODE_NAG ? i : 0];
+            float row_m = -INFINITY, row_l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nb; ++j) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), sf_cnt & 1u, abort_flag));
+                ++sf_cnt;
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s[4][32];
 #pragma unroll
-            for (int q = 0; q < 4; q++) tmem_ld32(tS + 32u * q, s[q]);
-            tmem_wait_ld();
-#pragma unroll
-            for (int q = 0; q < 4; q++) reg_fence32(s[q]);
-            if (j == nb - 1 && (Tk & (BN - 1))) {                  // ragged last block: keys >= Tk score -inf
-                const int valid = Tk - j * BN;
-#pragma unroll
-                for (int q = 0; q < 4; q++)
-#pragma unroll
-                    for (int e = 0; e < 32; e++)
-                        if (q * 32 + e >= valid) s[q][e] = 0xff800000u;
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) {                      // 3-input max: two scores per instruction
-                mx0 = max3(mx0, __uint_as_float(s[0][e]), __uint_as_float(s[0][e + 1]));
-                mx1 = max3(mx1, __uint_as_float(s[1][e]), __uint_as_float(s[1][e + 1]));
-                mx2 = max3(mx2, __uint_as_float(s[2][e]), __uint_as_float(s[2][e + 1]));
-                mx3 = max3(mx3, __uint_as_float(s[3][e]), __uint_as_float(s[3][e + 1]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-#ifdef KB_DEBUG
-            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 0) {
-                float* d = p.dbg + (size_t)i * 16384 + (size_t)(tid & 127) * 128;
-                for (int q = 0; q < 4; q++)
-                    for (int e = 0; e < 32; e++) d[q * 32 + e] = __uint_as_float(s[q][e]);
-            }
-#endif
-            if (j == 0) {
-                row_m = mx;
-            } else {
-                // Keep a stale maximum while the new one is less than 2^8 above it: P stays <= 256, which
-                // fp16/bf16 and the fp32 sums hold exactly as well, and O needs no rescale.
-                const bool need = (mx - row_m) * c > 8.f;
-                if (__any_sync(0xffffffffu, need)) {
-                    const float mn = fmaxf(row_m, mx);
-                    const float a = ex2((row_m - mn) * c);
-                    row_l *= a;
-                    row_m = mn;
-                    // The commit that completed S_i(j) was issued after PV_i(j-1), so O_i is quiescent here.
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        uint32_t o[32];
-                        tmem_ld32(tO + 32u * q, o);
-                        tmem_wait_ld();
-                        reg_fence32(o);
-#pragma unroll
-                        for (int e = 0; e < 32; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * a);
-                        tmem_st32(tO + 32u * q, o);
-                    }
-                }
-            }
-            // p = 2^(s*c - m*c) on packed pairs: one FFMA2 per two scores, then MUFU ex2 for most pairs and the
-            // FMA-pipe polynomial for POLY_PAIRS of every 8 pairs (the MUFU unit is the co-bottleneck of this
-            // kernel: 128 ex2 per thread and block take as long as the two MMAs they overlap with).
-            const uint64_t c2 = pack2(c, c), nmc2 = pack2(-row_m * c, -row_m * c);
-            uint64_t sum2a = pack2(0.f, 0.f), sum2b = sum2a;
-#pragma unroll
-            for (int q = 0; q < 2; q++) {
-                uint32_t pk[32];
-#pragma unroll
-                for (int e = 0; e < 32; e++) {                     // pair e of this half: scores 2e, 2e+1 of chunk 2q + e/16
-                    const int ch = 2 * q + (e >> 4), ee = (e & 15) * 2;
-                    const uint64_t x2 = fma2(pack2u(s[ch][ee], s[ch][ee + 1]), c2, nmc2);
-                    uint64_t p2;
-                    if ((e & 7) >= 8 - POLY_PAIRS) {
-                        p2 = ex2_poly2(x2);
-                    } else {
-                        float x0, x1;
-                        unpack2(x2, x0, x1);
-                        p2 = pack2(ex2(x0), ex2(x1));
-                    }
-                    if (e & 1) sum2b = add2(sum2b, p2); else sum2a = add2(sum2a, p2);
-                    float p0, p1;
-                    unpack2(p2, p0, p1);
-                    pk[e] = pack16<DT_F16>(p0, p1);
-                }
-                tmem_st32(tS + 32u * q, pk);                       // P: key pair (2c, 2c+1) in column c
-            }
-            float sum0, sum1, sum2, sum3;
-            unpack2(sum2a, sum0, sum1);
-            unpack2(sum2b, sum2, sum3);
-            sum0 += sum2; sum1 += sum3;
-            row_l += sum0 + sum1;
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAR_PFULL + i));
-        }
-        if (ok && nb > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), 0u, abort_flag));
-            tc_fence_after();
-        }
-#ifdef KB_DEBUG
-        if (p.dbg && ok && nb > 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-            float* d = p.dbg + 32768 + (size_t)i * 16384 + (size_t)(tid & 127) * 128;
-            for (int q = 0; q < 4; q++) {
-                uint32_t o[32];
-                tmem_ld32(tO + 32u * q, o);
+                for (int q = 0; q < 4; q++) tmem_ld32(tS + 32u * q, s[q]);
                 tmem_wait_ld();
-                reg_fence32(o);
-                for (int e = 0; e < 32; e++) d[q * 32 + e] = __uint_as_float(o[e]);
-            }
-            p.dbg[65536 + i * 256 + (tid & 127)] = row_m;
-            p.dbg[65536 + i * 256 + 128 + (tid & 127)] = row_l;
-        }
-#endif
-        // -------------------------------------------------------------------- epilogue (softmax warps)
-        if (MODE == MODE_PAIR) {
-            // Make `ok` uniform over the stream's four warps before any barrier that only they take part in:
-            // this barrier is reached unconditionally, so a warp that gave up cannot leave the others waiting.
-            if (nblk[warp >> 2] > 0) {
-                if (lane == 0) warp_ok[warp] = ok ? 1u : 0u;
-                named_bar_sync(3 + (warp >> 2), 128);
-                const int w0 = warp & 4;
-                ok = (warp_ok[w0] & warp_ok[w0 + 1] & warp_ok[w0 + 2] & warp_ok[w0 + 3]) != 0u;
-            }
-            if (ok && nblk[warp >> 2] > 0) {
-                const int i = warp >> 2;
-                const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-                const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(i * 128);
-                const float mc = row_m * p.scale_log2;
-                float scale = 1.f, l = row_l;
-                if (p.npad[0]) {                                         // engine/src/tcflash.cuh:140-144
-                    const float mn = fmaxf(mc, 0.f);
-                    scale = exp2f(mc - mn);
-                    l = l * scale + (float)p.npad[0] * exp2f(-mn);
+#pragma unroll
+                for (int q = 0; q < 4; q++) reg_fence32(s[q]);
+                if (j == nb - 1 && (Tk & (BN - 1))) {              // ragged last block: keys >= Tk score -inf
+                    const int valid = Tk - j * BN;
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+#pragma unroll
+                        for (int e = 0; e < 32; e++)
+                            if (q * 32 + e >= valid) s[q][e] = 0xff800000u;
                 }
-                const float inv = scale / l;
-                const int t = tid & 127;
-                if constexpr (sizeof(OutT) == 2) {
-                    // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream has
-                    // completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
-                    constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
-                    uint8_t* const stage = smem + i * TILE_BYTES;
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        uint32_t o[32];
-                        tmem_ld32(tO + 32u * q, o);
-                        tmem_wait_ld();
-                        reg_fence32(o);
-#pragma unroll
-                        for (int c = 0; c < 4; c++) {                    // 16-byte chunk 4q + c of the row, XOR-swizzled against bank conflicts
-                            uint4 pk;
-                            pk.x = pack16<ODT>(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
-                            pk.y = pack16<ODT>(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
-                            pk.z = pack16<ODT>(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
-                            pk.w = pack16<ODT>(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
-                            *reinterpret_cast<uint4*>(stage + t * 256 + (((4 * q + c) ^ (t & 15)) << 4)) = pk;
-                        }
-                    }
-                    named_bar_sync(3 + i, 128);                          // this stream's four warps
-                    const int np = p.n_peers > 0 ? p.n_peers : 1;
-                    const int wq = warp & 3;
-                    for (int rr = 0; rr < 32; rr++) {
-                        const int lr = 32 * wq + rr, row = q0 + i * BM + lr;
-                        if (row >= p.Tq) break;                          // warp-uniform
-                        const uint2 val = *reinterpret_cast<const uint2*>(stage + lr * 256 + (((lane >> 1) ^ (lr & 15)) << 4) + (lane & 1) * 8);
-                        const size_t off = ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)(p.col0 + h * HD) + (size_t)lane * 4;
-                        for (int pe = 0; pe < np; pe++) {
-                            OutT* base_out = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out);
-                            *reinterpret_cast<uint2*>(base_out + off) = val;
-                        }
-                    }
-                    if (p.n_peers > 0) {
-                        __threadfence_system();                          // the tile is visible to every GPU before the arrival
-                        named_bar_sync(3 + i, 128);
-                        if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
-                    }
+                for (int e = 0; e < 32; e += 2) {                  // 3-input max: two scores per instruction
+                    mx0 = max3(mx0, __uint_as_float(s[0][e]), __uint_as_float(s[0][e + 1]));
+                    mx1 = max3(mx1, __uint_as_float(s[1][e]), __uint_as_float(s[1][e + 1]));
+                    mx2 = max3(mx2, __uint_as_float(s[2][e]), __uint_as_float(s[2][e + 1]));
+                    mx3 = max3(mx3, __uint_as_float(s[3][e]), __uint_as_float(s[3][e + 1]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                if (j == 0) {
+                    row_m = mx;
                 } else {
-                    const int row = q0 + i * BM + t;
-                    OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD;
+                    // Keep a stale maximum while the new one is less than 2^8 above it: P stays <= 256, which
+                    // fp16 and the fp32 sums hold exactly as well, and O needs no rescale.
+                    const bool need = (mx - row_m) * c > 8.f;
+                    if (__any_sync(0xffffffffu, need)) {
+                        const float mn = fmaxf(row_m, mx);
+                        const float a = ex2((row_m - mn) * c);
+                        row_l *= a;
+                        row_m = mn;
+                        // The commit that completed S_i(j) was issued after PV_i(j-1), so O_i is quiescent here.
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        uint32_t o[32];
-                        float v[32];
-                        tmem_ld32(tO + 32u * q, o);
+                        for (int q = 0; q < 4; q++) {
+                            uint32_t o[32];
+                            tmem_ld32(tO + 32u * q, o);
+                            tmem_wait_ld();
+                            reg_fence32(o);
+#pragma unroll
+                            for (int e = 0; e < 32; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * a);
+                            tmem_st32(tO + 32u * q, o);
+                        }
+                    }
+                }
+                // p = 2^(s*c - m*c) on packed pairs: one FFMA2 per two scores, then MUFU ex2 (and the FMA-pipe
+                // polynomial for POLY_PAIRS of every 8 pairs, when enabled).
+                const uint64_t c2 = pack2(c, c), nmc2 = pack2(-row_m * c, -row_m * c);
+                uint64_t sum2a = pack2(0.f, 0.f), sum2b = sum2a;
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {                 // pair e of this half: scores 2e, 2e+1 of chunk 2q + e/16
+                        const int ch = 2 * q + (e >> 4), ee = (e & 15) * 2;
+                        const uint64_t x2 = fma2(pack2u(s[ch][ee], s[ch][ee + 1]), c2, nmc2);
+                        uint64_t p2;
+                        if ((e & 7) >= 8 - POLY_PAIRS) {
+                            p2 = ex2_poly2(x2);
+                        } else {
+                            float x0, x1;
+                            unpack2(x2, x0, x1);
+                            p2 = pack2(ex2(x0), ex2(x1));
+                        }
+                        if (e & 1) sum2b = add2(sum2b, p2); else sum2a = add2(sum2a, p2);
+                        float p0, p1;
+                        unpack2(p2, p0, p1);
+                        pk[e] = pack16<DT_F16>(p0, p1);
+                    }
+                    tmem_st32(tS + 32u * q, pk);                   // P: key pair (2c, 2c+1) in column c
+                }
+                float sum0, sum1, sum2, sum3;
+                unpack2(sum2a, sum0, sum1);
+                unpack2(sum2b, sum2, sum3);
+                row_l += (sum0 + sum2) + (sum1 + sum3);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_PFULL + i));
+            }
+            if (ok && nb > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), od_cnt & 1u, abort_flag));
+                tc_fence_after();
+            }
+            if (nb > 0) ++od_cnt;
+
+            // ---------------------------------------------------------------- epilogue of the item
+            if (MODE == MODE_PAIR) {
+                if (nb > 0) {
+                    // Make `ok` uniform over the stream's four warps before barriers only they take part in; this
+                    // barrier is reached unconditionally, so a warp that gave up cannot leave the others waiting.
+                    if (lane == 0) warp_ok[warp] = ok ? 1u : 0u;
+                    named_bar_sync(3 + i, 128);
+                    const int w0 = warp & 4;
+                    ok = (warp_ok[w0] & warp_ok[w0 + 1] & warp_ok[w0 + 2] & warp_ok[w0 + 3]) != 0u;
+                    if (ok) {
+                        const float mc = row_m * p.scale_log2;
+                        float scale = 1.f, l = row_l;
+                        if (p.npad[0]) {                                     // engine/src/tcflash.cuh:140-144
+                            const float mn = fmaxf(mc, 0.f);
+                            scale = exp2f(mc - mn);
+                            l = l * scale + (float)p.npad[0] * exp2f(-mn);
+                        }
+                        const float inv = scale / l;
+                        if constexpr (sizeof(OutT) == 2) {
+                            // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream
+                            // has completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
+                            constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+                            uint8_t* const stage = smem + i * TILE_BYTES;
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                uint32_t o[32];
+                                tmem_ld32(tO + 32u * q, o);
+                                tmem_wait_ld();
+                                reg_fence32(o);
+#pragma unroll
+                                for (int cc = 0; cc < 4; cc++) {             // 16-byte chunk 4q + cc of the row, XOR-swizzled against bank conflicts
+                                    uint4 pk;
+                                    pk.x = pack16<ODT>(__uint_as_float(o[8 * cc + 0]) * inv, __uint_as_float(o[8 * cc + 1]) * inv);
+                                    pk.y = pack16<ODT>(__uint_as_float(o[8 * cc + 2]) * inv, __uint_as_float(o[8 * cc + 3]) * inv);
+                                    pk.z = pack16<ODT>(__uint_as_float(o[8 * cc + 4]) * inv, __uint_as_float(o[8 * cc + 5]) * inv);
+                                    pk.w = pack16<ODT>(__uint_as_float(o[8 * cc + 6]) * inv, __uint_as_float(o[8 * cc + 7]) * inv);
+                                    *reinterpret_cast<uint4*>(stage + t * 256 + (((4 * q + cc) ^ (t & 15)) << 4)) = pk;
+                                }
+                            }
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next item's P*V may start
+                            named_bar_sync(3 + i, 128);                      // the staged tile is complete
+                            const int np = p.n_peers > 0 ? p.n_peers : 1;
+                            const int wq = warp & 3;
+                            for (int rr = 0; rr < 32; rr++) {
+                                const int lr = 32 * wq + rr, row = it.q0 + i * BM + lr;
+                                if (row >= p.Tq) break;                      // warp-uniform
+                                const uint2 val = *reinterpret_cast<const uint2*>(stage + lr * 256 + (((lane >> 1) ^ (lr & 15)) << 4) + (lane & 1) * 8);
+                                const size_t off = ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                                for (int pe = 0; pe < np; pe++) {
+                                    OutT* base_out = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out);
+                                    *reinterpret_cast<uint2*>(base_out + off) = val;
+                                }
+                            }
+                            if (p.n_peers > 0) __threadfence_system();       // the tile is visible to every GPU before the arrival
+                            named_bar_sync(3 + i, 128);                      // every warp is done with the staging tile
+                            if (p.n_peers > 0 && t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
+                        } else {
+                            const int row = it.q0 + i * BM + t;
+                            OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)it.h * HD;
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                uint32_t o[32];
+                                float v[32];
+                                tmem_ld32(tO + 32u * q, o);
+                                tmem_wait_ld();
+                                reg_fence32(o);
+#pragma unroll
+                                for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
+                                if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                            }
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
+                        }
+                        // the Q tile (and the staging space in it) may be overwritten by the next item's Q
+                        if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
+                    }
+                }
+            } else {
+                // NAG combine (engine/src/dit.cu:295-324) on Z+ = O0/l0 and Z- = O1/l1 straight from TMEM.
+                float* const f_inv = fbuf;             // [2][128]  1/l per stream
+                float* const f_part = fbuf + 256;      // [2 column halves][2 norms][128]; later [2 norms][128] totals
+                const int wg = i;                      // warpgroup 0 also finishes |Z+|_1, warpgroup 1 |g|_1
+                const uint32_t tOp = tmem_base + lane_base + 256u + (uint32_t)(wg * 64);
+                const uint32_t tOn = tmem_base + lane_base + 384u + (uint32_t)(wg * 64);
+                const float s = p.nag_s, sm1 = p.nag_s - 1.f;
+                {
+                    const float mc = row_m * p.scale_log2;
+                    float scale = 1.f, l = row_l;
+                    if (p.npad[wg]) {
+                        const float mn = fmaxf(mc, 0.f);
+                        scale = exp2f(mc - mn);
+                        l = l * scale + (float)p.npad[wg] * exp2f(-mn);
+                    }
+                    f_inv[wg * 128 + t] = scale / l;
+                }
+                if (lane == 0) warp_ok[warp] = ok ? 1u : 0u;
+                tc_fence_before();
+                named_bar_sync(1, 256);                                   // both streams' O and 1/l are final
+                ok = (warp_ok[0] & warp_ok[1] & warp_ok[2] & warp_ok[3] & warp_ok[4] & warp_ok[5] & warp_ok[6] & warp_ok[7]) != 0u;
+                if (t == 0 && wg == 0 && ok) mbar_arrive(bar(BAR_QEMPTY + 0));   // every S MMA of the item has completed
+                const float ip = f_inv[t], in = f_inv[128 + t];
+                float lp = 0.f, lg = 0.f;
+                // warpgroup wg takes head columns [64 wg, 64 wg + 64) of both outputs
+                if (ok) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int q = 0; q < 2; q++) {
+                        uint32_t a[32], n[32];
+                        tmem_ld32(tOp + 32u * q, a);
+                        tmem_ld32(tOn + 32u * q, n);
                         tmem_wait_ld();
-                        reg_fence32(o);
+                        reg_fence32(a);
+                        reg_fence32(n);
 #pragma unroll
-                        for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
+                        for (int e = 0; e < 32; e++) {
+                            const float pv = __uint_as_float(a[e]) * ip;
+                            const float nv = __uint_as_float(n[e]) * in;
+                            lp += fabsf(pv);
+                            lg += fabsf(pv * s - nv * sm1);
+                        }
+                    }
+                }
+                f_part[(wg * 2 + 0) * 128 + t] = lp;
+                f_part[(wg * 2 + 1) * 128 + t] = lg;
+                named_bar_sync(1, 256);
+                // publish this head's norms: warpgroup 0 writes |Z+|_1, warpgroup 1 writes |g|_1 (fixed order: deterministic)
+                float* const gpart = p.nag_part + ((size_t)it.qt * p.H) * 256;   // [H][2][128] of this query tile
+                gpart[(size_t)it.h * 256 + wg * 128 + t] = f_part[(0 * 2 + wg) * 128 + t] + f_part[(1 * 2 + wg) * 128 + t];
+                __threadfence();
+                named_bar_sync(1, 256);
+                if (tid == 0) {
+                    // arrive, then wait (bounded) for the other heads of this query tile: they are adjacent work items
+                    // and therefore in flight on other SMs now (the launch is cooperative: all CTAs are resident)
+                    atomicAdd(p.nag_flag + it.qt, 1u);
+                    const uint64_t t0 = globaltimer_ns();
+                    uint32_t seen = 0;
+                    for (;;) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
+                        if (seen >= (uint32_t)p.H || *abort_flag) break;
+                        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
+                        __nanosleep(64);
+                    }
+                    wg_stop[0] = (seen >= (uint32_t)p.H) ? 0u : 1u;
+                }
+                named_bar_sync(1, 256);
+                const bool all_here = wg_stop[0] == 0u;
+                float tot = 0.f;
+                if (all_here)
+                    for (int hh = 0; hh < p.H; hh++) tot += __ldcg(gpart + (size_t)hh * 256 + wg * 128 + t);   // head order: same sum everywhere
+                f_part[wg * 128 + t] = tot;                                 // [2 norms][128] (the column-half partials were consumed above)
+                named_bar_sync(1, 256);
+                const float ratio = f_part[128 + t] / fmaxf(f_part[t], 1e-12f);
+                const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
+                const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
+                const int row = it.q0 + t;
+                OutT* dst = reinterpret_cast<OutT*>(p.out) + (size_t)row * (size_t)p.ldo + (size_t)it.h * HD + wg * 64;
+                if (ok && all_here) {
+#pragma unroll
+                    for (int q = 0; q < 2; q++) {
+                        uint32_t a[32], n[32];
+                        float v[32];
+                        tmem_ld32(tOp + 32u * q, a);
+                        tmem_ld32(tOn + 32u * q, n);
+                        tmem_wait_ld();
+                        reg_fence32(a);
+                        reg_fence32(n);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) {
+                            const float pv = __uint_as_float(a[e]) * ip;
+                            const float nv = __uint_as_float(n[e]) * in;
+                            v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                        }
                         if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
                     }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
                 }
             }
-            tc_fence_before();
-            cta_sync();
-        } else {
-            // NAG combine (engine/src/dit.cu:295-324) on Z+ = O0/l0 and Z- = O1/l1 without leaving the chip.
-            float* const f_inv = fbuf;             // [2][128]  1/l per stream
-            float* const f_part = fbuf + 256;      // [2 column halves][2 norms][128]
-            float* const f_hsum = fbuf + 768;      // [2 norms][128]  this head's |Z+|_1 and |g|_1
-            const int t = tid & 127, w = warp >> 2;
-            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-            const uint32_t tOp = tmem_base + lane_base + 256u + (uint32_t)(w * 64);
-            const uint32_t tOn = tmem_base + lane_base + 384u + (uint32_t)(w * 64);
-            const float s = p.nag_s, sm1 = p.nag_s - 1.f;
-            {
-                const float mc = row_m * p.scale_log2;
-                float scale = 1.f, l = row_l;
-                if (p.npad[w]) {
-                    const float mn = fmaxf(mc, 0.f);
-                    scale = exp2f(mc - mn);
-                    l = l * scale + (float)p.npad[w] * exp2f(-mn);
-                }
-                f_inv[w * 128 + t] = scale / l;
-            }
-            tc_fence_before();
-            named_bar_sync(1, 256);                                       // both streams' O and 1/l are final
-            const float ip = f_inv[t], in = f_inv[128 + t];
-            float lp = 0.f, lg = 0.f;
-            // warpgroup w takes head columns [64w, 64w+64) of both outputs
-            if (__all_sync(0xffffffffu, ok)) {
-                tc_fence_after();
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    uint32_t a[32], n[32];
-                    tmem_ld32(tOp + 32u * q, a);
-                    tmem_ld32(tOn + 32u * q, n);
-                    tmem_wait_ld();
-                    reg_fence32(a);
-                    reg_fence32(n);
-#pragma unroll
-                    for (int e = 0; e < 32; e++) {
-                        const float pv = __uint_as_float(a[e]) * ip;
-                        const float nv = __uint_as_float(n[e]) * in;
-                        lp += fabsf(pv);
-                        lg += fabsf(pv * s - nv * sm1);
-                    }
-                }
-            }
-            f_part[(w * 2 + 0) * 128 + t] = lp;
-            f_part[(w * 2 + 1) * 128 + t] = lg;
-            named_bar_sync(1, 256);
-            // warpgroup 0 finishes |Z+|_1, warpgroup 1 finishes |g|_1 (fixed order: deterministic)
-            f_hsum[w * 128 + t] = f_part[(0 * 2 + w) * 128 + t] + f_part[(1 * 2 + w) * 128 + t];
-            cta_sync();
-            cluster_arrive();
-            cluster_wait();
-            float tot = 0.f;
-            {
-                const uint32_t nrank = cluster_nctarank();
-                const uint32_t my = smem_u32(&f_hsum[w * 128 + t]);
-                for (uint32_t r = 0; r < nrank; r++) tot += dsmem_ld_f32(my, r);   // rank order: same sum in every CTA
-            }
-            cluster_arrive();                                             // our reads of the peers are done
-            float* const f_tot = f_part;                                  // reuse: [2 norms][128]
-            f_tot[w * 128 + t] = tot;
-            named_bar_sync(1, 256);
-            const float ratio = f_tot[128 + t] / fmaxf(f_tot[t], 1e-12f);
-            const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
-            const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
-            const int row = q0 + t;
-            OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)h * HD + w * 64;
-            if (__all_sync(0xffffffffu, ok)) {
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    uint32_t a[32], n[32];
-                    float v[32];
-                    tmem_ld32(tOp + 32u * q, a);
-                    tmem_ld32(tOn + 32u * q, n);
-                    tmem_wait_ld();
-                    reg_fence32(a);
-                    reg_fence32(n);
-#pragma unroll
-                    for (int e = 0; e < 32; e++) {
-                        const float pv = __uint_as_float(a[e]) * ip;
-                        const float nv = __uint_as_float(n[e]) * in;
-                        v[e] = ag * (pv * s - nv * sm1) + ap * pv;
-                    }
-                    if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
-                }
-            }
-            tc_fence_before();
-            cta_sync();
-            cluster_wait();                                               // peers are done reading our f_hsum
-        }
-    } else {
-        setmaxnreg_dec<56>();
-        if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issue (one lane)
-        if (lane == 0) {
-            // Operands are fp16 throughout (bf16/fp32 inputs are staged as fp16 by the pre-pass): with bf16
-            // P the 2^-9 rounding of each weight alone costs ~1e-3 relative error on outputs that are sums
-            // of random-sign terms, and tcgen05 does not take an fp16 A with a bf16 B.
-            constexpr uint32_t IDESC_S = idesc_f16(0, 0, 0, 0, BM, BN);   // S = Q K^T, both K-major
-            constexpr uint32_t IDESC_PV = idesc_f16(0, 0, 0, 1, BM, HD);  // O += P V, V is MN-major (rows = keys)
-            uint32_t n = 0;                                              // ring slot being consumed
-            bool good = true;
-            auto kv_wait = [&](uint32_t idx) { return mbar_wait(bar(BAR_KVFULL + idx % NSTAGE), (idx / NSTAGE) & 1u, abort_flag); };
-            auto kv_addr = [&](uint32_t idx) { return sKV + (idx % NSTAGE) * TILE_BYTES; };
-            auto kv_release = [&](uint32_t idx) { tc_commit(bar(BAR_KVEMPTY + idx % NSTAGE)); };
-            auto issue_S = [&](int i, uint32_t k_saddr) {
-                const uint32_t q_saddr = sQ + (MODE == MODE_NAG ? 0 : i) * TILE_BYTES;
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    const uint32_t off = (uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u;
-                    mma_ss(tmem_base + (uint32_t)(i * 128), smem_desc_sw128(q_saddr + off, 16, 1024),
-                           smem_desc_sw128(k_saddr + off, 16, 1024), IDESC_S, kk > 0);
-                }
-                tc_commit(bar(BAR_SFULL + i));
-            };
-            auto issue_PV = [&](int i, uint32_t v_saddr, int j, int Tk) {
-                const int valid = min(BN, Tk - j * BN);
-                const int nkk = (valid + 15) >> 4;                       // 16 keys per MMA; P is 0 past `valid`
-                for (int kk = 0; kk < nkk; kk++)
-                    mma_ts(tmem_base + 256u + (uint32_t)(i * 128), tmem_base + (uint32_t)(i * 128) + (uint32_t)(kk * 8),
-                           smem_desc_sw128(v_saddr + (uint32_t)kk * 2048u, HALF_BYTES, 1024), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-            };
+            // leave the item loop together once any role has given up (uniform per warpgroup; in NAG mode per CTA)
             if (MODE == MODE_PAIR) {
-                const int nb = nblk[0];
-                const bool two = nblk[1] > 0;
-                good = mbar_wait(bar(BAR_QFULL + 0), 0u, abort_flag) && kv_wait(n);
-                if (good) {
-                    issue_S(0, kv_addr(n));
-                    if (two) {
-                        good = mbar_wait(bar(BAR_QFULL + 1), 0u, abort_flag);
-                        if (good) issue_S(1, kv_addr(n));
-                    }
-                    kv_release(n);
-                    ++n;
-                }
-                for (int j = 0; j < nb && good; ++j) {
-                    const uint32_t nv = n, nk = n + 1;
-                    const bool more = j + 1 < nb;
-                    good = kv_wait(nv) && mbar_wait(bar(BAR_PFULL + 0), (uint32_t)(j & 1), abort_flag);
-                    if (!good) break;
-                    tc_fence_after();
-                    issue_PV(0, kv_addr(nv), j, p.Tk[0]);
-                    if (!more) tc_commit(bar(BAR_ODONE + 0));
-                    if (more) {
-                        good = kv_wait(nk);
-                        if (!good) break;
-                        issue_S(0, kv_addr(nk));
-                    }
-                    if (two) {
-                        good = mbar_wait(bar(BAR_PFULL + 1), (uint32_t)(j & 1), abort_flag);
-                        if (!good) break;
-                        tc_fence_after();
-                        issue_PV(1, kv_addr(nv), j, p.Tk[0]);
-                        if (!more) tc_commit(bar(BAR_ODONE + 1));
-                    }
-                    kv_release(nv);
-                    ++n;
-                    if (more) {
-                        if (two) issue_S(1, kv_addr(nk));
-                        kv_release(nk);
-                        ++n;
-                    }
-                }
+                if (t == 0) wg_stop[i] = *abort_flag;
+                named_bar_sync(3 + i, 128);
+                const bool stop = wg_stop[i] != 0u;
+                named_bar_sync(3 + i, 128);
+                if (stop) break;
             } else {
-                good = mbar_wait(bar(BAR_QFULL + 0), 0u, abort_flag);
-                for (int i = 0; i < 2 && good; i++) {
-                    good = kv_wait(n);
-                    if (good) { issue_S(i, kv_addr(n)); kv_release(n); ++n; }
-                }
-                const int nmax = max(nblk[0], nblk[1]);
-                for (int j = 0; j < nmax && good; ++j) {
-                    for (int i = 0; i < 2 && good; i++) {
-                        if (j >= nblk[i]) continue;
-                        good = kv_wait(n) && mbar_wait(bar(BAR_PFULL + i), (uint32_t)(j & 1), abort_flag);
+                named_bar_sync(1, 256);
+                if (tid == 0) wg_stop[1] = *abort_flag;
+                named_bar_sync(1, 256);
+                if (wg_stop[1] != 0u) break;
+            }
+        }
+        tc_fence_before();
+        cta_sync();
+    } else {
+        setmaxnreg_dec<88>();
+        if (warp == 8) {
+            // ------------------------------------------------------------------ MMA issue (one lane)
+            if (lane == 0) {
+                // Operands are fp16 throughout (bf16/fp32 inputs are staged as fp16 by the pre-pass): with bf16
+                // P the 2^-9 rounding of each weight alone costs ~1e-3 relative error on outputs that are sums
+                // of random-sign terms, and tcgen05 does not take an fp16 A with a bf16 B.
+                constexpr uint32_t IDESC_S = idesc_f16(0, 0, 0, 0, BM, BN);   // S = Q K^T, both K-major
+                constexpr uint32_t IDESC_PV = idesc_f16(0, 0, 0, 1, BM, HD);  // O += P V, V is MN-major (rows = keys)
+                uint32_t ring = 0;                                            // ring slot being consumed (same order as the loader)
+                uint32_t qf_cnt[2] = {0, 0}, pf_cnt[2] = {0, 0}, of_cnt[2] = {0, 0};
+                bool good = true;
+                auto kv_wait = [&](uint32_t idx) { return mbar_wait(bar(BAR_KVFULL + idx % NSTAGE), (idx / NSTAGE) & 1u, abort_flag); };
+                auto kv_addr = [&](uint32_t idx) { return sKV + (idx % NSTAGE) * TILE_BYTES; };
+                auto kv_release = [&](uint32_t idx) { tc_commit(bar(BAR_KVEMPTY + idx % NSTAGE)); };
+                auto q_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_QFULL + i), qf_cnt[i] & 1u, abort_flag); ++qf_cnt[i]; return r; };
+                auto p_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_PFULL + i), pf_cnt[i] & 1u, abort_flag); ++pf_cnt[i]; tc_fence_after(); return r; };
+                // O_i (and, in NAG mode, both O) of the previous item has been read out; passes at once for the first item
+                auto o_free_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_OFREE + i), (of_cnt[i] & 1u) ^ 1u, abort_flag); ++of_cnt[i]; tc_fence_after(); return r; };
+                auto issue_S = [&](int i, uint32_t k_saddr) {
+                    const uint32_t q_saddr = sQ + (MODE == MODE_NAG ? 0 : i) * TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++) {
+                        const uint32_t off = (uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u;
+                        mma_ss(tmem_base + (uint32_t)(i * 128), smem_desc_sw128(q_saddr + off, 16, 1024),
+                               smem_desc_sw128(k_saddr + off, 16, 1024), IDESC_S, kk > 0);
+                    }
+                    tc_commit(bar(BAR_SFULL + i));
+                };
+                auto issue_PV = [&](int i, uint32_t v_saddr, int j, int Tk) {
+                    const int valid = min(BN, Tk - j * BN);
+                    const int nkk = (valid + 15) >> 4;                        // 16 keys per MMA; P is 0 past `valid`
+                    for (int kk = 0; kk < nkk; kk++)
+                        mma_ts(tmem_base + 256u + (uint32_t)(i * 128), tmem_base + (uint32_t)(i * 128) + (uint32_t)(kk * 8),
+                               smem_desc_sw128(v_saddr + (uint32_t)kk * 2048u, HALF_BYTES, 1024), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                };
+                for (int w = blockIdx.x; w < p.n_items && good; w += gridDim.x) {
+                    const Item it = decode_item<MODE>(w, p);
+                    if (MODE == MODE_PAIR) {
+                        const int nb = it.nblk[0];
+                        const bool two = it.nblk[1] > 0;
+                        good = q_wait(0) && kv_wait(ring);
                         if (!good) break;
-                        tc_fence_after();
-                        issue_PV(i, kv_addr(n), j, p.Tk[i]);
-                        if (j + 1 == nblk[i]) tc_commit(bar(BAR_ODONE + i));
-                        kv_release(n);
-                        ++n;
-                        if (j + 1 < nblk[i]) {
-                            good = kv_wait(n);
+                        issue_S(0, kv_addr(ring));
+                        if (two) {
+                            good = q_wait(1);
                             if (!good) break;
-                            issue_S(i, kv_addr(n));
-                            kv_release(n);
-                            ++n;
+                            issue_S(1, kv_addr(ring));
+                        }
+                        kv_release(ring);
+                        ++ring;
+                        for (int j = 0; j < nb && good; ++j) {
+                            const uint32_t nv = ring, nk = ring + 1;
+                            const bool more = j + 1 < nb;
+                            good = kv_wait(nv) && (j > 0 || o_free_wait(0)) && p_wait(0);
+                            if (!good) break;
+                            issue_PV(0, kv_addr(nv), j, p.Tk[0]);
+                            if (!more) tc_commit(bar(BAR_ODONE + 0));
+                            if (more) {
+                                good = kv_wait(nk);
+                                if (!good) break;
+                                issue_S(0, kv_addr(nk));
+                            }
+                            if (two) {
+                                good = (j > 0 || o_free_wait(1)) && p_wait(1);
+                                if (!good) break;
+                                issue_PV(1, kv_addr(nv), j, p.Tk[0]);
+                                if (!more) tc_commit(bar(BAR_ODONE + 1));
+                            }
+                            kv_release(nv);
+                            ++ring;
+                            if (more) {
+                                if (two) issue_S(1, kv_addr(nk));
+                                kv_release(nk);
+                                ++ring;
+                            }
+                        }
+                    } else {
+                        good = q_wait(0);
+                        for (int i = 0; i < 2 && good; i++) {
+                            good = kv_wait(ring);
+                            if (good) { issue_S(i, kv_addr(ring)); kv_release(ring); ++ring; }
+                        }
+                        const int nmax = max(it.nblk[0], it.nblk[1]);
+                        for (int j = 0; j < nmax && good; ++j) {
+                            for (int i = 0; i < 2 && good; i++) {
+                                if (j >= it.nblk[i]) continue;
+                                good = kv_wait(ring) && (j > 0 || o_free_wait(i)) && p_wait(i);
+                                if (!good) break;
+                                issue_PV(i, kv_addr(ring), j, p.Tk[i]);
+                                if (j + 1 == it.nblk[i]) tc_commit(bar(BAR_ODONE + i));
+                                kv_release(ring);
+                                ++ring;
+                                if (j + 1 < it.nblk[i]) {
+                                    good = kv_wait(ring);
+                                    if (!good) break;
+                                    issue_S(i, kv_addr(ring));
+                                    kv_release(ring);
+                                    ++ring;
+                                }
+                            }
                         }
                     }
                 }
             }
-        }
-        __syncwarp();
+            __syncwarp();
         } else if (warp == 9) {
-        // ------------------------------------------------------------------ TMA loads (one lane)
-        if (lane == 0) {
-            uint32_t n = 0;
-            bool good = true;
-            // one 128x128 tile = two 64-column boxes, each landing as a 128-byte-swizzled [128][64] half
-            auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0, int bb) {
-                tma_load_3d(dst, tm, mbar, h * HD, row0, bb);
-                tma_load_3d(dst + HALF_BYTES, tm, mbar, h * HD + 64, row0, bb);
-            };
-            auto load_kv = [&](const CUtensorMap* tm, int row0) {
-                const uint32_t st = n % NSTAGE;
-                good = mbar_wait(bar(BAR_KVEMPTY + st), ((n / NSTAGE) & 1u) ^ 1u, abort_flag);
-                if (!good) return;
-                mbar_expect_tx(bar(BAR_KVFULL + st), TILE_BYTES);
-                load_tile(sKV + st * TILE_BYTES, tm, bar(BAR_KVFULL + st), row0, MODE == MODE_NAG ? 0 : b);
-                ++n;
-            };
-            mbar_expect_tx(bar(BAR_QFULL + 0), TILE_BYTES);
-            load_tile(sQ, &tmQ, bar(BAR_QFULL + 0), q0, b);
-            if (MODE == MODE_PAIR) {
-                const int nb = nblk[0];
-                if (nb > 0) load_kv(&tmK0, 0);
-                if (nblk[1] > 0) {
-                    mbar_expect_tx(bar(BAR_QFULL + 1), TILE_BYTES);
-                    load_tile(sQ + TILE_BYTES, &tmQ, bar(BAR_QFULL + 1), q0 + BM, b);
-                }
-                for (int j = 0; j < nb && good; ++j) {
-                    load_kv(&tmV0, j * BN);
-                    if (good && j + 1 < nb) load_kv(&tmK0, (j + 1) * BN);
-                }
-            } else {
-                if (nblk[0] > 0) load_kv(&tmK0, 0);
-                if (good && nblk[1] > 0) load_kv(&tmK1, 0);
-                const int nmax = max(nblk[0], nblk[1]);
-                for (int j = 0; j < nmax && good; ++j) {
-                    for (int i = 0; i < 2 && good; i++) {
-                        if (j >= nblk[i]) continue;
-                        load_kv(i ? &tmV1 : &tmV0, j * BN);
-                        if (good && j + 1 < nblk[i]) load_kv(i ? &tmK1 : &tmK0, (j + 1) * BN);
+            // ------------------------------------------------------------------ TMA loads (one lane)
+            if (lane == 0) {
+                uint32_t n = 0;
+                uint32_t qe_cnt[2] = {0, 0};
+                bool good = true;
+                Item it;
+                // one 128x128 tile = two 64-column boxes, each landing as a 128-byte-swizzled [128][64] half
+                auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0, int bb) {
+                    tma_load_3d(dst, tm, mbar, it.h * HD, row0, bb);
+                    tma_load_3d(dst + HALF_BYTES, tm, mbar, it.h * HD + 64, row0, bb);
+                };
+                auto load_q = [&](int i) {
+                    // the previous item's S MMAs (and its output staging in the same space) are done with this tile
+                    good = mbar_wait(bar(BAR_QEMPTY + i), (qe_cnt[i] & 1u) ^ 1u, abort_flag);
+                    ++qe_cnt[i];
+                    if (!good) return;
+                    mbar_expect_tx(bar(BAR_QFULL + i), TILE_BYTES);
+                    load_tile(sQ + i * TILE_BYTES, &tmQ, bar(BAR_QFULL + i), it.q0 + i * BM, it.b);
+                };
+                auto load_kv = [&](const CUtensorMap* tm, int row0) {
+                    const uint32_t st = n % NSTAGE;
+                    good = mbar_wait(bar(BAR_KVEMPTY + st), ((n / NSTAGE) & 1u) ^ 1u, abort_flag);
+                    if (!good) return;
+                    mbar_expect_tx(bar(BAR_KVFULL + st), TILE_BYTES);
+                    load_tile(sKV + st * TILE_BYTES, tm, bar(BAR_KVFULL + st), row0, MODE == MODE_NAG ? 0 : it.b);
+                    ++n;
+                };
+                for (int w = blockIdx.x; w < p.n_items && good; w += gridDim.x) {
+                    it = decode_item<MODE>(w, p);
+                    load_q(0);
+                    if (!good) break;
+                    if (MODE == MODE_PAIR) {
+                        const int nb = it.nblk[0];
+                        if (nb > 0) load_kv(&tmK0, 0);
+                        if (good && it.nblk[1] > 0) load_q(1);
+                        for (int j = 0; j < nb && good; ++j) {
+                            load_kv(&tmV0, j * BN);
+                            if (good && j + 1 < nb) load_kv(&tmK0, (j + 1) * BN);
+                        }
+                    } else {
+                        if (it.nblk[0] > 0) load_kv(&tmK0, 0);
+                        if (good && it.nblk[1] > 0) load_kv(&tmK1, 0);
+                        const int nmax = max(it.nblk[0], it.nblk[1]);
+                        for (int j = 0; j < nmax && good; ++j) {
+                            for (int i = 0; i < 2 && good; i++) {
+                                if (j >= it.nblk[i]) continue;
+                                load_kv(i ? &tmV1 : &tmV0, j * BN);
+                                if (good && j + 1 < it.nblk[i]) load_kv(i ? &tmK1 : &tmK0, (j + 1) * BN);
+                            }
+                        }
                     }
                 }
+                // on failure, let the copies already in flight land before the CTA's shared memory goes away
+                if (!good || *abort_flag) {
+                    const uint64_t t0 = globaltimer_ns();
+                    while (globaltimer_ns() - t0 < 20000ull) {}
+                }
             }
-            // on failure, let the copies already in flight land before the CTA's shared memory goes away
-            if (!good || *abort_flag) {
-                const uint64_t t0 = globaltimer_ns();
-                while (globaltimer_ns() - t0 < 20000ull) {}
-            }
+            __syncwarp();
         }
-        __syncwarp();
-    }
-
-        // the same full-CTA and cluster barriers the softmax branch runs
-        if (MODE == MODE_PAIR) {
-            cta_sync();
-        } else {
-            cta_sync();
-            cluster_arrive();
-            cluster_wait();
-            cluster_arrive();
-            cta_sync();
-            cluster_wait();
-        }
+        cta_sync();
         if (warp == 8) {
             if (lane == 0 && *abort_flag) atomicOr(p.status, ST_TIMEOUT);
             tc_fence_after();

@@ -310,7 +310,8 @@ def test_argument_errors(kb):
     assert L.kb_attn_self(P(t), P(t), P(t), P(t), None, None, None, None, 1, 256, 2, 256, 256, 256, 256, 1, 1, 1e-6, None, 0, None) == -4   # bf16 needs staging
     small = torch.empty(1024, dtype=torch.uint8, device="cuda")
     assert L.kb_attn_self(P(t), P(t), P(t), P(t), P(w), None, None, None, 1, 256, 2, 256, 256, 256, 256, 0, 0, 1e-6, P(small), 1024, None) == -4
-    assert L.kb_attn_nag(P(t), P(t), None, P(t), P(t), 10, 0, P(t), P(t), 10, 0, 5.0, 2.5, 0.25, 256, 3, 256, 256, 256, 0, 0, 1e-6, None, 0, None) == -3
+    assert L.kb_attn_nag(P(t), P(t), None, P(t), P(t), 10, 0, P(t), P(t), 10, 0, 5.0, 2.5, 0.25, 256, 65, 256, 256, 256, 0, 0, 1e-6, None, 0, None) == -3
+    assert L.kb_attn_nag(P(t), P(t), None, P(t), P(t), 10, 0, P(t), P(t), 10, 0, 5.0, 2.5, 0.25, 256, 2, 256, 256, 256, 0, 0, 1e-6, None, 0, None) == -4   # NAG always needs its scratch
     assert kb.check_status() == 0
     with pytest.raises(kb.KilnError):
         kb.attn_cross(t, t, t, t, 256, 0, 0, 2)
