@@ -313,14 +313,192 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------ per-config report
+def run_all_configs(args):
+    """BASELINE.json's five configurations on one GPU: time and accuracy of this library next to the reference's own
+    kernels (tfa::k_flash, k_rmsnorm_warp, k_rope_half, k_nag compiled for sm_100a into oracle/_ref/, when present) and
+    the CPU oracle on sampled query rows. One JSON line per case on stdout."""
+    import ctypes
+    import numpy as np
+    import torch
+    import kiln_b200 as kb
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    assert kb.lib().kb_init() == 0
+    dev = "cuda"
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libkiln_ref.so")
+    R = ctypes.CDLL(ref_path) if os.path.exists(ref_path) else None
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    cf = ctypes.c_float
+    sustained, burst, hbm, src = read_peaks()
+    NSET = 6                                                    # rotating input sets: more than L2 for every case below
+
+    def seeded(seed, rows, kind):
+        return oracle.round16(oracle.randn(seed, rows * D), kind).reshape(rows, D)
+
+    def timed(fn, reps=20, warm=3):
+        for i in range(warm):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3                 # us
+
+    def errs(out, ref):
+        d = np.abs(out.astype(np.float64) - ref.astype(np.float64))
+        return {"max_abs": float(d.max()), "mean_rel": float(d.sum() / np.abs(ref).sum()),
+                "rel_l2": float(np.sqrt((d * d).sum() / (ref.astype(np.float64) ** 2).sum()))}
+
+    def rows_sample(Tq, n=48):
+        return np.array(sorted(set([0, 127, 128, Tq - 1] + list(np.random.RandomState(0).randint(0, Tq, n)))), np.int64)
+
+    def emit(rec):
+        print(json.dumps(rec), flush=True)
+
+    def attention_case(name, kind, Tq, Tk_rows, Tk, npad, flop):
+        dt = torch.float16 if kind == 0 else torch.bfloat16
+        q, k, v = seeded(1, Tq, kind), seeded(2, Tk_rows, kind), seeded(3, Tk_rows, kind)
+        sets = [tuple(torch.from_numpy(a).to(dev).to(dt).clone() for a in (q, k, v)) for _ in range(NSET)]
+        out = torch.empty(Tq, D, device=dev, dtype=dt)
+        ws = torch.empty(max(16, kb.workspace_bytes(Tq, Tk_rows, H, dt)), dtype=torch.uint8, device=dev)
+        us = timed(lambda i: kb.attn_cross(out, *sets[i % NSET], Tq, Tk, npad, H, workspace=ws))
+        # kernel-only time from the library's per-launch event pairs: short kernels are otherwise hidden behind the
+        # host cost of a Python/ctypes call (argument marshalling + three tensor-map encodes), which a C++ caller does not pay
+        kb.prof_enable(True)
+        for i in range(10):
+            kb.attn_cross(out, *sets[i % NSET], Tq, Tk, npad, H, workspace=ws)
+        k_ms, k_n = kb.prof_read(kb.PROF_ATTENTION)
+        s_ms, s_n = kb.prof_read(kb.PROF_NORM_ROPE)
+        kb.prof_enable(False)
+        out32 = torch.empty(Tq, D, device=dev, dtype=torch.float32)
+        kb.attn_cross(out32, *sets[0], Tq, Tk, npad, H, workspace=ws)
+        assert kb.check_status() == 0
+        rows = rows_sample(Tq)
+        ref = oracle.attention(q[rows], k[:Tk], v[:Tk], H, npad)
+        rec = {"case": name, "dtype": "f16" if kind == 0 else "bf16", "Tq": Tq, "Tk": Tk, "npad": npad, "ours_us": us,
+               "ours_kernel_us": k_ms / k_n * 1e3, "ours_staging_us": (s_ms / s_n * 1e3) if s_n else 0.0,
+               "ours_tflops": flop / us / 1e6, "frac_of_burst_peak": flop / us / 1e6 / burst,
+               "hbm_gbs": (2 * Tq + 2 * Tk) * D * 2 / us / 1e3, "err_fp32_out": errs(out32.cpu().numpy()[rows], ref),
+               "err_16bit_out": errs(out.float().cpu().numpy()[rows], ref)}
+        if R is not None:
+            f32 = [tuple(t.float() for t in st) for st in sets[:2]]
+            o16 = torch.empty(Tq, D, device=dev, dtype=torch.float16)
+            rus = timed(lambda i: R.kref_tfa_f16(P(o16), D, P(f32[i % 2][0]), D, P(f32[i % 2][1]), D, P(f32[i % 2][2]), D, Tq, Tk, H, npad), reps=10)
+            rec.update({"reference_tfa_us": rus, "reference_tfa_tflops": flop / rus / 1e6, "speedup_vs_reference_kernel": rus / us,
+                        "reference_tfa_err": errs(o16.float().cpu().numpy()[rows], ref)})
+        emit(rec)
+
+    # config 1: self-attention fp16, 1536 tokens
+    attention_case("cfg1 self 1536 fp16", 0, 1536, 1536, 1536, 0, 4.0 * 1536 * 1536 * 128 * H)
+    # config 2: cross-attention fp16, L = 512 padded context: reference semantics (npad = L - valid) and -inf masking (npad = 0)
+    draw = int(np.random.RandomState(2).randint(16, 513))
+    for valid in (16, 26, 77, 256, 512, draw):
+        attention_case(f"cfg2 cross valid={valid} zero-key padding (reference)", 0, 1536, 512, valid, 512 - valid, 4.0 * 1536 * valid * 128 * H)
+        if valid < 512:
+            attention_case(f"cfg2 cross valid={valid} masked padding", 0, 1536, 512, valid, 0, 4.0 * 1536 * valid * 128 * H)
+    # config 3: NAG fp16, two contexts with independent seeded valid lengths, s = 5 (reference default) and s = 6 (BASELINE literal)
+    rs = np.random.RandomState(3)
+    vp_len, vn_len = int(rs.randint(16, 513)), int(rs.randint(16, 513))
+    Tq = 1536
+    q = seeded(7, Tq, 0)
+    ctx = [seeded(sd, 512, 0) for sd in (8, 9, 10, 11)]
+    dq = torch.from_numpy(q).to(dev).half()
+    dctx = [torch.from_numpy(a).to(dev).half() for a in ctx]
+    ws = torch.empty(kb.workspace_bytes(Tq, 512, H, torch.float16, n_ctx=2), dtype=torch.uint8, device=dev)
+    rows = rows_sample(Tq)
+    zp = oracle.attention(q[rows], ctx[0][:vp_len], ctx[1][:vp_len], H, 512 - vp_len)
+    zn = oracle.attention(q[rows], ctx[2][:vn_len], ctx[3][:vn_len], H, 512 - vn_len)
+    for sc in (5.0, 6.0):
+        out = torch.empty(Tq, D, device=dev, dtype=torch.float16)
+        out32 = torch.empty(Tq, D, device=dev, dtype=torch.float32)
+        fn = lambda o: kb.attn_nag(o, dq, dctx[0], dctx[1], vp_len, 512 - vp_len, dctx[2], dctx[3], vn_len, 512 - vn_len, sc, 2.5, 0.25, Tq, H, workspace=ws)
+        us = timed(lambda i: fn(out))
+        fn(out32)
+        assert kb.check_status() == 0
+        ref = oracle.nag(zp, zn, sc, 2.5, 0.25)
+        flop = 4.0 * Tq * (vp_len + vn_len) * 128 * H
+        rec = {"case": f"cfg3 NAG s={sc} valid+={vp_len} valid-={vn_len}", "dtype": "f16", "ours_us": us, "ours_tflops": flop / us / 1e6,
+               "hbm_gbs": (2 * Tq + 2 * (vp_len + vn_len)) * D * 2 / us / 1e3, "err_fp32_out": errs(out32.cpu().numpy()[rows], ref),
+               "err_16bit_out": errs(out.float().cpu().numpy()[rows], ref)}
+        if R is not None:
+            qf, cf32 = dq.float(), [t.float() for t in dctx]
+            a16, n16 = torch.empty(Tq, D, device=dev, dtype=torch.float16), torch.empty(Tq, D, device=dev, dtype=torch.float16)
+            def ref_nag(i):
+                R.kref_tfa_f16(P(a16), D, P(qf), D, P(cf32[0]), D, P(cf32[1]), D, Tq, vp_len, H, 512 - vp_len)
+                R.kref_tfa_f16(P(n16), D, P(qf), D, P(cf32[2]), D, P(cf32[3]), D, Tq, vn_len, H, 512 - vn_len)
+                R.kref_nag_f16(P(a16), P(n16), Tq, D, cf(sc), cf(2.5), cf(0.25))
+            rus = timed(ref_nag, reps=10)
+            rec.update({"reference_unfused_us": rus, "speedup_vs_reference_kernels": rus / us, "reference_err": errs(a16.float().cpu().numpy()[rows], ref)})
+        emit(rec)
+    # config 4: full-step self-attention bf16, B=2, 3456 tokens (48x72), Q/K RMSNorm (1 + N(0, 0.02)) + 3D RoPE; one call, x28 for the step
+    Hp, Wp, B = 48, 72, 2
+    Tt = Hp * Wp
+    bfk = 1
+    q, k, v = seeded(1, B * Tt, bfk), seeded(2, B * Tt, bfk), seeded(3, B * Tt, bfk)
+    wq = oracle.round16(1 + 0.02 * oracle.randn(7, 128), 1)
+    wk = oracle.round16(1 + 0.02 * oracle.randn(8, 128), 1)
+    bits = lambda w: (w.view(np.uint32) >> 16).astype(np.uint16)
+    c, s_ = oracle.cosmos_rope(Hp, Wp)
+    sets = [tuple(torch.from_numpy(a).to(dev).bfloat16().clone() for a in (q, k, v)) for _ in range(3)]
+    dwq, dwk = torch.from_numpy(wq).to(dev).bfloat16(), torch.from_numpy(wk).to(dev).bfloat16()
+    dc, ds = torch.from_numpy(c).to(dev), torch.from_numpy(s_).to(dev)
+    ws = torch.empty(kb.workspace_bytes(B * Tt, B * Tt, H, torch.bfloat16, True, True), dtype=torch.uint8, device=dev)
+    out = torch.empty(B * Tt, D, device=dev, dtype=torch.bfloat16)
+    out32 = torch.empty(B * Tt, D, device=dev, dtype=torch.float32)
+    call = lambda o, st: kb.attn_self(o, *st, B, Tt, H, qn_w=dwq, kn_w=dwk, rope_cos=dc, rope_sin=ds, workspace=ws)
+    us = timed(lambda i: call(out, sets[i % 3]))
+    call(out32, sets[0])
+    assert kb.check_status() == 0
+    flop = 4.0 * Tt * Tt * 128 * H * B
+    nr = lambda x, w: np.concatenate([oracle.rope_half(oracle.rmsnorm(x[b * Tt:(b + 1) * Tt], bits(w), H), Tt, H, c, s_) for b in range(B)])
+    kn = nr(k, wk)
+    rows = rows_sample(Tt, 24)
+    qn = nr(q, wq)
+    ref = np.concatenate([oracle.attention(qn[b * Tt:(b + 1) * Tt][rows], kn[b * Tt:(b + 1) * Tt], v[b * Tt:(b + 1) * Tt], H) for b in range(B)])
+    pick = np.concatenate([rows + b * Tt for b in range(B)])
+    rec = {"case": "cfg4 self B=2 3456 tokens bf16 + Q/K RMSNorm + 3D RoPE (one block; a step is 28 of these)", "dtype": "bf16", "ours_us": us,
+           "ours_ms_per_28_blocks": us * 28 / 1e3, "ours_tflops": flop / us / 1e6, "frac_of_sustained_peak": flop / us / 1e6 / sustained,
+           "err_fp32_out": errs(out32.cpu().numpy()[pick], ref), "err_bf16_out": errs(out.float().cpu().numpy()[pick], ref)}
+    if R is not None:
+        qf, kf, vf = (t.float() for t in sets[0])
+        wqb = torch.from_numpy(bits(wq).view(np.int16)).to(dev)
+        wkb = torch.from_numpy(bits(wk).view(np.int16)).to(dev)
+        o16 = torch.empty(B * Tt, D, device=dev, dtype=torch.float16)
+        q2, k2 = qf.clone(), kf.clone()
+        def ref_block(i):
+            q2.copy_(qf); k2.copy_(kf)                               # the reference ops work in place
+            R.kref_rmsnorm(P(q2), P(q2), P(wqb), B * Tt * H, 128, cf(1e-6))
+            R.kref_rmsnorm(P(k2), P(k2), P(wkb), B * Tt * H, 128, cf(1e-6))
+            for b in range(B):
+                qb, kb_, vb, ob = q2[b * Tt:], k2[b * Tt:], vf[b * Tt:], o16[b * Tt:]
+                R.kref_rope_half(P(qb), Tt, H, 128, P(dc), P(ds))
+                R.kref_rope_half(P(kb_), Tt, H, 128, P(dc), P(ds))
+                R.kref_tfa_f16(P(ob), D, P(qb), D, P(kb_), D, P(vb), D, Tt, Tt, H, 0)
+        rus = timed(ref_block, reps=5, warm=2)
+        copy_us = timed(lambda i: (q2.copy_(qf), k2.copy_(kf)), reps=5, warm=2)
+        rec.update({"reference_unfused_us": rus - copy_us, "speedup_vs_reference_kernels": (rus - copy_us) / us,
+                    "reference_err": errs(o16.float().cpu().numpy()[pick], ref)})
+    emit(rec)
+    # config 5 is the default bench run (python bench.py); other token counts of the metric:
+    for T_ in (1536, 3456, 4096):
+        attention_case(f"self {T_} tokens bf16 (metric token count)", 1, T_, T_, T_, 0, 4.0 * T_ * T_ * 128 * H)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--all-configs", action="store_true", help="one JSON line per BASELINE.json configuration (1 GPU) instead of the benchmark line")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.all_configs:
+        run_all_configs(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -347,17 +347,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next item's P*V may start
                             named_bar_sync(3 + i, 128);                      // the staged tile is complete
+                            // each warp copies 32 rows out: all shared-memory reads first, then 256-byte row stores
                             const int np = p.n_peers > 0 ? p.n_peers : 1;
-                            const int wq = warp & 3;
-                            for (int rr = 0; rr < 32; rr++) {
-                                const int lr = 32 * wq + rr, row = it.q0 + i * BM + lr;
-                                if (row >= p.Tq) break;                      // warp-uniform
-                                const uint2 val = *reinterpret_cast<const uint2*>(stage + lr * 256 + (((lane >> 1) ^ (lr & 15)) << 4) + (lane & 1) * 8);
-                                const size_t off = ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
-                                for (int pe = 0; pe < np; pe++) {
-                                    OutT* base_out = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out);
-                                    *reinterpret_cast<uint2*>(base_out + off) = val;
-                                }
+                            const int lr0 = 32 * (warp & 3);
+                            const int row0 = it.q0 + i * BM + lr0;
+                            const int nrow = p.Tq - row0;                    // rows of this warp that exist (warp-uniform)
+                            uint2 vals[32];
+#pragma unroll
+                            for (int rr = 0; rr < 32; rr++)
+                                vals[rr] = *reinterpret_cast<const uint2*>(stage + (lr0 + rr) * 256 + (((lane >> 1) ^ ((lr0 + rr) & 15)) << 4) + (lane & 1) * 8);
+                            const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                            for (int pe = 0; pe < np; pe++) {
+                                OutT* g = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out) + off;
+#pragma unroll
+                                for (int rr = 0; rr < 32; rr++)
+                                    if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
                             }
                             if (p.n_peers > 0) __threadfence_system();       // the tile is visible to every GPU before the arrival
                             named_bar_sync(3 + i, 128);                      // every warp is done with the staging tile
@@ -461,29 +465,79 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const float ratio = f_part[128 + t] / fmaxf(f_part[t], 1e-12f);
                 const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
                 const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
-                const int row = it.q0 + t;
-                OutT* dst = reinterpret_cast<OutT*>(p.out) + (size_t)row * (size_t)p.ldo + (size_t)it.h * HD + wg * 64;
-                if (ok && all_here) {
+                const bool go = ok && all_here;                               // uniform over the 256 softmax threads
+                if constexpr (sizeof(OutT) == 2) {
+                    // blend into the (never loaded in this mode) second Q tile, then whole 256-byte rows go out
+                    constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+                    uint8_t* const stage = smem + TILE_BYTES;
+                    if (go) {
 #pragma unroll
-                    for (int q = 0; q < 2; q++) {
-                        uint32_t a[32], n[32];
-                        float v[32];
-                        tmem_ld32(tOp + 32u * q, a);
-                        tmem_ld32(tOn + 32u * q, n);
-                        tmem_wait_ld();
-                        reg_fence32(a);
-                        reg_fence32(n);
+                        for (int q = 0; q < 2; q++) {
+                            uint32_t a[32], n[32];
+                            tmem_ld32(tOp + 32u * q, a);
+                            tmem_ld32(tOn + 32u * q, n);
+                            tmem_wait_ld();
+                            reg_fence32(a);
+                            reg_fence32(n);
+                            float v[32];
 #pragma unroll
-                        for (int e = 0; e < 32; e++) {
-                            const float pv = __uint_as_float(a[e]) * ip;
-                            const float nv = __uint_as_float(n[e]) * in;
-                            v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                            for (int e = 0; e < 32; e++) {
+                                const float pv = __uint_as_float(a[e]) * ip;
+                                const float nv = __uint_as_float(n[e]) * in;
+                                v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                            }
+#pragma unroll
+                            for (int cc = 0; cc < 4; cc++) {                   // 16-byte chunk 8 wg + 4 q + cc of the row
+                                uint4 pk;
+                                pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
+                                pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
+                                pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
+                                pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
+                                *reinterpret_cast<uint4*>(stage + t * 256 + (((8 * wg + 4 * q + cc) ^ (t & 15)) << 4)) = pk;
+                            }
                         }
-                        if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
+                    named_bar_sync(1, 256);
+                    if (go) {
+                        const int lr0 = 16 * warp;                            // 8 warps x 16 rows
+                        const int nrow = p.Tq - (it.q0 + lr0);
+                        uint2 vals[16];
+#pragma unroll
+                        for (int rr = 0; rr < 16; rr++)
+                            vals[rr] = *reinterpret_cast<const uint2*>(stage + (lr0 + rr) * 256 + (((lane >> 1) ^ ((lr0 + rr) & 15)) << 4) + (lane & 1) * 8);
+                        OutT* g = reinterpret_cast<OutT*>(p.out) + (size_t)(it.q0 + lr0) * (size_t)p.ldo + (size_t)it.h * HD + (size_t)lane * 4;
+#pragma unroll
+                        for (int rr = 0; rr < 16; rr++)
+                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                    }
+                } else {
+                    const int row = it.q0 + t;
+                    OutT* dst = reinterpret_cast<OutT*>(p.out) + (size_t)row * (size_t)p.ldo + (size_t)it.h * HD + wg * 64;
+                    if (go) {
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            uint32_t a[32], n[32];
+                            float v[32];
+                            tmem_ld32(tOp + 32u * q, a);
+                            tmem_ld32(tOn + 32u * q, n);
+                            tmem_wait_ld();
+                            reg_fence32(a);
+                            reg_fence32(n);
+#pragma unroll
+                            for (int e = 0; e < 32; e++) {
+                                const float pv = __uint_as_float(a[e]) * ip;
+                                const float nv = __uint_as_float(n[e]) * in;
+                                v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                            }
+                            if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                        }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
+                    }
                 }
             }
             // leave the item loop together once any role has given up (uniform per warpgroup; in NAG mode per CTA)
