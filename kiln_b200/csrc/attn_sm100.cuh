@@ -669,7 +669,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 uint32_t n = 0;
                 uint32_t qe_cnt[2] = {0, 0};
                 bool good = true;
-                Item it;
+                Item it = {};
                 // one 128x128 tile = two 64-column boxes, each landing as a 128-byte-swizzled [128][64] half
                 auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0, int bb) {
                     tma_load_3d(dst, tm, mbar, it.h * HD, row0, bb);
