@@ -315,7 +315,7 @@ def run_ours(args):
 
 # ------------------------------------------------------------------------------------------------ per-config report
 def run_all_configs(args):
-    """BASELINE.json's five configurations on one GPU: time and accuracy of this library next to the reference's own
+    """The five benchmark configurations on one GPU: time and accuracy of this library next to the reference's own
     kernels (tfa::k_flash, k_rmsnorm_warp, k_rope_half, k_nag compiled for sm_100a into oracle/_ref/, when present) and
     the CPU oracle on sampled query rows. One JSON line per case on stdout."""
     import ctypes
@@ -400,7 +400,7 @@ def run_all_configs(args):
         attention_case(f"cfg2 cross valid={valid} zero-key padding (reference)", 0, 1536, 512, valid, 512 - valid, 4.0 * 1536 * valid * 128 * H)
         if valid < 512:
             attention_case(f"cfg2 cross valid={valid} masked padding", 0, 1536, 512, valid, 0, 4.0 * 1536 * valid * 128 * H)
-    # config 3: NAG fp16, two contexts with independent seeded valid lengths, s = 5 (reference default) and s = 6 (BASELINE literal)
+    # config 3: NAG fp16, two contexts with independent seeded valid lengths, s = 5 (reference default) and s = 6 (the same formula written as z+ + 5 (z+ - z-))
     rs = np.random.RandomState(3)
     vp_len, vn_len = int(rs.randint(16, 513)), int(rs.randint(16, 513))
     Tq = 1536
@@ -494,7 +494,7 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--all-configs", action="store_true", help="one JSON line per BASELINE.json configuration (1 GPU) instead of the benchmark line")
+    ap.add_argument("--all-configs", action="store_true", help="one JSON line per benchmark configuration (1 GPU) instead of the benchmark line")
     args = ap.parse_args()
     if args.all_configs:
         run_all_configs(args)

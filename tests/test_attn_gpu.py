@@ -77,7 +77,7 @@ def test_self_small_full_oracle(kb, T, H, kind):
 
 @pytest.mark.parametrize("T,kind", [(1536, "f16"), (3456, "bf16"), (4096, "bf16")])
 def test_self_full_size_sampled_rows(kb, T, kind):
-    """BASELINE configs 1, 4 (one image, no norm) and 5 at full size; the oracle runs on sampled query rows."""
+    """Benchmark configurations 1, 4 (one image, no norm) and 5 at full size; the oracle runs on sampled query rows."""
     H = 16
     q, k, v = (seeded(s, T, H * 128, kind) for s in (1, 2, 3))
     out = _self(kb, q, k, v, 1, T, H, kind, "f32")
@@ -192,7 +192,7 @@ def test_qk_prep_vs_reference_kernels_golden(kb, golden):
 
 
 def test_self_config4_full_size(kb):
-    """BASELINE config 4: bf16, B=2, T=3456 (48x72 patches), per-head Q/K RMSNorm (1 + N(0,0.02)) and 3D RoPE."""
+    """Benchmark configuration 4: bf16, B=2, T=3456 (48x72 patches), per-head Q/K RMSNorm (1 + N(0,0.02)) and 3D RoPE."""
     Hp, Wp, B, H, kind = 48, 72, 2, 16, "bf16"
     T = Hp * Wp
     q, k, v = (seeded(s, B * T, H * 128, kind) for s in (1, 2, 3))
@@ -213,7 +213,7 @@ def test_self_config4_full_size(kb):
 @pytest.mark.parametrize("Tk,npad", [(1, 0), (1, 511), (16, 496), (26, 486), (77, 0), (127, 385), (128, 384), (129, 0), (256, 256), (512, 0)])
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
 def test_cross_lengths(kb, Tk, npad, kind):
-    """BASELINE config 2 shapes: reference semantics (Tk = valid, npad = L - valid) and -inf masking (npad = 0)."""
+    """Benchmark configuration 2 shapes: reference semantics (Tk = valid, npad = L - valid) and -inf masking (npad = 0)."""
     Tq, H = 1536, 16
     q = seeded(4, Tq, H * 128, kind)
     k, v = seeded(5, 512, H * 128, kind), seeded(6, 512, H * 128, kind)
@@ -268,7 +268,7 @@ def _nag_ref(q, kp, vp, Tp, npp, kn, vn, Tn, npn, s, tau, alpha, H):
                                                 (300, 8, 129, 128, "f16", 5.0), (1536, 16, 333, 45, "f16", 5.0), (1536, 16, 333, 45, "f16", 6.0),
                                                 (1536, 16, 512, 512, "bf16", 5.0)])
 def test_nag(kb, Tq, H, Tp, Tn, kind, s):
-    """BASELINE config 3: reference default s=5 (engine/src/models.h:80) and the s=6 literal, tau=2.5, alpha=0.25."""
+    """Benchmark configuration 3: reference default s=5 (engine/src/models.h:80) and s=6 (the "z+ + 5 (z+ - z-)" wording of the same formula), tau=2.5, alpha=0.25."""
     L = 512
     q = seeded(7, Tq, H * 128, kind)
     kp, vp, kn, vn = (seeded(sd, L, H * 128, kind) for sd in (8, 9, 10, 11))
