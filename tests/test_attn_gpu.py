@@ -175,6 +175,26 @@ def test_self_with_norm_rope_small(kb, Hp, Wp, B, kind):
     assert_close(out, ref, f"norm+rope self {Hp}x{Wp} B={B} {kind}")
 
 
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_q_norm_only_strided_many_items(kb, kind):
+    """The cross-attention call pattern on a self-sized problem: Q gets RMSNorm, K arrives normalised; Q/K/V are column
+    slices of one buffer, the token count is ragged and there are more work items (160) than SMs."""
+    Hp, Wp, H = 45, 50, 16
+    T = Hp * Wp
+    big = seeded(1, T, 3 * H * 128, kind)
+    q, k, v = big[:, :H * 128], big[:, H * 128:2 * H * 128], big[:, 2 * H * 128:]
+    wq = oracle.round16(1 + 0.05 * oracle.randn(7, 128), 1)
+    bits = (wq.view(np.uint32) >> 16).astype(np.uint16)
+    dbig = dev(big, kind)
+    dq, dk, dv = dbig[:, :H * 128], dbig[:, H * 128:2 * H * 128], dbig[:, 2 * H * 128:]
+    out = torch.full((T, H * 128), float("nan"), device="cuda", dtype=torch.float32)
+    kb.attn_self(out, dq, dk, dv, 1, T, H, qn_w=dev(wq).bfloat16(), workspace=_ws(kb, T, T, H, kind, norm=True))
+    assert kb.check_status() == 0
+    rows = sample_rows(T, 40)
+    qn = oracle.rmsnorm(np.ascontiguousarray(q), bits, H)
+    assert_close(out.cpu().numpy()[rows], oracle.attention(qn[rows], k, v, H), f"Q norm only {kind}")
+
+
 def test_qk_prep_vs_reference_kernels_golden(kb, golden):
     """The pre-pass alone against the reference's k_rmsnorm_warp and k_rope_half outputs (fp32 in, as the engine keeps Q/K)."""
     x, w_bits, H = gen.norm_inputs()
@@ -265,7 +285,7 @@ def _nag_ref(q, kp, vp, Tp, npp, kn, vn, Tn, npn, s, tau, alpha, H):
 
 
 @pytest.mark.parametrize("Tq,H,Tp,Tn,kind,s", [(200, 2, 77, 26, "f16", 5.0), (130, 1, 16, 300, "bf16", 5.0), (257, 4, 512, 1, "f16", 6.0),
-                                                (300, 8, 129, 128, "f16", 5.0), (1536, 16, 333, 45, "f16", 5.0), (1536, 16, 333, 45, "f16", 6.0),
+                                                (300, 8, 129, 128, "f16", 5.0), (520, 3, 40, 200, "bf16", 5.0), (1536, 16, 333, 45, "f16", 5.0), (1536, 16, 333, 45, "f16", 6.0),
                                                 (1536, 16, 512, 512, "bf16", 5.0)])
 def test_nag(kb, Tq, H, Tp, Tn, kind, s):
     """Benchmark configuration 3: reference default s=5 (engine/src/models.h:80) and s=6 (the "z+ + 5 (z+ - z-)" wording of the same formula), tau=2.5, alpha=0.25."""
