@@ -163,6 +163,28 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
                int rows, int H, int T, const void* w_bf16, float eps,
                const float* rope_cos, const float* rope_sin, void* stream);
 
+/* The projections either side of attention: C = epilogue(A[M,K] * W[N,K]^T), A and W fp16 row-major
+ * (row strides lda, ldw in elements), fp32 accumulation. Replaces the engine's fp16-activation GEMM
+ * linear16 -> tc16::launch (engine/src/kernels.cu:559-609, engine/src/tcgemm16.cuh:57-190; call sites
+ * engine/src/dit.cu:461-463 (q/k/v), 471 (o-proj into the residual), 475, 488) without its LoRA second
+ * product. Epilogues as there (engine/src/tcgemm16.cuh:145-174):
+ *   KB_EPI_F32     C fp32 = acc
+ *   KB_EPI_F16     C fp16 = acc
+ *   KB_EPI_GELU16  C fp16 = gelu_erf(acc)
+ *   KB_EPI_RESID   C fp32 += gate[c] * acc   (gate NULL = 1)
+ * and one the engine does not have:
+ *   KB_EPI_HEADS16 C fp16 = rope(rmsnorm(acc)) per 128-column head: head_w bf16[128] or NULL, rope tables
+ *                  fp32 [rope_T, 64] or NULL (row r uses table row r % rope_T). It fuses the engine's
+ *                  rmsnorm + rope_half launches (engine/src/dit.cu:464-468) and this library's staging
+ *                  pre-pass into the q / k projection, so the attention entry points get fp16 operands
+ *                  that need no further pass.
+ * N must be a multiple of 128 and K of 64 (the engine asks N % 128 == 0, K % 32 == 0; every DiT weight
+ * has K = 2048 or 8192); M is free. Pointers 16-byte aligned, strides multiples of 8 (fp16) / 4 (fp32). */
+enum { KB_EPI_F32 = 0, KB_EPI_F16 = 1, KB_EPI_GELU16 = 2, KB_EPI_RESID = 3, KB_EPI_HEADS16 = 4 };
+int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw, int M, int N, int K, int epi,
+                const float* gate, const void* head_w_bf16, const float* rope_cos, const float* rope_sin, int rope_T,
+                float eps, void* stream);
+
 /* Read and clear the device status word of the current device (synchronises the device).
  * *status_bits = 0 when every kernel since the last call finished normally; returns KB_ERR_TIMEOUT
  * when a kernel gave up on a bounded wait. */
@@ -173,7 +195,7 @@ int kb_status(unsigned* status_bits);
  * (re)starts recording one CUDA event pair per kernel launch on the launch's stream, up to 8192 launches;
  * the event pool is created on the first enable, never per call. kb_prof_read synchronises the device
  * and returns the summed kernel time and launch count of one category since the last enable. */
-enum { KB_PROF_NORM_ROPE = 0, KB_PROF_ATTENTION = 1, KB_PROF_NAG = 2, KB_PROF_CATEGORIES = 3 };
+enum { KB_PROF_NORM_ROPE = 0, KB_PROF_ATTENTION = 1, KB_PROF_NAG = 2, KB_PROF_LINEAR = 3, KB_PROF_CATEGORIES = 4 };
 int kb_prof_enable(int on);
 int kb_prof_read(int category, double* total_ms, int* launches);
 

@@ -13,6 +13,7 @@
 #include "prep.cuh"
 #include "combine.cuh"
 #include "selfcheck.cuh"
+#include "gemm_sm100.cuh"
 
 namespace {
 
@@ -412,6 +413,103 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
     pb.pp.H = H; pb.pp.eps = eps;
     pb.add(out, ld_out, in, ld_in, rows, T, w_bf16, rope_cos, rope_sin);
     return launch_prep(st, pb, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+namespace {
+
+// [rows][cols] view of a row-major fp16 matrix with row stride ld; box = 64 columns x 128 rows, 128-byte swizzle
+int make_tmap_mat(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows * (cuuint64_t)ld * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KB_OK : KB_ERR_CUDA;
+}
+
+template <int EPI, bool PAIR>
+int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, GemmParams p, cudaStream_t stream) {
+    static bool smem_set[MAX_DEVICES] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!smem_set[dev]) {
+        if (cudaFuncSetAttribute(gemm16_kernel<EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess) return KB_ERR_CUDA;
+        smem_set[dev] = true;
+    }
+    const int tile = PAIR ? 256 : 128, per_group = PAIR ? 2 : 1;
+    p.tiles_m = (p.M + tile - 1) / tile;
+    p.tiles_n = p.N / tile;
+    const int n_tiles = p.tiles_m * p.tiles_n, max_groups = st->sm_count / per_group;
+    const int groups = n_tiles < max_groups ? n_tiles : max_groups;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(groups * per_group));
+    cfg.blockDim = dim3(G_THREADS);
+    cfg.dynamicSmemBytes = G_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = per_group; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ProfScope ps(st, KB_PROF_LINEAR, stream);
+    return cudaLaunchKernelEx(&cfg, gemm16_kernel<EPI, PAIR>, ta, tw, p) == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+}
+
+// CTA pairs on 256x256 tiles when that fills the device better. Measured on B200 a CTA of a pair spends about 11/8 of the
+// time a single CTA spends per 64-wide k step while doing twice the work, so compare waves x time per step.
+template <int EPI>
+int launch_gemm(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
+    if (p.N % 256 == 0 && p.M > 128) {
+        const long long tp = (long long)((p.M + 255) / 256) * (p.N / 256), ts = (long long)((p.M + 127) / 128) * (p.N / 128);
+        const long long gp = st->sm_count / 2, gs = st->sm_count;
+        const long long pair_cost = ((tp + gp - 1) / gp) * 11, single_cost = ((ts + gs - 1) / gs) * 8;
+        if (pair_cost <= single_cost) return launch_gemm_shape<EPI, true>(st, ta, tw, p, stream);
+    }
+    return launch_gemm_shape<EPI, false>(st, ta, tw, p, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw, int M, int N, int K, int epi,
+                const float* gate, const void* head_w_bf16, const float* rope_cos, const float* rope_sin, int rope_T,
+                float eps, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!C || !A || !W || M < 0 || N <= 0 || K <= 0) return KB_ERR_ARG;
+    if (epi < KB_EPI_F32 || epi > KB_EPI_HEADS16) return KB_ERR_ARG;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
+    if (rope_cos && rope_T <= 0) return KB_ERR_ARG;
+    if (epi != KB_EPI_HEADS16 && (head_w_bf16 || rope_cos)) return KB_ERR_ARG;
+    if (epi != KB_EPI_RESID && gate) return KB_ERR_ARG;
+    const bool c32 = epi == KB_EPI_F32 || epi == KB_EPI_RESID;
+    if (!aligned16(C) || !aligned16(A) || !aligned16(W) || (lda & 7) || (ldw & 7) || (ldc & (c32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (gate && !aligned16(gate)) return KB_ERR_ALIGN;
+    if (head_w_bf16 && !aligned16(head_w_bf16)) return KB_ERR_ALIGN;
+    if (rope_cos && (!aligned16(rope_cos) || !aligned16(rope_sin))) return KB_ERR_ALIGN;
+    if ((N % 128) || (K % GB_K) || lda < K || ldw < K || ldc < N) return KB_ERR_SHAPE;
+    if (M == 0) return KB_OK;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    CUtensorMap ta, tw;
+    if ((rc = make_tmap_mat(&ta, A, M, K, lda)) || (rc = make_tmap_mat(&tw, W, N, K, ldw))) return rc;
+    GemmParams p = {};
+    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.gate = gate; p.head_w = static_cast<const __nv_bfloat16*>(head_w_bf16);
+    p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T > 0 ? rope_T : 1; p.eps = eps;
+    p.status = st->status;
+    switch (epi) {
+        case KB_EPI_F32: return launch_gemm<EPI_F32>(st, ta, tw, p, stream);
+        case KB_EPI_F16: return launch_gemm<EPI_F16>(st, ta, tw, p, stream);
+        case KB_EPI_GELU16: return launch_gemm<EPI_GELU16>(st, ta, tw, p, stream);
+        case KB_EPI_RESID: return launch_gemm<EPI_RESID>(st, ta, tw, p, stream);
+        default: return launch_gemm<EPI_HEADS16>(st, ta, tw, p, stream);
+    }
 }
 
 int kb_status(unsigned* status_bits) {

@@ -47,6 +47,8 @@ def lib():
         L.kb_attn_nag.argtypes = [vp, vp, vp, vp, vp, i, i, vp, vp, i, i, f, f, f, i, i, i, i, i, i, i, f, vp, sz, vp]
         L.kb_qk_prep.restype = i
         L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
+        L.kb_linear16.restype = i
+        L.kb_linear16.argtypes = [vp, i, vp, i, vp, i, i, i, i, i, vp, vp, vp, vp, i, f, vp]
         L.kb_status.restype = i
         L.kb_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         ull = ctypes.c_ulonglong
@@ -175,6 +177,23 @@ def qk_prep(out, x, rows, H, T, w=None, rope_cos=None, rope_sin=None, eps=1e-6):
     return out
 
 
+EPI_F32, EPI_F16, EPI_GELU16, EPI_RESID, EPI_HEADS16 = 0, 1, 2, 3, 4
+
+
+def linear16(C, A, W, epi, gate=None, head_w=None, rope_cos=None, rope_sin=None, eps=1e-6):
+    """C = epilogue(A @ W.T): A [M, K] and W [N, K] fp16, fp32 accumulation (engine: linear16, engine/src/kernels.cu:559-609).
+
+    EPI_F32 / EPI_RESID take an fp32 C, the others an fp16 C; EPI_HEADS16 applies the per-head RMSNorm (head_w bf16[128])
+    and rotate-half RoPE (tables [T, 64]) to every 128-column head before the fp16 store.
+    """
+    M, K = A.shape
+    N = W.shape[0]
+    rope_T = rope_cos.shape[0] if rope_cos is not None else 0
+    _check(lib().kb_linear16(_ptr(C), _ld(C), _ptr(A), _ld(A), _ptr(W), _ld(W), M, N, K, epi, _ptr(gate), _ptr(head_w),
+                             _ptr(rope_cos), _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16")
+    return C
+
+
 def check_status():
     """Synchronise and raise if any kernel since the last call gave up on a bounded wait."""
     bits = ctypes.c_uint(0)
@@ -182,7 +201,7 @@ def check_status():
     return bits.value
 
 
-PROF_NORM_ROPE, PROF_ATTENTION, PROF_NAG = 0, 1, 2
+PROF_NORM_ROPE, PROF_ATTENTION, PROF_NAG, PROF_LINEAR = 0, 1, 2, 3
 
 
 def prof_enable(on=True):

@@ -259,6 +259,29 @@ void ko_cosmos_rope(float* c, float* s, int Hp, int Wp) {
     }
 }
 
+/* ---- fp16-activation linear layer (tcgemm16.cuh:57-175 behind linear16, kernels.cu:559-609) ----
+ * C = epi(A[M,K] . W[N,K]^T); A and W hold fp16-exact values as fp32. The products of fp16 values are exact in
+ * fp32; they are summed in double here (the tensor-core kernels sum in fp32, and the reference's own kernel in fp16
+ * within each 32-wide k tile: both differ from this only by summation rounding).
+ * epi (tcgemm16.cuh:145-174): 0 C = acc; 1 C = fp16(acc); 2 C = fp16(gelu_erf(acc)); 3 C += gate[c] * acc. */
+void ko_linear16(float* C, int ldc, const float* A, int lda, const float* W, int ldw, int M, int N, int K, int epi,
+                 const float* gate) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < M; r++)
+        for (int c = 0; c < N; c++) {
+            const float* a = A + (size_t)r * lda;
+            const float* w = W + (size_t)c * ldw;
+            double acc = 0;
+            for (int k = 0; k < K; k++) acc += (double)a[k] * (double)w[k];
+            float v = (float)acc;
+            float* dst = C + (size_t)r * ldc + c;
+            if (epi == 0) *dst = v;
+            else if (epi == 1) *dst = ko_f16_to_f32(ko_f32_to_f16(v));
+            else if (epi == 2) *dst = ko_f16_to_f32(ko_f32_to_f16(0.5f * v * (1.f + erff(v * 0.70710678118654752f))));
+            else *dst += (gate ? gate[c] : 1.f) * v;
+        }
+}
+
 /* ---- NAG combine in place on a (dit.cu:295-324): rows of `dim` (= all heads together) ----
  * g = s*p - (s-1)*n; ratio = |g|_1 / max(|p|_1, 1e-12); k = ratio > tau ? tau/ratio : 1;
  * a <- alpha*g*k + (1-alpha)*p.  acc64 != 0 sums the norms in double. */

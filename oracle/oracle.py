@@ -29,6 +29,7 @@ def lib():
         L.ko_rope_half.argtypes = [vp, i, i, i, vp, vp]
         L.ko_cosmos_rope.argtypes = [vp, vp, i, i]
         L.ko_nag.argtypes = [vp, vp, i, i, f, f, f, i]
+        L.ko_linear16.argtypes = [vp, i, vp, i, vp, i, i, i, i, i, vp]
         L.ko_torch_randn.argtypes = [ctypes.c_uint64, ctypes.c_size_t, vp]
         L.ko_torch_randn.restype = i
         L.ko_round16.argtypes = [vp, ctypes.c_size_t, i]
@@ -106,3 +107,29 @@ def nag(zp, zn, s, tau, alpha, acc64=True):
     n = _f32(zn)
     lib().ko_nag(_p(a), _p(n), a.shape[0], a.shape[1], s, tau, alpha, int(acc64))
     return a
+
+
+def linear16(x, w, epi=0, gate=None, c=None):
+    """epi(x [M, K] . w [N, K]^T) with fp16-exact inputs (reference: engine/src/tcgemm16.cuh:57-175).
+
+    epi 0 fp32, 1 fp16-rounded, 2 fp16-rounded GELU, 3 c + gate * acc (c is the fp32 residual stream, copied).
+    """
+    x, w = _f32(x), _f32(w)
+    M, K = x.shape
+    N = w.shape[0]
+    out = np.zeros((M, N), np.float32) if c is None else _f32(c).copy()
+    g = None if gate is None else _f32(gate)
+    lib().ko_linear16(_p(out), N, _p(x), K, _p(w), K, M, N, K, epi, None if g is None else _p(g))
+    return out
+
+
+def linear_heads16(x, w, H, head_w_bits=None, cos_t=None, sin_t=None, eps=1e-6):
+    """The engine's q / k projection chain: linear16 (fp32 out), per-head RMSNorm, rotate-half RoPE
+    (reference: engine/src/dit.cu:461-468), then the fp16 rounding the attention kernel applies while staging
+    (engine/src/tcflash.cuh:56-64). Returns fp32 holding fp16-exact values."""
+    y = linear16(x, w, 0)
+    if head_w_bits is not None:
+        y = rmsnorm(y, head_w_bits, H, eps)
+    if cos_t is not None:
+        y = rope_half(y, y.shape[0], H, cos_t, sin_t)
+    return round16(y, 0)

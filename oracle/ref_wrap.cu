@@ -59,6 +59,41 @@ float kref_time_tfa_f16(void* out, int ldo, const float* q, int ldq, const float
     return cudaGetLastError() == cudaSuccess ? ms / reps : -1.f;
 }
 
+// the reference's fp16-activation GEMM (tc16::launch, engine/src/tcgemm16.cuh:198-201) without the LoRA product;
+// epi: 0 fp32 store, 1 fp16 store, 2 fp16 GELU, 3 gated add into fp32 C
+static void ref_gemm16(void* C, int ldc, const void* A16, const void* W16, int M, int N, int K, int epi, const float* gate) {
+    tc16::Args a;
+    a.A = (const __half*)A16; a.W = (const __half*)W16; a.K = K;
+    a.C = C; a.ldc = ldc; a.gate = gate; a.M = M; a.N = N;
+    switch (epi) {
+        case 0: tc16::launch<tc16::EPI_F32>(a, 0, 100); break;
+        case 1: tc16::launch<tc16::EPI_F16>(a, 0, 100); break;
+        case 2: tc16::launch<tc16::EPI_GELU16>(a, 0, 100); break;
+        default: tc16::launch<tc16::EPI_RESID>(a, 0, 100); break;
+    }
+}
+
+int kref_linear16(void* C, int ldc, const void* A16, const void* W16, int M, int N, int K, int epi, const float* gate) {
+    if (!tc16::eligible(M, N, K) || epi < 0 || epi > 3) return -1;
+    ref_gemm16(C, ldc, A16, W16, M, N, K, epi, gate);
+    return (int)cudaGetLastError();
+}
+
+// average milliseconds of `reps` back-to-back launches after `warm` warm-ups
+float kref_time_linear16(void* C, int ldc, const void* A16, const void* W16, int M, int N, int K, int epi, const float* gate,
+                         int warm, int reps) {
+    if (!tc16::eligible(M, N, K) || epi < 0 || epi > 3) return -1.f;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    for (int i = 0; i < warm; i++) ref_gemm16(C, ldc, A16, W16, M, N, K, epi, gate);
+    cudaEventRecord(e0);
+    for (int i = 0; i < reps; i++) ref_gemm16(C, ldc, A16, W16, M, N, K, epi, gate);
+    cudaEventRecord(e1); cudaEventSynchronize(e1);
+    float ms = 0.f; cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    return cudaGetLastError() == cudaSuccess ? ms / reps : -1.f;
+}
+
 int kref_rmsnorm(float* y, const float* x, const uint16_t* w_bf16, int rows, int dim, float eps) {
     if (dim > 256) return -1;
     k_rmsnorm_warp<<<nblk(rows, 8), 256>>>(y, x, w_bf16, rows, dim, eps);

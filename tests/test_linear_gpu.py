@@ -1,0 +1,198 @@
+"""GPU parity tests of the fp16 projection GEMM (kb_linear16) through the C ABI, against the CPU oracle
+(fp64-accumulating restatement of the reference's linear16) and the reference kernel's own golden outputs.
+
+Tolerances: the GEMM accumulates exact fp16 x fp16 products in fp32, so fp32 outputs are held to
+1e-5 * sqrt(K) * scale; fp16 outputs to one fp16 rounding step (2^-10 |ref|) on top. The fused head
+epilogue is held to the attention path's tolerance (2e-3 max-abs, 1e-3 mean-relative)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util_gpu import assert_close, dev, sample_rows, seeded
+
+pytestmark = pytest.mark.gpu
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_spec = importlib.util.spec_from_file_location("make_ref_gemm_fixtures", os.path.join(_HERE, "golden", "make_ref_gemm_fixtures.py"))
+ggen = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(ggen)
+
+
+@pytest.fixture(scope="module")
+def kb(built_lib):
+    import kiln_b200
+    assert kiln_b200.lib().kb_init() == 0, "sm_100 device and the CUDA library are required (there is no fallback)"
+    return kiln_b200
+
+
+@pytest.fixture(scope="module")
+def gemm_golden():
+    return np.load(os.path.join(_HERE, "golden", "ref_gemm_fixtures.npz"))
+
+
+def _run(kb, x, w, epi, gate=None, resid=None, ldc_pad=0, **kw):
+    from kiln_b200 import ops
+    M, N = x.shape[0], w.shape[0]
+    c32 = epi in (ops.EPI_F32, ops.EPI_RESID)
+    full = torch.full((M, N + ldc_pad), float("nan"), device="cuda", dtype=torch.float32 if c32 else torch.float16)
+    c = full[:, :N]
+    if epi == ops.EPI_RESID:
+        c.copy_(dev(resid))
+    ops.linear16(c, dev(x, "f16"), dev(w, "f16"), epi, gate=None if gate is None else dev(gate), **kw)
+    assert kb.check_status() == 0
+    if ldc_pad:
+        assert torch.isnan(full[:, N:].float()).all(), "wrote outside the output columns"
+    return c.float().cpu().numpy()
+
+
+def _close(out, ref, K, what, f16_out):
+    scale = max(1.0, float(np.abs(ref).max()))
+    d = np.abs(out.astype(np.float64) - ref.astype(np.float64))
+    bound = 1e-5 * np.sqrt(K) * scale + (np.abs(ref) * 2.0 ** -10 + 1e-7 if f16_out else 0.0)
+    assert not np.isnan(out).any(), f"{what}: NaN"
+    assert np.all(d <= bound), f"{what}: worst excess {np.max(d - bound):.3e} (max err {d.max():.3e})"
+
+
+@pytest.mark.parametrize("case", ggen.GEMM_CASES, ids=[c[0] for c in ggen.GEMM_CASES])
+def test_epilogues_vs_oracle_and_reference_golden(kb, gemm_golden, case):
+    from kiln_b200 import ops
+    name, M, N, K = case
+    x, w, gate, resid = ggen.gemm_inputs(case)
+    for ename, epi in ggen.EPIS.items():
+        out = _run(kb, x, w, epi, gate=gate if epi == ops.EPI_RESID else None, resid=resid, ldc_pad=8)
+        ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None)
+        _close(out, ref, K, f"{name}/{ename} vs oracle", epi in (1, 2))
+        # the reference kernel sums each 32-wide k tile in fp16: hold it (and so us against it) to that error
+        g = gemm_golden[f"{name}/{ename}"].astype(np.float32)
+        tile_err = 2.0 ** -11 * np.sqrt(K / 32) * 4.0
+        assert np.abs(out - g).max() <= tile_err + 2.0 ** -9 * np.abs(g).max(), f"{name}/{ename} vs reference kernel: {np.abs(out - g).max():.3e}"
+
+
+def test_resid_without_gate(kb):
+    from kiln_b200 import ops
+    x, w = seeded(11, 70, 128, "f16"), seeded(12, 128, 128, "f16", 0.05)
+    resid = oracle.randn(13, 70 * 128).reshape(70, 128)
+    out = _run(kb, x, w, ops.EPI_RESID, resid=resid)
+    _close(out, oracle.linear16(x, w, 3, None, resid), 128, "resid, no gate", False)
+
+
+def _heads_inputs(M, H, K, seed):
+    x = seeded(seed, M, K, "f16")
+    w = seeded(seed + 1, H * 128, K, "f16", 1.0 / np.sqrt(K))
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(seed + 2, 128), 1)
+    return x, w, nw, (nw.view(np.uint32) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("H", [3, 4], ids=["single_cta_tiles", "cta_pair_tiles"])
+@pytest.mark.parametrize("norm,rope", [(True, True), (True, False), (False, True), (False, False)])
+def test_heads_epilogue(kb, norm, rope, H):
+    """The q / k projection with the per-head RMSNorm and RoPE fused, against the engine's chain of separate ops."""
+    from kiln_b200 import ops
+    Hp, Wp, B, K = 9, 13, 3, 320                             # 117 tokens per image, 3 images: rope row = r % 117
+    M = B * Hp * Wp
+    x, w, nw, nbits = _heads_inputs(M, H, K, 40)
+    cos, sin = oracle.cosmos_rope(Hp, Wp)
+    kw = {}
+    if norm:
+        kw["head_w"] = dev(nw).to(torch.bfloat16)
+    if rope:
+        kw["rope_cos"], kw["rope_sin"] = dev(cos), dev(sin)
+    out = _run(kb, x, w, ops.EPI_HEADS16, ldc_pad=16, **kw)
+    ref = oracle.linear_heads16(x, w, H, nbits if norm else None, np.tile(cos, (B, 1)) if rope else None, np.tile(sin, (B, 1)) if rope else None)
+    assert_close(out, ref, f"heads16 norm={norm} rope={rope}")
+    # tighter: the only differences are fp32 summation order and one fp16 rounding
+    assert np.abs(out - ref).max() <= 2.0 ** -10 * np.abs(ref).max() + 1e-4
+
+
+def test_dit_projection_sizes_sampled_rows(kb):
+    """4096 tokens x 2048 -> 2048 (512 tiles, several per CTA): oracle on sampled rows at the full K and N."""
+    from kiln_b200 import ops
+    M, N, K = 4096, 2048, 2048
+    x, w, nw, nbits = _heads_inputs(M, N // 128, K, 60)
+    rows = sample_rows(M, 24, 5)
+    out = _run(kb, x, w, ops.EPI_F32)
+    _close(out[rows], oracle.linear16(x[rows], w, 0), K, "4096x2048x2048 fp32", False)
+    cos, sin = oracle.cosmos_rope(64, 64)
+    outh = _run(kb, x, w, ops.EPI_HEADS16, head_w=dev(nw).to(torch.bfloat16), rope_cos=dev(cos), rope_sin=dev(sin))
+    y = oracle.rmsnorm(oracle.linear16(x[rows], w, 0), nbits, N // 128)
+    refh = oracle.round16(oracle.rope_half(y, len(rows), N // 128, cos[rows], sin[rows]), 0)
+    assert_close(outh[rows], refh, "4096x2048x2048 heads16")
+    # MLP shapes: K = 8192 down-projection into the residual stream, GELU up-projection on a ragged M
+    xm = seeded(70, 300, 8192, "f16", 0.5)
+    wm = seeded(71, 256, 8192, "f16", 0.01)
+    resid = oracle.randn(72, 300 * 256).reshape(300, 256)
+    gate = oracle.randn(73, 256)
+    _close(_run(kb, xm, wm, ops.EPI_RESID, gate=gate, resid=resid), oracle.linear16(xm, wm, 3, gate, resid), 8192, "K=8192 resid", False)
+    _close(_run(kb, xm, wm, ops.EPI_GELU16), oracle.linear16(xm, wm, 2), 8192, "K=8192 gelu16", True)
+
+
+def test_linearity_full_size(kb):
+    """Size-independent property at the full DiT size: (a X1 + b X2) W^T = a X1 W^T + b X2 W^T with exactly
+    representable scalings, so the three fp32 results agree to summation rounding."""
+    from kiln_b200 import ops
+    M, N, K = 4096, 2048, 2048
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x1 = (torch.randint(-8, 9, (M, K), device="cuda", generator=g).half()) / 8
+    x2 = (torch.randint(-8, 9, (M, K), device="cuda", generator=g).half()) / 8
+    w = (torch.randint(-8, 9, (N, K), device="cuda", generator=g).half()) / 64
+    outs = []
+    for xx in (x1, x2, x1 * 2 + x2 * 0.5):
+        c = torch.empty((M, N), device="cuda", dtype=torch.float32)
+        ops.linear16(c, xx.contiguous(), w, ops.EPI_F32)
+        outs.append(c)
+    assert kb.check_status() == 0
+    # every product is a multiple of 2^-10 and every partial sum stays below 2^10: fp32 sums are exact
+    assert torch.equal(outs[2], outs[0] * 2 + outs[1] * 0.5)
+    assert torch.equal(outs[0], (x1.double() @ w.double().T).float())
+
+
+def test_projection_feeds_attention(kb):
+    """Fused projections -> attention with fp16 operands and no workspace equals fp32 projections ->
+    attention entry point doing norm + RoPE itself."""
+    from kiln_b200 import ops
+    Hp, Wp, H, K = 12, 16, 2, 256
+    T = Hp * Wp
+    x = seeded(80, T, K, "f16")
+    ws = [seeded(81 + i, H * 128, K, "f16", 1.5 / np.sqrt(K)) for i in range(3)]
+    nq = oracle.round16(1.0 + 0.05 * oracle.randn(90, 128), 1)
+    nk = oracle.round16(1.0 + 0.05 * oracle.randn(91, 128), 1)
+    cos, sin = oracle.cosmos_rope(Hp, Wp)
+    dx, dcos, dsin = dev(x, "f16"), dev(cos), dev(sin)
+    q = torch.empty((T, H * 128), device="cuda", dtype=torch.float16)
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    ops.linear16(q, dx, dev(ws[0], "f16"), ops.EPI_HEADS16, head_w=dev(nq).to(torch.bfloat16), rope_cos=dcos, rope_sin=dsin)
+    ops.linear16(k, dx, dev(ws[1], "f16"), ops.EPI_HEADS16, head_w=dev(nk).to(torch.bfloat16), rope_cos=dcos, rope_sin=dsin)
+    ops.linear16(v, dx, dev(ws[2], "f16"), ops.EPI_F16)
+    out = torch.empty((T, H * 128), device="cuda", dtype=torch.float32)
+    ops.attn_self(out, q, k, v, 1, T, H)                     # fp16, no norm, no RoPE: no staging pass, no workspace
+    assert kb.check_status() == 0
+    bits = lambda a: (a.view(np.uint32) >> 16).astype(np.uint16)
+    qr = oracle.linear_heads16(x, ws[0], H, bits(nq), cos, sin)
+    kr = oracle.linear_heads16(x, ws[1], H, bits(nk), cos, sin)
+    vr = oracle.linear16(x, ws[2], 1)
+    assert_close(out.cpu().numpy(), oracle.attention(qr, kr, vr, H), "projection -> attention chain")
+
+
+def test_argument_errors(kb):
+    import ctypes
+    L = kb.lib()
+    a = torch.zeros((128, 128), device="cuda", dtype=torch.float16)
+    c = torch.zeros((128, 128), device="cuda", dtype=torch.float32)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def call(C=c, ldc=128, A=a, lda=128, W=a, ldw=128, M=128, N=128, K=128, epi=0, gate=None, hw=None, cos=None, sin=None, T=0):
+        return L.kb_linear16(p(C), ldc, p(A), lda, p(W), ldw, M, N, K, epi, gate, hw, cos, sin, T, 1e-6, None)
+
+    assert call() == 0
+    assert call(M=0) == 0
+    assert call(N=64) == -3 and call(K=32) == -3 and call(lda=64) == -3          # KB_ERR_SHAPE
+    assert call(epi=5) == -1 and call(epi=0, gate=p(c)) == -1                     # KB_ERR_ARG
+    assert call(epi=4, cos=p(c), sin=None) == -1 and call(epi=4, cos=p(c), sin=p(c), T=0) == -1
+    assert call(lda=132) == -2 and call(ldc=130) == -2                            # KB_ERR_ALIGN
+    assert L.kb_linear16(ctypes.c_void_p(a.data_ptr() + 2), 128, p(a), 128, p(a), 128, 128, 128, 128, 1, None, None, None, None, 0,
+                         1e-6, None) == -2
+    assert kb.check_status() == 0

@@ -1,5 +1,7 @@
 """CPU tests: the oracle (oracle/kiln_oracle.c) against the golden vectors produced by the
 reference's own kernels on a B200 (tests/golden/ref_fixtures.npz) and against torch on CPU."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -103,3 +105,30 @@ def test_nag_identities():
     out = oracle.nag(zp, zn, 5.0, 2.5, 1.0)                                                    # alpha=1: clamped g
     ratio = np.abs(out).sum(1) / np.abs(zp).sum(1)
     assert np.all(ratio <= 2.5 * (1 + 1e-5))
+
+
+# ---------------------------------------------------------------- the fp16 GEMM behind the projections
+def _gemm_gen():
+    import importlib.util
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "make_ref_gemm_fixtures.py")
+    spec = importlib.util.spec_from_file_location("make_ref_gemm_fixtures", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_linear16_oracle_vs_reference_kernel_golden():
+    """ko_linear16 against the outputs of the reference's tc16::k_gemm16 (all four epilogues). The reference sums each
+    32-wide k tile in fp16 before flushing to fp32, so it is the less exact side: the bound is that tile error."""
+    ggen = _gemm_gen()
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_gemm_fixtures.npz"))
+    for case in ggen.GEMM_CASES:
+        name, M, N, K = case
+        x, w, gate, resid = ggen.gemm_inputs(case)
+        for ename, epi in ggen.EPIS.items():
+            ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None)
+            got = g[f"{name}/{ename}"].astype(np.float32)
+            scale = np.abs(gate).max() if epi == 3 else 1.0
+            bound = (2.0 ** -11 * np.sqrt(K / 32) * 4.0 + 2.0 ** -9 * np.abs(ref).max()) * scale
+            assert np.abs(got - ref).max() <= bound, (name, ename, np.abs(got - ref).max(), bound)
+            assert np.abs(got - ref).sum() / np.abs(ref).sum() <= 1e-3, (name, ename)
