@@ -419,6 +419,20 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
 
 namespace {
 
+// [rows][cols] view of the output with row stride ld; box = 128 bytes of columns x 32 rows with 128-byte swizzle, or
+// (half_heads: the fused head epilogue stores 32-column half-heads) 64 bytes x 32 rows unswizzled
+int make_tmap_out(CUtensorMap* tm, void* ptr, int rows, int cols, int ld, bool f32, bool half_heads) {
+    const cuuint64_t esz = f32 ? 4 : 2;
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * esz, (cuuint64_t)rows * (cuuint64_t)ld * esz};
+    const cuuint32_t box[3] = {half_heads ? 32u : (cuuint32_t)(128 / esz), 32, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, ptr, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, half_heads ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KB_OK : KB_ERR_CUDA;
+}
+
 // [rows][cols] view of a row-major fp16 matrix with row stride ld; box = 64 columns x 128 rows, 128-byte swizzle
 int make_tmap_mat(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
     const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
@@ -432,7 +446,7 @@ int make_tmap_mat(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) 
 }
 
 template <int EPI, bool PAIR>
-int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, GemmParams p, cudaStream_t stream) {
+int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmParams p, cudaStream_t stream) {
     static bool smem_set[MAX_DEVICES] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -456,20 +470,20 @@ int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap&
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ProfScope ps(st, KB_PROF_LINEAR, stream);
-    return cudaLaunchKernelEx(&cfg, gemm16_kernel<EPI, PAIR>, ta, tw, p) == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, gemm16_kernel<EPI, PAIR>, ta, tw, tc, p) == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 // CTA pairs on 256x256 tiles when that fills the device better. Measured on B200 a CTA of a pair spends about 11/8 of the
 // time a single CTA spends per 64-wide k step while doing twice the work, so compare waves x time per step.
 template <int EPI>
-int launch_gemm(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
+int launch_gemm(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
     if (p.N % 256 == 0 && p.M > 128) {
         const long long tp = (long long)((p.M + 255) / 256) * (p.N / 256), ts = (long long)((p.M + 127) / 128) * (p.N / 128);
         const long long gp = st->sm_count / 2, gs = st->sm_count;
         const long long pair_cost = ((tp + gp - 1) / gp) * 11, single_cost = ((ts + gs - 1) / gs) * 8;
-        if (pair_cost <= single_cost) return launch_gemm_shape<EPI, true>(st, ta, tw, p, stream);
+        if (pair_cost <= single_cost) return launch_gemm_shape<EPI, true>(st, ta, tw, tc, p, stream);
     }
-    return launch_gemm_shape<EPI, false>(st, ta, tw, p, stream);
+    return launch_gemm_shape<EPI, false>(st, ta, tw, tc, p, stream);
 }
 
 }  // namespace
@@ -496,19 +510,19 @@ int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw
     DeviceState* st;
     int rc;
     if ((rc = get_state(&st))) return rc;
-    CUtensorMap ta, tw;
-    if ((rc = make_tmap_mat(&ta, A, M, K, lda)) || (rc = make_tmap_mat(&tw, W, N, K, ldw))) return rc;
+    CUtensorMap ta, tw, tc;
+    if ((rc = make_tmap_mat(&ta, A, M, K, lda)) || (rc = make_tmap_mat(&tw, W, N, K, ldw)) || (rc = make_tmap_out(&tc, C, M, N, ldc, c32, epi == KB_EPI_HEADS16))) return rc;
     GemmParams p = {};
     p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
     p.gate = gate; p.head_w = static_cast<const __nv_bfloat16*>(head_w_bf16);
     p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T > 0 ? rope_T : 1; p.eps = eps;
     p.status = st->status;
     switch (epi) {
-        case KB_EPI_F32: return launch_gemm<EPI_F32>(st, ta, tw, p, stream);
-        case KB_EPI_F16: return launch_gemm<EPI_F16>(st, ta, tw, p, stream);
-        case KB_EPI_GELU16: return launch_gemm<EPI_GELU16>(st, ta, tw, p, stream);
-        case KB_EPI_RESID: return launch_gemm<EPI_RESID>(st, ta, tw, p, stream);
-        default: return launch_gemm<EPI_HEADS16>(st, ta, tw, p, stream);
+        case KB_EPI_F32: return launch_gemm<EPI_F32>(st, ta, tw, tc, p, stream);
+        case KB_EPI_F16: return launch_gemm<EPI_F16>(st, ta, tw, tc, p, stream);
+        case KB_EPI_GELU16: return launch_gemm<EPI_GELU16>(st, ta, tw, tc, p, stream);
+        case KB_EPI_RESID: return launch_gemm<EPI_RESID>(st, ta, tw, tc, p, stream);
+        default: return launch_gemm<EPI_HEADS16>(st, ta, tw, tc, p, stream);
     }
 }
 

@@ -68,53 +68,10 @@ __device__ __forceinline__ void gemm_tile(int w, const GemmParams& p, int& tm, i
     tn = in_g / gsz;
 }
 
-// per-head RMSNorm and rotate-half RoPE on one accumulator row of one head (engine/src/kernels.cu:656-666, 759-772)
-__device__ __forceinline__ void head_norm_rope(float (&v)[128], const GemmParams& p, int row) {
-    if (p.head_w) {
-        uint4 wv[16];
-#pragma unroll
-        for (int q = 0; q < 16; q++) wv[q] = __ldg(reinterpret_cast<const uint4*>(p.head_w) + q);
-        float ss = 0.f;
-#pragma unroll
-        for (int c = 0; c < 128; c++) ss = fmaf(v[c], v[c], ss);
-        const float rs = rsqrtf(ss * (1.f / 128.f) + p.eps);
-#pragma unroll
-        for (int q = 0; q < 16; q++) {
-            const uint32_t wd[4] = {wv[q].x, wv[q].y, wv[q].z, wv[q].w};
-#pragma unroll
-            for (int m = 0; m < 4; m++) {   // a bf16 is the top half of an fp32
-                v[8 * q + 2 * m] = v[8 * q + 2 * m] * rs * __uint_as_float(wd[m] << 16);
-                v[8 * q + 2 * m + 1] = v[8 * q + 2 * m + 1] * rs * __uint_as_float(wd[m] & 0xffff0000u);
-            }
-        }
-    }
-    if (p.rope_cos) {
-        const int tr = min(row, p.M - 1) % p.rope_T;
-        const float4* cr = reinterpret_cast<const float4*>(p.rope_cos + (size_t)tr * 64);
-        const float4* sr = reinterpret_cast<const float4*>(p.rope_sin + (size_t)tr * 64);
-#pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-            float4 cv[8], sv[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) { cv[q] = __ldg(cr + hf * 8 + q); sv[q] = __ldg(sr + hf * 8 + q); }
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const float cc[4] = {cv[q].x, cv[q].y, cv[q].z, cv[q].w}, sn[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
-#pragma unroll
-                for (int m = 0; m < 4; m++) {
-                    const int e = hf * 32 + q * 4 + m;
-                    const float x0 = v[e], x1 = v[e + 64];
-                    v[e] = x0 * cc[m] - x1 * sn[m];
-                    v[e + 64] = x1 * cc[m] + x0 * sn[m];
-                }
-            }
-        }
-    }
-}
-
 template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
+gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
+              const GemmParams p) {
     constexpr int BN = PAIR ? 256 : 128;                                  // accumulator columns per tile
     constexpr int TILE_M = PAIR ? 256 : 128;                              // tile rows over the CTA group
     constexpr bool OUT32 = (EPI == EPI_F32 || EPI == EPI_RESID);
@@ -146,7 +103,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         mbar_fence_init();
         fence_proxy_async_smem();
     }
-    if (warp == G_EPI_WARPS + 1 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); }
+    if (warp == G_EPI_WARPS + 1 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmC); }
     if (warp == G_EPI_WARPS) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);                       // two accumulator buffers
         tmem_relinquish();
@@ -159,94 +116,219 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     if (warp < G_EPI_WARPS) {
         setmaxnreg_inc<224>();                                            // the row buffers of the epilogue live in registers
         // ------------------------------------------------------------------ epilogue: one output row per thread
-        const int quarter = warp & 3, chunk0 = warp >> 2;                // TMEM lanes [32 quarter, +32); chunks chunk0, chunk0 + 2, ...
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        uint8_t* const my_stage = stage_out + warp * 32 * 256;           // this warp's 32 rows, re-read by this warp only
-        uint32_t use[2] = {0, 0};
-        int k = 0;
-        for (int w = group; w < n_tiles; w += n_groups, ++k) {
-            const int buf = k & 1;
-            int tm, tn;
-            gemm_tile(w, p, tm, tn);
-            const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = tn * BN;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(GBAR_ACC_FULL + buf), use[buf] & 1u, abort_flag));
-            ++use[buf];
-            if (!ok) break;                                               // warps are independent from here on
-            tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const int nrow = p.M - (m0 + quarter * 32);                      // rows of this warp inside the matrix
-#pragma unroll 1
-            for (int ch = chunk0; ch < NCH; ch += 2) {
-                float v[CW];
-                {
-                    uint32_t a[CW / 32][32];
+        if constexpr (EPI == EPI_HEADS16) {
+            // The two warps of a TMEM lane quarter split every head by RoPE half: warp half hs owns columns [32 hs, +32) and
+            // their rotation partners [64 + 32 hs, +32). A thread normalises its row of the accumulator, the warp turns its
+            // 32 rows x 64 values through shared memory, and the rotation runs after the turn, one (i, i + 64) pair per
+            // lane per row: there a table row is one coalesced 128-byte read (measured: reading the tables in the
+            // thread-per-row layout, 32 different lines per instruction, cost 4 us per tile). The 32 + 32 table values of
+            // a lane are loaded once per tile, before the accumulator is waited for, and serve both heads of the tile.
+            constexpr int NH = BN / 128;
+            const int quarter = warp & 3, hs = warp >> 2;
+            const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+            uint8_t* const my_stage = stage_out + warp * 32 * 256;        // 32 rows x 64 fp32, written and re-read by this warp only
+            float* const ss_buf = reinterpret_cast<float*>(ctrl + 1024) + quarter * 64;
+            volatile uint32_t* const ok_buf = reinterpret_cast<volatile uint32_t*>(ctrl + 640) + quarter * 2;
+            const int pair_bar = 1 + quarter;
+            uint4 w0[4], w1[4];                                           // RMSNorm weights of this warp's 32 + 32 columns (bf16)
+            if (p.head_w) {
 #pragma unroll
-                    for (int q = 0; q < CW / 32; q++) tmem_ld32(tmem_base + lane_base + (uint32_t)(buf * BN + ch * CW + 32 * q), a[q]);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int q = 0; q < CW / 32; q++) {
-                        reg_fence32(a[q]);
-#pragma unroll
-                        for (int e = 0; e < 32; e++) v[32 * q + e] = __uint_as_float(a[q][e]);
-                    }
-                }
-                if (ch + 2 >= NCH) {                                      // this warp's last chunk is in registers: the MMA warp may reuse it
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR && rank != 0) mbar_arrive_cluster(mapa_u32(bar(GBAR_ACC_EMPTY + buf), 0));
-                        else mbar_arrive(bar(GBAR_ACC_EMPTY + buf));
-                    }
-                }
-                if constexpr (EPI == EPI_GELU16) {
-#pragma unroll
-                    for (int c = 0; c < CW; c++) v[c] = gelu_erf(v[c]);
-                }
-                if constexpr (EPI == EPI_HEADS16) head_norm_rope(v, p, row);
-                // re-order through shared memory (16-byte pieces XOR-swizzled by row) so that whole 256-byte row chunks go out
-                __syncwarp();
-                uint8_t* const my_row = my_stage + lane * 256;
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    uint4 pk;
-                    if constexpr (OUT32) {
-                        pk = make_uint4(__float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]), __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
-                    } else {
-                        pk.x = pack16<DT_F16>(v[8 * c + 0], v[8 * c + 1]); pk.y = pack16<DT_F16>(v[8 * c + 2], v[8 * c + 3]);
-                        pk.z = pack16<DT_F16>(v[8 * c + 4], v[8 * c + 5]); pk.w = pack16<DT_F16>(v[8 * c + 6], v[8 * c + 7]);
-                    }
-                    *reinterpret_cast<uint4*>(my_row + ((c ^ (lane & 15)) << 4)) = pk;
-                }
-                __syncwarp();
-                uint2 vals[32];
-#pragma unroll
-                for (int rr = 0; rr < 32; rr++)
-                    vals[rr] = *reinterpret_cast<const uint2*>(my_stage + rr * 256 + (((lane >> 1) ^ (rr & 15)) << 4) + (lane & 1) * 8);
-                if constexpr (OUT32) {
-                    float* g = static_cast<float*>(p.C) + (size_t)(m0 + quarter * 32) * p.ldc + n0 + ch * CW + lane * 2;
-                    if (EPI == EPI_RESID) {
-                        const float2 gt = p.gate ? __ldg(reinterpret_cast<const float2*>(p.gate + n0 + ch * CW + lane * 2)) : make_float2(1.f, 1.f);
-                        float2 old[32];
-#pragma unroll
-                        for (int rr = 0; rr < 32; rr++)
-                            if (rr < nrow) old[rr] = *reinterpret_cast<const float2*>(g + (size_t)rr * p.ldc);
-#pragma unroll
-                        for (int rr = 0; rr < 32; rr++)
-                            if (rr < nrow)
-                                *reinterpret_cast<float2*>(g + (size_t)rr * p.ldc) =
-                                    make_float2(fmaf(gt.x, __uint_as_float(vals[rr].x), old[rr].x), fmaf(gt.y, __uint_as_float(vals[rr].y), old[rr].y));
-                    } else {
-#pragma unroll
-                        for (int rr = 0; rr < 32; rr++)
-                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * p.ldc) = vals[rr];
-                    }
-                } else {
-                    __half* g = static_cast<__half*>(p.C) + (size_t)(m0 + quarter * 32) * p.ldc + n0 + ch * CW + lane * 4;
-#pragma unroll
-                    for (int rr = 0; rr < 32; rr++)
-                        if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * p.ldc) = vals[rr];
+                for (int q = 0; q < 4; q++) {
+                    w0[q] = __ldg(reinterpret_cast<const uint4*>(p.head_w + hs * 32) + q);
+                    w1[q] = __ldg(reinterpret_cast<const uint4*>(p.head_w + 64 + hs * 32) + q);
                 }
             }
+            uint32_t use[2] = {0, 0};
+            int k = 0;
+            for (int w = group; w < n_tiles; w += n_groups, ++k) {
+                const int buf = k & 1;
+                int tm, tn;
+                gemm_tile(w, p, tm, tn);
+                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = tn * BN;
+                const int row0 = m0 + quarter * 32;
+                const int nrow = p.M - row0;
+                float cr[32], sr[32];
+                if (p.rope_cos) {
+                    int tr = min(row0, p.M - 1) % p.rope_T;
+#pragma unroll
+                    for (int rr = 0; rr < 32; rr++) {
+                        cr[rr] = __ldg(p.rope_cos + (size_t)tr * 64 + hs * 32 + lane);
+                        sr[rr] = __ldg(p.rope_sin + (size_t)tr * 64 + hs * 32 + lane);
+                        if (row0 + rr + 1 < p.M) tr = (tr + 1 == p.rope_T) ? 0 : tr + 1;
+                    }
+                }
+                bool ok = __all_sync(0xffffffffu, mbar_wait(bar(GBAR_ACC_FULL + buf), use[buf] & 1u, abort_flag));
+                ++use[buf];
+                if (lane == 0) ok_buf[hs] = ok ? 1u : 0u;                 // leave only together: the pair meets at named barriers below
+                named_bar_sync(pair_bar, 64);
+                ok = ok_buf[0] != 0u && ok_buf[1] != 0u;
+                named_bar_sync(pair_bar, 64);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int h = 0; h < NH; h++) {
+                    float x0[32], x1[32];
+                    {
+                        uint32_t a0[32], a1[32];
+                        tmem_ld32(tmem_base + lane_base + (uint32_t)(buf * BN + h * 128 + hs * 32), a0);
+                        tmem_ld32(tmem_base + lane_base + (uint32_t)(buf * BN + h * 128 + 64 + hs * 32), a1);
+                        tmem_wait_ld();
+                        reg_fence32(a0);
+                        reg_fence32(a1);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) { x0[e] = __uint_as_float(a0[e]); x1[e] = __uint_as_float(a1[e]); }
+                    }
+                    if (h == NH - 1) {                                    // this warp's share of the accumulator is in registers
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (PAIR && rank != 0) mbar_arrive_cluster(mapa_u32(bar(GBAR_ACC_EMPTY + buf), 0));
+                            else mbar_arrive(bar(GBAR_ACC_EMPTY + buf));
+                        }
+                    }
+                    if (p.head_w) {                                       // engine/src/kernels.cu:656-666
+                        float ss = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 32; e++) ss = fmaf(x0[e], x0[e], fmaf(x1[e], x1[e], ss));
+                        ss_buf[hs * 32 + lane] = ss;
+                        named_bar_sync(pair_bar, 64);
+                        const float rs = rsqrtf((ss + ss_buf[(hs ^ 1) * 32 + lane]) * (1.f / 128.f) + p.eps);
+                        named_bar_sync(pair_bar, 64);                     // both sums are read before the next head overwrites them
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const uint32_t d0[4] = {w0[q].x, w0[q].y, w0[q].z, w0[q].w}, d1[4] = {w1[q].x, w1[q].y, w1[q].z, w1[q].w};
+#pragma unroll
+                            for (int m = 0; m < 4; m++) {                 // a bf16 is the top half of an fp32
+                                x0[8 * q + 2 * m] = x0[8 * q + 2 * m] * rs * __uint_as_float(d0[m] << 16);
+                                x0[8 * q + 2 * m + 1] = x0[8 * q + 2 * m + 1] * rs * __uint_as_float(d0[m] & 0xffff0000u);
+                                x1[8 * q + 2 * m] = x1[8 * q + 2 * m] * rs * __uint_as_float(d1[m] << 16);
+                                x1[8 * q + 2 * m + 1] = x1[8 * q + 2 * m + 1] * rs * __uint_as_float(d1[m] & 0xffff0000u);
+                            }
+                        }
+                    }
+                    if (lane == 0) tma_store_wait_read();                 // the boxes of the last head have left shared memory
+                    __syncwarp();
+                    uint8_t* const my_row = my_stage + lane * 256;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {                         // 16-byte pieces j (first half) and 8 + j (partners), XOR-swizzled by row
+                        *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 15)) << 4)) = make_float4(x0[4 * j], x0[4 * j + 1], x0[4 * j + 2], x0[4 * j + 3]);
+                        *reinterpret_cast<float4*>(my_row + (((8 + j) ^ (lane & 15)) << 4)) = make_float4(x1[4 * j], x1[4 * j + 1], x1[4 * j + 2], x1[4 * j + 3]);
+                    }
+                    __syncwarp();
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int rr = 0; rr < 32; rr++) {
+                        const uint8_t* src = my_stage + rr * 256 + (lane & 3) * 4;
+                        float a = *reinterpret_cast<const float*>(src + (((lane >> 2) ^ (rr & 15)) << 4));
+                        float b = *reinterpret_cast<const float*>(src + (((8 + (lane >> 2)) ^ (rr & 15)) << 4));
+                        if (p.rope_cos) {                                 // engine/src/kernels.cu:769-771
+                            const float ra = a * cr[rr] - b * sr[rr];
+                            b = b * cr[rr] + a * sr[rr];
+                            a = ra;
+                        }
+                        const float other = __shfl_xor_sync(0xffffffffu, (lane & 1) ? a : b, 1);
+                        pk[rr] = (lane & 1) ? pack16<DT_F16>(other, b) : pack16<DT_F16>(a, other);
+                    }
+                    // back into shared memory as two 32-row x 64-byte boxes (first half, partners), which leave by TMA
+                    __syncwarp();
+                    uint8_t* const my_out = my_stage + (lane & 1) * 2048 + (lane >> 1) * 4;
+#pragma unroll
+                    for (int rr = 0; rr < 32; rr++) *reinterpret_cast<uint32_t*>(my_out + rr * 64) = pk[rr];
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && nrow > 0) {
+                        const int x = n0 + h * 128 + hs * 32;
+                        tma_store_3d(&tmC, smem_u32(my_stage), x, row0, 0);
+                        tma_store_3d(&tmC, smem_u32(my_stage) + 2048, x + 64, row0, 0);
+                        tma_store_commit();
+                    }
+                }
+            }
+            if (lane == 0) tma_store_wait_all();
+        } else {
+            const int quarter = warp & 3, chunk0 = warp >> 2;                // TMEM lanes [32 quarter, +32); chunks chunk0, chunk0 + 2, ...
+            const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+            uint8_t* const my_stage = stage_out + warp * 32 * 256;           // this warp's 32 rows x 256 bytes on their way out
+            uint32_t use[2] = {0, 0};
+            int k = 0;
+            for (int w = group; w < n_tiles; w += n_groups, ++k) {
+                const int buf = k & 1;
+                int tm, tn;
+                gemm_tile(w, p, tm, tn);
+                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = tn * BN;
+                const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(GBAR_ACC_FULL + buf), use[buf] & 1u, abort_flag));
+                ++use[buf];
+                if (!ok) break;                                               // warps are independent from here on
+                tc_fence_after();
+                const int nrow = p.M - (m0 + quarter * 32);                      // rows of this warp inside the matrix
+#pragma unroll 1
+                for (int ch = chunk0; ch < NCH; ch += 2) {
+                    float v[CW];
+                    {
+                        uint32_t a[CW / 32][32];
+#pragma unroll
+                        for (int q = 0; q < CW / 32; q++) tmem_ld32(tmem_base + lane_base + (uint32_t)(buf * BN + ch * CW + 32 * q), a[q]);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int q = 0; q < CW / 32; q++) {
+                            reg_fence32(a[q]);
+#pragma unroll
+                            for (int e = 0; e < 32; e++) v[32 * q + e] = __uint_as_float(a[q][e]);
+                        }
+                    }
+                    if (ch + 2 >= NCH) {                                      // this warp's last chunk is in registers: the MMA warp may reuse it
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (PAIR && rank != 0) mbar_arrive_cluster(mapa_u32(bar(GBAR_ACC_EMPTY + buf), 0));
+                            else mbar_arrive(bar(GBAR_ACC_EMPTY + buf));
+                        }
+                    }
+                    if constexpr (EPI == EPI_GELU16) {
+#pragma unroll
+                        for (int c = 0; c < CW; c++) v[c] = gelu_erf(v[c]);
+                    }
+                    if constexpr (EPI == EPI_RESID) {
+                        if (p.gate) {
+#pragma unroll
+                            for (int c = 0; c < CW; c += 4) {
+                                const float4 gt = __ldg(reinterpret_cast<const float4*>(p.gate + n0 + ch * CW + c));
+                                v[c] *= gt.x; v[c + 1] *= gt.y; v[c + 2] *= gt.z; v[c + 3] *= gt.w;
+                            }
+                        }
+                    }
+                    // the 32 x 256-byte piece of the output goes through shared memory as two 128-byte-swizzled boxes and
+                    // leaves by TMA (measured: 32 row stores per warp took 3 us, the issue rate of plain global stores from
+                    // eight warps; the bulk copy takes them off the warp)
+                    if (lane == 0) tma_store_wait_read();                     // the boxes of the last chunk have been read
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 16; c++) {
+                        uint4 pk;
+                        if constexpr (OUT32) {
+                            pk = make_uint4(__float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]), __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
+                        } else {
+                            pk.x = pack16<DT_F16>(v[8 * c + 0], v[8 * c + 1]); pk.y = pack16<DT_F16>(v[8 * c + 2], v[8 * c + 3]);
+                            pk.z = pack16<DT_F16>(v[8 * c + 4], v[8 * c + 5]); pk.w = pack16<DT_F16>(v[8 * c + 6], v[8 * c + 7]);
+                        }
+                        *reinterpret_cast<uint4*>(my_stage + (c >> 3) * 4096 + lane * 128 + (((c & 7) ^ (lane & 7)) << 4)) = pk;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && nrow > 0) {
+                        const int x = n0 + ch * CW, y = m0 + quarter * 32;
+                        if constexpr (EPI == EPI_RESID) {
+                            tma_reduce_add_3d(&tmC, smem_u32(my_stage), x, y, 0);
+                            tma_reduce_add_3d(&tmC, smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
+                        } else {
+                            tma_store_3d(&tmC, smem_u32(my_stage), x, y, 0);
+                            tma_store_3d(&tmC, smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
+                        }
+                        tma_store_commit();
+                    }
+                }
+            }
+            if (lane == 0) tma_store_wait_all();
         }
     } else if (warp == G_EPI_WARPS) {
         setmaxnreg_dec<56>();
