@@ -66,6 +66,20 @@ void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16
           "nag_attention16");
 }
 
+void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi16 epi, const float* gate) {
+    if (W.rows % 128 || W.cols % 64) throw std::runtime_error("linear16: the weight is not tensor-core eligible");   // engine/src/kernels.cu:560
+    check(kb_linear16(y, ldy, x16, W.cols, W.p, W.cols, T, W.rows, W.cols, (int)epi, gate, nullptr, nullptr, nullptr, 0, 0.f, g_ctx.stream),
+          "linear16");
+}
+
+void linear16_heads(__half* y, int ldy, const __half* x16, int T, const Weight16& W, const uint16_t* norm_w_bf16, const float* rope_cos,
+                    const float* rope_sin, int rope_T, float eps) {
+    if (W.rows % 128 || W.cols % 64) throw std::runtime_error("linear16: the weight is not tensor-core eligible");
+    check(kb_linear16(y, ldy, x16, W.cols, W.p, W.cols, T, W.rows, W.cols, KB_EPI_HEADS16, nullptr, norm_w_bf16, rope_cos, rope_sin, rope_T,
+                      eps, g_ctx.stream),
+          "linear16_heads");
+}
+
 }  // namespace kiln_b200
 
 // C trampolines so the shim can be exercised from the test-suite without a C++ test runner:
@@ -96,6 +110,17 @@ int kbh_rmsnorm_rope(float* x, const uint16_t* w, int T, int H, float eps, const
         NR& a = *(NR*)p;
         kiln_b200::rmsnorm(a.x, a.x, a.w, a.rows, 128, a.eps);
         kiln_b200::rope_half(a.x, a.T, a.H, 128, a.c, a.s);
+    }, &a);
+}
+struct L16 { void* y; int ldy; const void* x; int T; const void* w; int rows, cols, epi; const float* gate; const uint16_t* nw; const float *c, *s; int rope_T; float eps; };
+int kbh_linear16(void* y, int ldy, const void* x16, int T, const void* w16, int rows, int cols, int epi, const float* gate,
+                 const uint16_t* norm_w, const float* c, const float* s, int rope_T, float eps, char* err, int n) {
+    L16 a{y, ldy, x16, T, w16, rows, cols, epi, gate, norm_w, c, s, rope_T, eps};
+    return guard(err, n, [](void* p) {
+        L16& a = *(L16*)p;
+        kiln_b200::Weight16 W; W.p = (const __half*)a.w; W.rows = a.rows; W.cols = a.cols;
+        if (a.epi == 4) kiln_b200::linear16_heads((__half*)a.y, a.ldy, (const __half*)a.x, a.T, W, a.nw, a.c, a.s, a.rope_T, a.eps);
+        else kiln_b200::linear16(a.y, a.ldy, (const __half*)a.x, a.T, W, (kiln_b200::Epi16)a.epi, a.gate);
     }, &a);
 }
 }

@@ -5,6 +5,7 @@
 //   attention16()  engine/src/gpu.h:155-156, engine/src/kernels.cu:868-873
 //   rmsnorm()      engine/src/gpu.h:133,     engine/src/kernels.cu:668-673   (rows of 128: the per-head Q/K norm)
 //   rope_half()    engine/src/gpu.h:145,     engine/src/kernels.cu:773-777
+//   linear16()     engine/src/gpu.h (Epi16, linear16), engine/src/kernels.cu:559-609   (without the LoRA side product)
 //   nag_combine is the k_nag launch of engine/src/dit.cu:486 (fp16 rows) / :524 (fp32 rows)
 //
 // Like the reference ops they run on one stream, take device pointers the caller owns, and throw
@@ -49,5 +50,18 @@ void self_attention16(__half* out, int ldo, const float* q, int ldq, const float
 void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16_t* qn_w, const float* k_pos, const float* v_pos,
                      int Tk_pos, int npad_pos, const float* k_neg, const float* v_neg, int Tk_neg, int npad_neg, int ld_kv,
                      float scale, float tau, float alpha, int Tq, int H, float eps);
+
+// The fp16-activation linear layer y = epi(x16 [T, in] . W^T), W an fp16 [out, in] weight (the reference's Weight with
+// f16 set; a bf16 weight is converted by the caller once, as the reference does into G.wbuf). Epilogues as the reference's
+// Epi16 (engine/src/kernels.cu:597-603); y is fp32 for F32 / Resid and fp16 for F16 / Gelu16.
+enum class Epi16 { F32 = 0, F16 = 1, Gelu16 = 2, Resid = 3 };
+struct Weight16 {
+    const __half* p = nullptr;
+    int rows = 0, cols = 0;          // out, in
+};
+void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi16 epi, const float* gate = nullptr);
+// linear16 + rmsnorm + rope_half of engine/src/dit.cu:461-468 in one launch, fp16 out: what attention consumes directly
+void linear16_heads(__half* y, int ldy, const __half* x16, int T, const Weight16& W, const uint16_t* norm_w_bf16,
+                    const float* rope_cos, const float* rope_sin, int rope_T, float eps);
 
 }  // namespace kiln_b200

@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     ap.add_argument("--norm", action="store_true", help="Q/K RMSNorm (+ RoPE for self) through the staging pre-pass")
+    ap.add_argument("--cublas", action="store_true", help="linear: also time torch.matmul on the same operands")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--warm", type=int, default=2)
     a = ap.parse_args()
@@ -122,6 +123,13 @@ def linear_cases(a):
         us = timed(fn, a.warm, a.reps)
         assert kb.check_status() == 0
         print(f"case=linear M={M} N={N} K={K} epi={a.epi}: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
+        if a.cublas and epi == ops.EPI_F16:                 # the library GEMM on the same operands, for scale
+
+            def mm():
+                it[0] = (it[0] + 1) % nset
+                torch.matmul(xs[it[0]], wts[it[0]].T, out=c)
+            us = timed(mm, a.warm, a.reps)
+            print(f"  cuBLAS (torch.matmul) fp16: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
         return
     D = H * 128
     x = rn(T, D)

@@ -64,3 +64,33 @@ def test_rmsnorm_rope_in_place_fp32_vs_reference_golden(shim, golden):
     assert shim.kbh_rmsnorm_rope(P(dx), P(dw), T, H, ctypes.c_float(1e-6), P(dev(c)), P(dev(s)), err, 256) == 0, err.value
     torch.cuda.synchronize()
     np.testing.assert_allclose(dx.cpu().numpy(), ref, rtol=1e-5, atol=2e-6)
+
+
+def test_linear16_epilogues_and_heads(shim):
+    """linear16 with the engine's Epi16 values and the fused head form, against the oracle; an ineligible weight throws."""
+    M, N, K, H = 150, 256, 128, 2
+    x = oracle.round16(oracle.randn(500, M * K), 0).reshape(M, K)
+    w = oracle.round16(oracle.randn(501, N * K) * np.float32(0.05), 0).reshape(N, K)
+    gate = oracle.randn(502, N)
+    resid = oracle.randn(503, M * N).reshape(M, N)
+    dx, dw = dev(x).half(), dev(w).half()
+    err = ctypes.create_string_buffer(256)
+    f = ctypes.c_float
+    for epi in range(4):
+        c32 = epi in (0, 3)
+        c = dev(resid).clone() if epi == 3 else torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32 if c32 else torch.float16)
+        assert shim.kbh_linear16(P(c), N, P(dx), M, P(dw), N, K, epi, P(dev(gate)) if epi == 3 else None, None, None, None, 0, f(0),
+                                 err, 256) == 0, err.value
+        torch.cuda.synchronize()
+        ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None)
+        assert np.abs(c.float().cpu().numpy() - ref).max() <= 2e-4 + 2.0 ** -10 * np.abs(ref).max(), epi
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(504, 128), 1)
+    bits = (nw.view(np.uint32) >> 16).astype(np.uint16)
+    cos, sin = oracle.cosmos_rope(10, 15)
+    y = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16)
+    assert shim.kbh_linear16(P(y), N, P(dx), M, P(dw), N, K, 4, None, P(dev(bits.view(np.int16))), P(dev(cos)), P(dev(sin)), 150, f(1e-6),
+                             err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    assert_close(y.float().cpu().numpy(), oracle.linear_heads16(x, w, H, bits, cos, sin), "shim linear16_heads")
+    assert shim.kbh_linear16(P(y), N, P(dx), M, P(dw), 192, K, 1, None, None, None, None, 0, f(0), err, 256) == -1
+    assert b"eligible" in err.value
