@@ -148,7 +148,7 @@ template <int MODE, typename OutT>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
-                const __grid_constant__ CUtensorMap tmV1, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
@@ -340,32 +340,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                     pk.y = pack16<ODT>(__uint_as_float(o[8 * cc + 2]) * inv, __uint_as_float(o[8 * cc + 3]) * inv);
                                     pk.z = pack16<ODT>(__uint_as_float(o[8 * cc + 4]) * inv, __uint_as_float(o[8 * cc + 5]) * inv);
                                     pk.w = pack16<ODT>(__uint_as_float(o[8 * cc + 6]) * inv, __uint_as_float(o[8 * cc + 7]) * inv);
-                                    *reinterpret_cast<uint4*>(stage + t * 256 + (((4 * q + cc) ^ (t & 15)) << 4)) = pk;
+                                    // the tile's own layout: two 128-byte-swizzled [128][64] halves (what TMA stores)
+                                    *reinterpret_cast<uint4*>(stage + (q >> 1) * HALF_BYTES + t * 128 + ((((4 * q + cc) & 7) ^ (t & 7)) << 4)) = pk;
                                 }
                             }
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next item's P*V may start
-                            named_bar_sync(3 + i, 128);                      // the staged tile is complete
-                            // each warp copies 32 rows out: all shared-memory reads first, then 256-byte row stores
-                            const int np = p.n_peers > 0 ? p.n_peers : 1;
-                            const int lr0 = 32 * (warp & 3);
-                            const int row0 = it.q0 + i * BM + lr0;
-                            const int nrow = p.Tq - row0;                    // rows of this warp that exist (warp-uniform)
-                            uint2 vals[32];
-#pragma unroll
-                            for (int rr = 0; rr < 32; rr++)
-                                vals[rr] = *reinterpret_cast<const uint2*>(stage + (lr0 + rr) * 256 + (((lane >> 1) ^ ((lr0 + rr) & 15)) << 4) + (lane & 1) * 8);
-                            const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
-                            for (int pe = 0; pe < np; pe++) {
-                                OutT* g = reinterpret_cast<OutT*>(p.n_peers > 0 ? p.out_peers[pe] : p.out) + off;
+                            if (p.n_peers == 0) {
+                                // one bulk tensor store per half; rows past Tq are clipped by the tensor map
+                                fence_proxy_async_smem();
+                                named_bar_sync(3 + i, 128);                  // the staged tile is complete
+                                if (t == 0) {
+                                    tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0 + i * BM, it.b);
+                                    tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0 + i * BM, it.b);
+                                    tma_store_commit();
+                                    tma_store_wait_read();                   // the staging space may be overwritten
+                                }
+                            } else {
+                                named_bar_sync(3 + i, 128);                  // the staged tile is complete
+                                // head-split runs: each warp copies 32 rows out as whole 256-byte rows to every peer buffer
+                                // (all shared-memory reads first, then the stores)
+                                const int lr0 = 32 * (warp & 3);
+                                const int row0 = it.q0 + i * BM + lr0;
+                                const int nrow = p.Tq - row0;                // rows of this warp that exist (warp-uniform)
+                                uint2 vals[32];
 #pragma unroll
                                 for (int rr = 0; rr < 32; rr++)
-                                    if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                                    vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                               ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                                const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                                for (int pe = 0; pe < p.n_peers; pe++) {
+                                    OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                                    for (int rr = 0; rr < 32; rr++)
+                                        if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                                }
+                                __threadfence_system();                      // the tile is visible to every GPU before the arrival
+                                named_bar_sync(3 + i, 128);                  // every warp is done with the staging tile
+                                if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
                             }
-                            if (p.n_peers > 0) __threadfence_system();       // the tile is visible to every GPU before the arrival
-                            named_bar_sync(3 + i, 128);                      // every warp is done with the staging tile
-                            if (p.n_peers > 0 && t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
                         } else {
                             const int row = it.q0 + i * BM + t;
                             OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)it.h * HD;
@@ -493,25 +507,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
                                 pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
                                 pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
-                                *reinterpret_cast<uint4*>(stage + t * 256 + (((8 * wg + 4 * q + cc) ^ (t & 15)) << 4)) = pk;
+                                // warpgroup wg fills the 128-byte-swizzled [128][64] half wg of the tile (what TMA stores)
+                                *reinterpret_cast<uint4*>(stage + wg * HALF_BYTES + t * 128 + (((4 * q + cc) ^ (t & 7)) << 4)) = pk;
                             }
                         }
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
+                        fence_proxy_async_smem();
                     }
                     named_bar_sync(1, 256);
-                    if (go) {
-                        const int lr0 = 16 * warp;                            // 8 warps x 16 rows
-                        const int nrow = p.Tq - (it.q0 + lr0);
-                        uint2 vals[16];
-#pragma unroll
-                        for (int rr = 0; rr < 16; rr++)
-                            vals[rr] = *reinterpret_cast<const uint2*>(stage + (lr0 + rr) * 256 + (((lane >> 1) ^ ((lr0 + rr) & 15)) << 4) + (lane & 1) * 8);
-                        OutT* g = reinterpret_cast<OutT*>(p.out) + (size_t)(it.q0 + lr0) * (size_t)p.ldo + (size_t)it.h * HD + (size_t)lane * 4;
-#pragma unroll
-                        for (int rr = 0; rr < 16; rr++)
-                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                    if (go && tid == 0) {                                     // one bulk tensor store per half; rows past Tq are clipped
+                        tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0, 0);
+                        tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0, 0);
+                        tma_store_commit();
+                        tma_store_wait_read();                                // before the next item blends into this space
                     }
                 } else {
                     const int row = it.q0 + t;
@@ -554,6 +564,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (wg_stop[1] != 0u) break;
             }
         }
+        if (lane == 0) tma_store_wait_all();                              // bulk stores issued by this thread have landed
         tc_fence_before();
         cta_sync();
     } else {
