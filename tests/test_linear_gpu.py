@@ -196,3 +196,29 @@ def test_argument_errors(kb):
     assert L.kb_linear16(ctypes.c_void_p(a.data_ptr() + 2), 128, p(a), 128, p(a), 128, 128, 128, 128, 1, None, None, None, None, 0,
                          1e-6, None) == -2
     assert kb.check_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (129, 256, 64), (257, 512, 128), (128, 256, 192), (640, 384, 64), (2, 256, 2048)],
+                         ids=["one_row", "pair_second_cta_one_row", "pair_ragged", "pair_not_taken_m128", "single_n384", "two_rows_long_k"])
+def test_edge_shapes_every_epilogue(kb, M, N, K):
+    """Smallest and raggedest shapes of both tile shapes (CTA pair: N % 256 == 0 and M > 128; single CTA otherwise), with a
+    padded row stride: every epilogue against the oracle, nothing written outside the M x N window."""
+    from kiln_b200 import ops
+    x = seeded(200 + M, M, K, "f16")
+    w = seeded(201 + N, N, K, "f16", 1.0 / np.sqrt(K))
+    gate = oracle.randn(202, max(N, 16))[:N].copy()
+    resid = oracle.randn(203, max(M * N, 16))[:M * N].reshape(M, N).copy()
+    for epi in (ops.EPI_F32, ops.EPI_F16, ops.EPI_GELU16, ops.EPI_RESID):
+        out = _run(kb, x, w, epi, gate=gate if epi == ops.EPI_RESID else None, resid=resid, ldc_pad=8)
+        ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None)
+        _close(out, ref, K, f"{M}x{N}x{K} epi {epi}", epi in (1, 2))
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(204, 128), 1)
+    bits = (nw.view(np.uint32) >> 16).astype(np.uint16)
+    T = 7                                                    # table shorter than M: rows wrap (batched images)
+    cos, sin = (a[5:5 + T].copy() for a in oracle.cosmos_rope(4, 8))
+    out = _run(kb, x, w, ops.EPI_HEADS16, ldc_pad=8, head_w=dev(nw).to(torch.bfloat16), rope_cos=dev(cos), rope_sin=dev(sin))
+    reps = (M + T - 1) // T
+    ref = oracle.linear_heads16(x, w, N // 128, bits, np.tile(cos, (reps, 1))[:M], np.tile(sin, (reps, 1))[:M])
+    # fp32 summation order and one fp16 rounding are the only differences: a one-ulp disagreement is the worst case
+    assert not np.isnan(out).any()
+    assert np.all(np.abs(out - ref) <= 2.0 ** -10 * np.abs(ref) + 1e-4), f"{M}x{N}x{K} heads16: {np.abs(out - ref).max():.3e}"
