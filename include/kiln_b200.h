@@ -185,6 +185,17 @@ int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw
                 const float* gate, const void* head_w_bf16, const float* rope_cos, const float* rope_sin, int rope_T,
                 float eps, void* stream);
 
+/* The q, k and v projections of one activation in ONE launch: C3[i] = heads16(A . W3[i]^T) for i = 0..2, every output
+ * fp16 [M, ldc] with N = 128 * heads columns, every weight fp16 [N, ldw]; head_w3[i] (bf16[128] or NULL) and
+ * rope_on3[i] choose the per-head RMSNorm and the RoPE of each projection (the engine: q and k normalised and
+ * rotated, v neither: engine/src/dit.cu:461-468). Same arithmetic as three kb_linear16(KB_EPI_HEADS16) calls — the
+ * results are bit-identical — with one pass over the tile schedule: 3x the tiles per launch fill the last wave
+ * better and two launches, two pipeline fills and two drains go away. The engine has no counterpart (it issues three
+ * linear16 calls, engine/src/dit.cu:461-463). */
+int kb_linear16_qkv(void* const* C3, int ldc, const void* A, int lda, const void* const* W3, int ldw, int M, int N, int K,
+                    const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
+                    float eps, void* stream);
+
 /* Read and clear the device status word of the current device (synchronises the device).
  * *status_bits = 0 when every kernel since the last call finished normally; returns KB_ERR_TIMEOUT
  * when a kernel gave up on a bounded wait. */

@@ -458,8 +458,9 @@ int make_tmap_mat(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) 
     return r == CUDA_SUCCESS ? KB_OK : KB_ERR_CUDA;
 }
 
+// p.N is the width of ONE segment; the launch covers n_seg of them side by side
 template <int EPI, bool PAIR>
-int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmParams p, cudaStream_t stream) {
+int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const GemmMaps& maps, GemmParams p, int n_seg, cudaStream_t stream) {
     static bool smem_set[MAX_DEVICES] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -469,7 +470,8 @@ int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap&
     }
     const int tile = PAIR ? 256 : 128, per_group = PAIR ? 2 : 1;
     p.tiles_m = (p.M + tile - 1) / tile;
-    p.tiles_n = p.N / tile;
+    p.tiles_n_seg = p.N / tile;
+    p.tiles_n = p.tiles_n_seg * n_seg;
     const int n_tiles = p.tiles_m * p.tiles_n, max_groups = st->sm_count / per_group;
     const int groups = n_tiles < max_groups ? n_tiles : max_groups;
     cudaLaunchConfig_t cfg = {};
@@ -483,20 +485,69 @@ int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const CUtensorMap&
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     ProfScope ps(st, KB_PROF_LINEAR, stream);
-    return cudaLaunchKernelEx(&cfg, gemm16_kernel<EPI, PAIR>, ta, tw, tc, p) == cudaSuccess ? KB_OK : KB_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, gemm16_kernel<EPI, PAIR>, ta, maps, p) == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 // CTA pairs on 256x256 tiles when that fills the device better. Measured on B200 a CTA of a pair spends about 11/8 of the
 // time a single CTA spends per 64-wide k step while doing twice the work, so compare waves x time per step.
 template <int EPI>
-int launch_gemm(DeviceState* st, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
+int launch_gemm(DeviceState* st, const CUtensorMap& ta, const GemmMaps& maps, const GemmParams& p, int n_seg, cudaStream_t stream) {
     if (p.N % 256 == 0 && p.M > 128) {
-        const long long tp = (long long)((p.M + 255) / 256) * (p.N / 256), ts = (long long)((p.M + 127) / 128) * (p.N / 128);
+        const long long tp = (long long)((p.M + 255) / 256) * (p.N / 256) * n_seg, ts = (long long)((p.M + 127) / 128) * (p.N / 128) * n_seg;
         const long long gp = st->sm_count / 2, gs = st->sm_count;
         const long long pair_cost = ((tp + gp - 1) / gp) * 11, single_cost = ((ts + gs - 1) / gs) * 8;
-        if (pair_cost <= single_cost) return launch_gemm_shape<EPI, true>(st, ta, tw, tc, p, stream);
+        if (pair_cost <= single_cost) return launch_gemm_shape<EPI, true>(st, ta, maps, p, n_seg, stream);
     }
-    return launch_gemm_shape<EPI, false>(st, ta, tw, tc, p, stream);
+    return launch_gemm_shape<EPI, false>(st, ta, maps, p, n_seg, stream);
+}
+
+// shared body of kb_linear16 (one weight matrix) and kb_linear16_qkv (three, one launch)
+int linear16_segments(void* const* C, int ldc, const void* A, int lda, const void* const* W, int ldw, int n_seg, int M, int N, int K, int epi,
+                      const float* gate, const void* const* head_w, const int* rope_on, const float* rope_cos, const float* rope_sin,
+                      int rope_T, float eps, cudaStream_t stream) {
+    if (!A || M < 0 || N <= 0 || K <= 0 || n_seg < 1 || n_seg > 3) return KB_ERR_ARG;
+    if (epi < KB_EPI_F32 || epi > KB_EPI_HEADS16) return KB_ERR_ARG;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
+    if (rope_cos && rope_T <= 0) return KB_ERR_ARG;
+    if (epi != KB_EPI_RESID && gate) return KB_ERR_ARG;
+    const bool c32 = epi == KB_EPI_F32 || epi == KB_EPI_RESID;
+    if (!aligned16(A) || (lda & 7) || (ldw & 7) || (ldc & (c32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (gate && !aligned16(gate)) return KB_ERR_ALIGN;
+    if (rope_cos && (!aligned16(rope_cos) || !aligned16(rope_sin))) return KB_ERR_ALIGN;
+    bool any_rope = false;
+    for (int i = 0; i < n_seg; i++) {
+        if (!C[i] || !W[i]) return KB_ERR_ARG;
+        if (!aligned16(C[i]) || !aligned16(W[i]) || (head_w[i] && !aligned16(head_w[i]))) return KB_ERR_ALIGN;
+        if (epi != KB_EPI_HEADS16 && (head_w[i] || rope_on[i])) return KB_ERR_ARG;
+        any_rope = any_rope || rope_on[i];
+    }
+    if (any_rope && !rope_cos) return KB_ERR_ARG;
+    if ((N % 128) || (K % GB_K) || lda < K || ldw < K || ldc < N) return KB_ERR_SHAPE;
+    if (M == 0) return KB_OK;
+    DeviceState* st;
+    int rc;
+    if ((rc = get_state(&st))) return rc;
+    CUtensorMap ta;
+    GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    if ((rc = make_tmap_mat(&ta, A, M, K, lda))) return rc;
+    GemmParams p = {};
+    for (int i = 0; i < n_seg; i++) {
+        if ((rc = make_tmap_mat(&maps.w[i], W[i], N, K, ldw)) || (rc = make_tmap_out(&maps.c[i], C[i], M, N, ldc, c32, epi == KB_EPI_HEADS16))) return rc;
+        p.head_w[i] = static_cast<const __nv_bfloat16*>(head_w[i]);
+        p.rope_on[i] = rope_on[i] ? 1 : 0;
+    }
+    p.C = C[0]; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.gate = gate;
+    p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T > 0 ? rope_T : 1; p.eps = eps;
+    p.status = st->status;
+    switch (epi) {
+        case KB_EPI_F32: return launch_gemm<EPI_F32>(st, ta, maps, p, n_seg, stream);
+        case KB_EPI_F16: return launch_gemm<EPI_F16>(st, ta, maps, p, n_seg, stream);
+        case KB_EPI_GELU16: return launch_gemm<EPI_GELU16>(st, ta, maps, p, n_seg, stream);
+        case KB_EPI_RESID: return launch_gemm<EPI_RESID>(st, ta, maps, p, n_seg, stream);
+        default: return launch_gemm<EPI_HEADS16>(st, ta, maps, p, n_seg, stream);
+    }
 }
 
 }  // namespace
@@ -505,38 +556,22 @@ extern "C" {
 
 int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw, int M, int N, int K, int epi,
                 const float* gate, const void* head_w_bf16, const float* rope_cos, const float* rope_sin, int rope_T,
-                float eps, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!C || !A || !W || M < 0 || N <= 0 || K <= 0) return KB_ERR_ARG;
-    if (epi < KB_EPI_F32 || epi > KB_EPI_HEADS16) return KB_ERR_ARG;
-    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
-    if (rope_cos && rope_T <= 0) return KB_ERR_ARG;
+                float eps, void* stream) {
     if (epi != KB_EPI_HEADS16 && (head_w_bf16 || rope_cos)) return KB_ERR_ARG;
-    if (epi != KB_EPI_RESID && gate) return KB_ERR_ARG;
-    const bool c32 = epi == KB_EPI_F32 || epi == KB_EPI_RESID;
-    if (!aligned16(C) || !aligned16(A) || !aligned16(W) || (lda & 7) || (ldw & 7) || (ldc & (c32 ? 3 : 7))) return KB_ERR_ALIGN;
-    if (gate && !aligned16(gate)) return KB_ERR_ALIGN;
-    if (head_w_bf16 && !aligned16(head_w_bf16)) return KB_ERR_ALIGN;
-    if (rope_cos && (!aligned16(rope_cos) || !aligned16(rope_sin))) return KB_ERR_ALIGN;
-    if ((N % 128) || (K % GB_K) || lda < K || ldw < K || ldc < N) return KB_ERR_SHAPE;
-    if (M == 0) return KB_OK;
-    DeviceState* st;
-    int rc;
-    if ((rc = get_state(&st))) return rc;
-    CUtensorMap ta, tw, tc;
-    if ((rc = make_tmap_mat(&ta, A, M, K, lda)) || (rc = make_tmap_mat(&tw, W, N, K, ldw)) || (rc = make_tmap_out(&tc, C, M, N, ldc, c32, epi == KB_EPI_HEADS16))) return rc;
-    GemmParams p = {};
-    p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-    p.gate = gate; p.head_w = static_cast<const __nv_bfloat16*>(head_w_bf16);
-    p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T > 0 ? rope_T : 1; p.eps = eps;
-    p.status = st->status;
-    switch (epi) {
-        case KB_EPI_F32: return launch_gemm<EPI_F32>(st, ta, tw, tc, p, stream);
-        case KB_EPI_F16: return launch_gemm<EPI_F16>(st, ta, tw, tc, p, stream);
-        case KB_EPI_GELU16: return launch_gemm<EPI_GELU16>(st, ta, tw, tc, p, stream);
-        case KB_EPI_RESID: return launch_gemm<EPI_RESID>(st, ta, tw, tc, p, stream);
-        default: return launch_gemm<EPI_HEADS16>(st, ta, tw, tc, p, stream);
-    }
+    void* const cs[1] = {C};
+    const void* const ws[1] = {W};
+    const void* const hw[1] = {head_w_bf16};
+    const int rope_on[1] = {rope_cos != nullptr};
+    return linear16_segments(cs, ldc, A, lda, ws, ldw, 1, M, N, K, epi, gate, hw, rope_on, rope_cos, rope_sin, rope_T, eps,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear16_qkv(void* const* C3, int ldc, const void* A, int lda, const void* const* W3, int ldw, int M, int N, int K,
+                    const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
+                    float eps, void* stream) {
+    if (!C3 || !W3 || !head_w3 || !rope_on3) return KB_ERR_ARG;
+    return linear16_segments(C3, ldc, A, lda, W3, ldw, 3, M, N, K, KB_EPI_HEADS16, nullptr, head_w3, rope_on3, rope_cos, rope_sin, rope_T, eps,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int kb_status(unsigned* status_bits) {

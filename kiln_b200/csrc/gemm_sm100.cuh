@@ -46,13 +46,22 @@ struct GemmParams {
     int ldc;
     int M, N, K;
     int tiles_m, tiles_n;          // in tiles of the launched shape (256x256 for PAIR, 128x128 otherwise)
+    // Up to three weight matrices [N, K] share one launch (the q, k, v projections of one activation): column tile tn
+    // belongs to segment tn / tiles_n_seg, which has its own W and C tensor maps and its own head epilogue settings.
+    int tiles_n_seg;               // column tiles per segment (= tiles_n for a single matrix)
     const float* gate;             // EPI_RESID: C[r, c] += gate[c] * acc (null = 1)
-    const __nv_bfloat16* head_w;   // EPI_HEADS16: RMSNorm weight[128] or null
+    const __nv_bfloat16* head_w[3];   // EPI_HEADS16: RMSNorm weight[128] of the segment, or null
+    int rope_on[3];                // EPI_HEADS16: the segment's heads are rotated (tables below)
     const float* rope_cos;         // EPI_HEADS16: tables [rope_T, 64] or null; row r uses table row r % rope_T
     const float* rope_sin;
     int rope_T;
     float eps;
     uint32_t* status;
+};
+
+struct alignas(64) GemmMaps {
+    CUtensorMap w[3];              // per segment: the weight matrix, box 64 columns x 128 rows
+    CUtensorMap c[3];              // per segment: the output, box as the epilogue stores it
 };
 
 enum { GBAR_FULL = 0, GBAR_EMPTY = G_STAGES, GBAR_ACC_FULL = 2 * G_STAGES, GBAR_ACC_EMPTY = 2 * G_STAGES + 2, GBAR_COUNT = 2 * G_STAGES + 4 };
@@ -70,8 +79,7 @@ __device__ __forceinline__ void gemm_tile(int w, const GemmParams& p, int& tm, i
 
 template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
-              const GemmParams p) {
+gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ GemmMaps maps, const GemmParams p) {
     constexpr int BN = PAIR ? 256 : 128;                                  // accumulator columns per tile
     constexpr int TILE_M = PAIR ? 256 : 128;                              // tile rows over the CTA group
     constexpr bool OUT32 = (EPI == EPI_F32 || EPI == EPI_RESID);
@@ -103,7 +111,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         mbar_fence_init();
         fence_proxy_async_smem();
     }
-    if (warp == G_EPI_WARPS + 1 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmC); }
+    if (warp == G_EPI_WARPS + 1 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&maps.w[0]); tma_prefetch_desc(&maps.c[0]); }
     if (warp == G_EPI_WARPS) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);                       // two accumulator buffers
         tmem_relinquish();
@@ -131,24 +139,29 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             volatile uint32_t* const ok_buf = reinterpret_cast<volatile uint32_t*>(ctrl + 640) + quarter * 2;
             const int pair_bar = 1 + quarter;
             uint4 w0[4], w1[4];                                           // RMSNorm weights of this warp's 32 + 32 columns (bf16)
-            if (p.head_w) {
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    w0[q] = __ldg(reinterpret_cast<const uint4*>(p.head_w + hs * 32) + q);
-                    w1[q] = __ldg(reinterpret_cast<const uint4*>(p.head_w + 64 + hs * 32) + q);
-                }
-            }
+            int w_seg = -1;                                               // segment they belong to
             uint32_t use[2] = {0, 0};
             int k = 0;
             for (int w = group; w < n_tiles; w += n_groups, ++k) {
                 const int buf = k & 1;
                 int tm, tn;
                 gemm_tile(w, p, tm, tn);
-                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = tn * BN;
+                const int seg = tn / p.tiles_n_seg;
+                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = (tn - seg * p.tiles_n_seg) * BN;
                 const int row0 = m0 + quarter * 32;
                 const int nrow = p.M - row0;
+                const __nv_bfloat16* const head_w = seg == 0 ? p.head_w[0] : seg == 1 ? p.head_w[1] : p.head_w[2];
+                const bool rope = (seg == 0 ? p.rope_on[0] : seg == 1 ? p.rope_on[1] : p.rope_on[2]) != 0;
+                if (head_w && seg != w_seg) {                             // L1 hits after the first tile of a segment
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        w0[q] = __ldg(reinterpret_cast<const uint4*>(head_w + hs * 32) + q);
+                        w1[q] = __ldg(reinterpret_cast<const uint4*>(head_w + 64 + hs * 32) + q);
+                    }
+                    w_seg = seg;
+                }
                 float cr[32], sr[32];
-                if (p.rope_cos) {
+                if (rope) {
                     int tr = min(row0, p.M - 1) % p.rope_T;
 #pragma unroll
                     for (int rr = 0; rr < 32; rr++) {
@@ -186,7 +199,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                             else mbar_arrive(bar(GBAR_ACC_EMPTY + buf));
                         }
                     }
-                    if (p.head_w) {                                       // engine/src/kernels.cu:656-666
+                    if (head_w) {                                         // engine/src/kernels.cu:656-666
                         float ss = 0.f;
 #pragma unroll
                         for (int e = 0; e < 32; e++) ss = fmaf(x0[e], x0[e], fmaf(x1[e], x1[e], ss));
@@ -221,7 +234,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         const uint8_t* src = my_stage + rr * 256 + (lane & 3) * 4;
                         float a = *reinterpret_cast<const float*>(src + (((lane >> 2) ^ (rr & 15)) << 4));
                         float b = *reinterpret_cast<const float*>(src + (((8 + (lane >> 2)) ^ (rr & 15)) << 4));
-                        if (p.rope_cos) {                                 // engine/src/kernels.cu:769-771
+                        if (rope) {                                       // engine/src/kernels.cu:769-771
                             const float ra = a * cr[rr] - b * sr[rr];
                             b = b * cr[rr] + a * sr[rr];
                             a = ra;
@@ -238,8 +251,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     __syncwarp();
                     if (lane == 0 && nrow > 0) {
                         const int x = n0 + h * 128 + hs * 32;
-                        tma_store_3d(&tmC, smem_u32(my_stage), x, row0, 0);
-                        tma_store_3d(&tmC, smem_u32(my_stage) + 2048, x + 64, row0, 0);
+                        tma_store_3d(&maps.c[seg], smem_u32(my_stage), x, row0, 0);
+                        tma_store_3d(&maps.c[seg], smem_u32(my_stage) + 2048, x + 64, row0, 0);
                         tma_store_commit();
                     }
                 }
@@ -255,7 +268,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const int buf = k & 1;
                 int tm, tn;
                 gemm_tile(w, p, tm, tn);
-                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = tn * BN;
+                const int seg = tn / p.tiles_n_seg;
+                const int m0 = tm * TILE_M + (int)rank * GB_M, n0 = (tn - seg * p.tiles_n_seg) * BN;
                 const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(GBAR_ACC_FULL + buf), use[buf] & 1u, abort_flag));
                 ++use[buf];
                 if (!ok) break;                                               // warps are independent from here on
@@ -318,11 +332,11 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     if (lane == 0 && nrow > 0) {
                         const int x = n0 + ch * CW, y = m0 + quarter * 32;
                         if constexpr (EPI == EPI_RESID) {
-                            tma_reduce_add_3d(&tmC, smem_u32(my_stage), x, y, 0);
-                            tma_reduce_add_3d(&tmC, smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
+                            tma_reduce_add_3d(&maps.c[seg], smem_u32(my_stage), x, y, 0);
+                            tma_reduce_add_3d(&maps.c[seg], smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
                         } else {
-                            tma_store_3d(&tmC, smem_u32(my_stage), x, y, 0);
-                            tma_store_3d(&tmC, smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
+                            tma_store_3d(&maps.c[seg], smem_u32(my_stage), x, y, 0);
+                            tma_store_3d(&maps.c[seg], smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
                         }
                         tma_store_commit();
                     }
@@ -375,7 +389,9 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             for (int w = group; w < n_tiles && good; w += n_groups) {
                 int tm, tn;
                 gemm_tile(w, p, tm, tn);
-                const int m0 = tm * TILE_M + (int)rank * GB_M, wrow0 = tn * BN + (int)rank * 128;
+                const int seg = tn / p.tiles_n_seg;
+                const CUtensorMap* const tmW = &maps.w[seg];
+                const int m0 = tm * TILE_M + (int)rank * GB_M, wrow0 = (tn - seg * p.tiles_n_seg) * BN + (int)rank * 128;
                 for (int ks = 0; ks < ksteps && good; ++ks, ++ring) {
                     const uint32_t st = ring % G_STAGES;
                     good = mbar_wait(bar(GBAR_EMPTY + st), ((ring / G_STAGES) & 1u) ^ 1u, abort_flag);
@@ -386,11 +402,11 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         if (rank == 0) mbar_expect_tx(bar(GBAR_FULL + st), 2 * G_STAGE_BYTES);
                         const uint32_t fb = mapa_u32(bar(GBAR_FULL + st), 0);
                         tma_load_3d_pair(a_s, &tmA, fb, ks * GB_K, m0, 0);
-                        tma_load_3d_pair(a_s + GB_M * GB_K * 2, &tmW, fb, ks * GB_K, wrow0, 0);
+                        tma_load_3d_pair(a_s + GB_M * GB_K * 2, tmW, fb, ks * GB_K, wrow0, 0);
                     } else {
                         mbar_expect_tx(bar(GBAR_FULL + st), G_STAGE_BYTES);
                         tma_load_3d(a_s, &tmA, bar(GBAR_FULL + st), ks * GB_K, m0, 0);
-                        tma_load_3d(a_s + GB_M * GB_K * 2, &tmW, bar(GBAR_FULL + st), ks * GB_K, wrow0, 0);
+                        tma_load_3d(a_s + GB_M * GB_K * 2, tmW, bar(GBAR_FULL + st), ks * GB_K, wrow0, 0);
                     }
                 }
             }

@@ -80,6 +80,19 @@ void linear16_heads(__half* y, int ldy, const __half* x16, int T, const Weight16
           "linear16_heads");
 }
 
+void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, int T, const Weight16& Wq, const Weight16& Wk,
+                  const Weight16& Wv, const uint16_t* qn_w_bf16, const uint16_t* kn_w_bf16, const float* rope_cos, const float* rope_sin,
+                  int rope_T, float eps) {
+    if (Wq.rows % 128 || Wq.cols % 64 || Wk.rows != Wq.rows || Wv.rows != Wq.rows || Wk.cols != Wq.cols || Wv.cols != Wq.cols)
+        throw std::runtime_error("linear16_qkv: the three weights must share one tensor-core eligible shape");
+    void* const C3[3] = {q, k, v};
+    const void* const W3[3] = {Wq.p, Wk.p, Wv.p};
+    const void* const hw3[3] = {qn_w_bf16, kn_w_bf16, nullptr};
+    const int rope3[3] = {rope_cos != nullptr, rope_cos != nullptr, 0};
+    check(kb_linear16_qkv(C3, ldy, x16, Wq.cols, W3, Wq.cols, T, Wq.rows, Wq.cols, hw3, rope3, rope_cos, rope_sin, rope_T, eps, g_ctx.stream),
+          "linear16_qkv");
+}
+
 }  // namespace kiln_b200
 
 // C trampolines so the shim can be exercised from the test-suite without a C++ test runner:

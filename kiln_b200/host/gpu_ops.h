@@ -64,4 +64,10 @@ void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi
 void linear16_heads(__half* y, int ldy, const __half* x16, int T, const Weight16& W, const uint16_t* norm_w_bf16,
                     const float* rope_cos, const float* rope_sin, int rope_T, float eps);
 
+// the three linear16_heads / linear16 calls of a block's q, k, v projections in one launch (outputs fp16 [T, ldy]; q and k
+// normalised with their own weights and rotated, v plain)
+void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, int T, const Weight16& Wq, const Weight16& Wk,
+                  const Weight16& Wv, const uint16_t* qn_w_bf16, const uint16_t* kn_w_bf16, const float* rope_cos, const float* rope_sin,
+                  int rope_T, float eps);
+
 }  // namespace kiln_b200

@@ -49,6 +49,8 @@ def lib():
         L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
         L.kb_linear16.restype = i
         L.kb_linear16.argtypes = [vp, i, vp, i, vp, i, i, i, i, i, vp, vp, vp, vp, i, f, vp]
+        L.kb_linear16_qkv.restype = i
+        L.kb_linear16_qkv.argtypes = [ctypes.POINTER(vp), i, vp, i, ctypes.POINTER(vp), i, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), vp, vp, i, f, vp]
         L.kb_status.restype = i
         L.kb_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         ull = ctypes.c_ulonglong
@@ -192,6 +194,20 @@ def linear16(C, A, W, epi, gate=None, head_w=None, rope_cos=None, rope_sin=None,
     _check(lib().kb_linear16(_ptr(C), _ld(C), _ptr(A), _ld(A), _ptr(W), _ld(W), M, N, K, epi, _ptr(gate), _ptr(head_w),
                              _ptr(rope_cos), _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16")
     return C
+
+
+def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, False), rope_cos=None, rope_sin=None, eps=1e-6):
+    """Three projections of one activation in one launch: Cs[i] = heads16(A @ Ws[i].T), fp16; see kb_linear16_qkv."""
+    M, K = A.shape
+    N = Ws[0].shape[0]
+    vp3 = ctypes.c_void_p * 3
+    arr = lambda ts: vp3(*[None if t is None else t.data_ptr() for t in ts])
+    on = (ctypes.c_int * 3)(*[int(bool(r) and rope_cos is not None) for r in rope_on])
+    rope_T = rope_cos.shape[0] if rope_cos is not None else 0
+    assert all(_ld(c) == _ld(Cs[0]) for c in Cs) and all(_ld(w) == _ld(Ws[0]) for w in Ws)
+    _check(lib().kb_linear16_qkv(arr(Cs), _ld(Cs[0]), _ptr(A), _ld(A), arr(Ws), _ld(Ws[0]), M, N, K, arr(head_ws), on, _ptr(rope_cos),
+                                 _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16_qkv")
+    return Cs
 
 
 def check_status():

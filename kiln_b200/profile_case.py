@@ -147,6 +147,11 @@ def linear_cases(a):
         kb.attn_self(o16, q16, k16, v16, 1, T, H)
         ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
 
+    def fused_one_launch():
+        ops.linear16_qkv([q16, k16, v16], x, [wq, wk, wv], head_ws=(hw, hw, None), rope_on=(True, True, False), rope_cos=cos, rope_sin=sin)
+        kb.attn_self(o16, q16, k16, v16, 1, T, H)
+        ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
+
     def engine_order():
         ops.linear16(q32, x, wq, ops.EPI_F32)
         ops.linear16(k32, x, wk, ops.EPI_F32)
@@ -155,7 +160,7 @@ def linear_cases(a):
         ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
 
     flop = 4.0 * T * T * 128 * H + 4 * 2.0 * T * D * D
-    for name, fn in (("fused head epilogue", fused), ("engine order", engine_order)):
+    for name, fn in (("q, k, v in one launch", fused_one_launch), ("fused head epilogue", fused), ("engine order", engine_order)):
         us = timed(fn, a.warm, a.reps)
         assert kb.check_status() == 0
         print(f"case=block tokens={T} heads={H} [{name}]: {us:.1f} us/block-half, {flop / us / 1e6:.1f} TFLOP/s")

@@ -222,3 +222,41 @@ def test_edge_shapes_every_epilogue(kb, M, N, K):
     # fp32 summation order and one fp16 rounding are the only differences: a one-ulp disagreement is the worst case
     assert not np.isnan(out).any()
     assert np.all(np.abs(out - ref) <= 2.0 ** -10 * np.abs(ref) + 1e-4), f"{M}x{N}x{K} heads16: {np.abs(out - ref).max():.3e}"
+
+
+@pytest.mark.parametrize("M,H,K", [(300, 2, 128), (333, 3, 192), (4096, 16, 2048)], ids=["pair_tiles", "single_tiles", "dit_size"])
+def test_qkv_one_launch_equals_three_calls(kb, M, H, K):
+    """kb_linear16_qkv: q and k with their own norm weights and RoPE, v plain — bit-identical to three kb_linear16 calls."""
+    from kiln_b200 import ops
+    N = H * 128
+    side = int(np.sqrt(M))
+    dx = dev(seeded(300, M, K, "f16"), "f16")
+    ws = [dev(seeded(301 + i, N, K, "f16", 1.0 / np.sqrt(K)), "f16") for i in range(3)]
+    nws = [dev(oracle.round16(1.0 + 0.05 * oracle.randn(310 + i, 128), 1)).to(torch.bfloat16) for i in range(2)]
+    cos, sin = (dev(a) for a in oracle.cosmos_rope(side, side))          # table shorter than M: rows wrap
+    one = [torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16) for _ in range(3)]
+    ops.linear16_qkv(one, dx, ws, head_ws=(nws[0], nws[1], None), rope_on=(True, True, False), rope_cos=cos, rope_sin=sin)
+    three = [torch.empty((M, N), device="cuda", dtype=torch.float16) for _ in range(3)]
+    ops.linear16(three[0], dx, ws[0], ops.EPI_HEADS16, head_w=nws[0], rope_cos=cos, rope_sin=sin)
+    ops.linear16(three[1], dx, ws[1], ops.EPI_HEADS16, head_w=nws[1], rope_cos=cos, rope_sin=sin)
+    ops.linear16(three[2], dx, ws[2], ops.EPI_F16)
+    assert kb.check_status() == 0
+    for i in range(3):
+        assert torch.equal(one[i], three[i]), f"projection {i} differs from its own launch"
+
+
+def test_qkv_argument_errors(kb):
+    import ctypes
+    L = kb.lib()
+    a = torch.zeros((128, 128), device="cuda", dtype=torch.float16)
+    vp3 = ctypes.c_void_p * 3
+    ptrs = vp3(a.data_ptr(), a.data_ptr(), a.data_ptr())
+    none3 = vp3(None, None, None)
+    on = (ctypes.c_int * 3)(1, 1, 0)
+    off = (ctypes.c_int * 3)(0, 0, 0)
+    args = lambda C=ptrs, W=ptrs, hw=none3, r=off, cos=None: (C, 128, ctypes.c_void_p(a.data_ptr()), 128, W, 128, 128, 128, 128, hw, r, cos, cos, 128, 1e-6, None)
+    assert L.kb_linear16_qkv(*args()) == 0
+    assert L.kb_linear16_qkv(*args(r=on)) == -1                                   # RoPE asked for without tables
+    assert L.kb_linear16_qkv(*args(W=vp3(a.data_ptr(), None, a.data_ptr()))) == -1
+    assert L.kb_linear16_qkv(*args(C=vp3(a.data_ptr(), a.data_ptr() + 2, a.data_ptr()))) == -2
+    assert kb.check_status() == 0
