@@ -70,6 +70,14 @@ int set_smem(K kernel) {
     return KB_OK;
 }
 
+template <int EPI>
+int set_gemm_smem() {
+    if (cudaFuncSetAttribute(gemm16_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm16_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess)
+        return KB_ERR_CUDA;
+    return KB_OK;
+}
+
 int init_device(DeviceState& st, int dev) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return KB_ERR_DEVICE;
@@ -90,6 +98,9 @@ int init_device(DeviceState& st, int dev) {
     if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>))) return rc;
+    if ((rc = set_gemm_smem<EPI_F32>()) || (rc = set_gemm_smem<EPI_F16>()) || (rc = set_gemm_smem<EPI_GELU16>()) ||
+        (rc = set_gemm_smem<EPI_RESID>()) || (rc = set_gemm_smem<EPI_HEADS16>()))
+        return rc;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return KB_ERR_CUDA;
     st.status = static_cast<unsigned int*>(p);
@@ -461,13 +472,6 @@ int make_tmap_mat(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) 
 // p.N is the width of ONE segment; the launch covers n_seg of them side by side
 template <int EPI, bool PAIR>
 int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const GemmMaps& maps, GemmParams p, int n_seg, cudaStream_t stream) {
-    static bool smem_set[MAX_DEVICES] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!smem_set[dev]) {
-        if (cudaFuncSetAttribute(gemm16_kernel<EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess) return KB_ERR_CUDA;
-        smem_set[dev] = true;
-    }
     const int tile = PAIR ? 256 : 128, per_group = PAIR ? 2 : 1;
     p.tiles_m = (p.M + tile - 1) / tile;
     p.tiles_n_seg = p.N / tile;
