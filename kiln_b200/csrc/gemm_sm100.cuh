@@ -6,16 +6,18 @@
 // loads its own 128 rows of A and 128 of the 256 W rows per 64-wide k step (32 KiB) and keeps its 128x256 half of the
 // accumulator, so a CTA moves half the shared-memory bytes per flop of the single-CTA shape. That matters because
 // measured on B200 a 128x128 single-CTA tile is bound by shared-memory bandwidth (TMA writes plus operand reads,
-// about 100 B/clk/SM), not by the tensor pipe. Single: one CTA per 128x128 tile, for N not a multiple of 256 or M <= 128.
+// about 100 B/clk/SM), not by the tensor pipe. Single: one CTA per 128x128 tile, for N not a multiple of 256, M <= 128,
+// or when the pair shape would fill the device worse (the host decides).
 //
 // It takes the place of the reference's fp16-activation GEMM tc16::k_gemm16 (engine/src/tcgemm16.cuh:57-175,
 // host wrapper linear16 at engine/src/kernels.cu:559-609) with its four epilogues — fp32 store, fp16 store,
 // fp16 GELU, gated add into the fp32 residual stream (engine/src/tcgemm16.cuh:145-174) — and adds a fifth that the
 // attention path wants: EPI_HEADS16 treats every 128 output columns as one attention head and applies the
 // per-head RMSNorm (engine/src/kernels.cu:656-666) and rotate-half RoPE (engine/src/kernels.cu:759-772) to the
-// accumulator row before storing fp16. A thread of the epilogue owns one token row of one head (tcgen05.ld
-// 32x32b), so both are thread-local. With it the Q and K projections emit exactly what the attention kernel
-// consumes, and the separate rmsnorm / rope_half launches and the staging pre-pass disappear.
+// accumulator row before storing fp16 (how the epilogue warps share that work is described at the code). With it the
+// Q and K projections emit exactly what the attention kernel consumes, and the separate rmsnorm / rope_half launches
+// and the staging pre-pass disappear. Up to three weight matrices can share one launch (q, k, v of one activation).
+// Outputs leave through TMA stores, the residual epilogue through a TMA reduce-add.
 // (The reference accumulates each 32-wide k tile in fp16 before flushing to fp32; here every product is
 // accumulated in fp32.)
 #pragma once
@@ -24,7 +26,7 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
-#include "attn_sm100.cuh"   // pack16, store32, ST_TIMEOUT
+#include "attn_sm100.cuh"   // pack16, ST_TIMEOUT
 #include "ptx.cuh"
 
 namespace kb {
