@@ -328,6 +328,8 @@ def run_all_configs(args):
     dev = "cuda"
     ref_path = os.path.join(ROOT, "oracle", "_ref", "libkiln_ref.so")
     R = ctypes.CDLL(ref_path) if os.path.exists(ref_path) else None
+    if R is not None:
+        R.kref_time_tfa_f16.restype = ctypes.c_float
     P = lambda t: ctypes.c_void_p(t.data_ptr())
     cf = ctypes.c_float
     sustained, burst, hbm, src = read_peaks()
@@ -347,6 +349,27 @@ def run_all_configs(args):
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps * 1e3                 # us
+
+    def graph_us(fn, n=20, replays=5):
+        """Per-call device time with the host out of the picture: n calls captured in one CUDA graph, replayed."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn(0)                                               # attributes, status word: before the capture
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(n):
+                    fn(i)
+            g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            side.synchronize()
+            e0.record(side)
+            for _ in range(replays):
+                g.replay()
+            e1.record(side)
+            side.synchronize()
+        torch.cuda.current_stream().wait_stream(side)
+        return e0.elapsed_time(e1) / (n * replays) * 1e3        # us
 
     def errs(out, ref):
         d = np.abs(out.astype(np.float64) - ref.astype(np.float64))
@@ -374,13 +397,14 @@ def run_all_configs(args):
         k_ms, k_n = kb.prof_read(kb.PROF_ATTENTION)
         s_ms, s_n = kb.prof_read(kb.PROF_NORM_ROPE)
         kb.prof_enable(False)
+        g_us = graph_us(lambda i: kb.attn_cross(out, *sets[i % NSET], Tq, Tk, npad, H, workspace=ws))
         out32 = torch.empty(Tq, D, device=dev, dtype=torch.float32)
         kb.attn_cross(out32, *sets[0], Tq, Tk, npad, H, workspace=ws)
         assert kb.check_status() == 0
         rows = rows_sample(Tq)
         ref = oracle.attention(q[rows], k[:Tk], v[:Tk], H, npad)
         rec = {"case": name, "dtype": "f16" if kind == 0 else "bf16", "Tq": Tq, "Tk": Tk, "npad": npad, "ours_us": us,
-               "ours_kernel_us": k_ms / k_n * 1e3, "ours_staging_us": (s_ms / s_n * 1e3) if s_n else 0.0,
+               "ours_kernel_us": k_ms / k_n * 1e3, "ours_staging_us": (s_ms / s_n * 1e3) if s_n else 0.0, "ours_graph_us": g_us,
                "ours_tflops": flop / us / 1e6, "frac_of_burst_peak": flop / us / 1e6 / burst,
                "hbm_gbs": (2 * Tq + 2 * Tk) * D * 2 / us / 1e3, "err_fp32_out": errs(out32.cpu().numpy()[rows], ref),
                "err_16bit_out": errs(out.float().cpu().numpy()[rows], ref)}
@@ -388,7 +412,10 @@ def run_all_configs(args):
             f32 = [tuple(t.float() for t in st) for st in sets[:2]]
             o16 = torch.empty(Tq, D, device=dev, dtype=torch.float16)
             rus = timed(lambda i: R.kref_tfa_f16(P(o16), D, P(f32[i % 2][0]), D, P(f32[i % 2][1]), D, P(f32[i % 2][2]), D, Tq, Tk, H, npad), reps=10)
+            # both without host cost: ours replayed from a CUDA graph, the reference kernel launched back to back from C
+            rloop = R.kref_time_tfa_f16(P(o16), D, P(f32[0][0]), D, P(f32[0][1]), D, P(f32[0][2]), D, Tq, Tk, H, npad, 3, 20) * 1e3
             rec.update({"reference_tfa_us": rus, "reference_tfa_tflops": flop / rus / 1e6, "speedup_vs_reference_kernel": rus / us,
+                        "reference_tfa_loop_us": rloop, "speedup_device_time": rloop / g_us,
                         "reference_tfa_err": errs(o16.float().cpu().numpy()[rows], ref)})
         emit(rec)
 
