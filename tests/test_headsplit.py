@@ -107,6 +107,32 @@ def test_push_epilogue_two_peer_buffers_on_one_gpu(built_lib):
 
 
 @pytest.mark.gpu
+def test_bounded_wait_runs_out_and_is_reported(built_lib):
+    """Failure detection without a GPU fault: a wait for arrivals that never come gives up at its limit (2 s), the kernel
+    returns normally with the time-out bit in the device status word, kb_status reports KB_ERR_TIMEOUT once and clears it,
+    and the context stays usable (the next attention call is correct)."""
+    import time
+    import kiln_b200 as kb
+    from kiln_b200.ops import KilnError
+    assert kb.lib().kb_init() == 0
+    assert kb.check_status() == 0
+    ctr = torch.zeros(1, dtype=torch.int64, device="cuda")             # nothing will ever bump it
+    t0 = time.time()
+    kb.wait_arrivals(ctr.data_ptr(), 1)
+    with pytest.raises(KilnError) as ei:
+        kb.check_status()
+    assert ei.value.code == -7                                           # KB_ERR_TIMEOUT
+    assert 1.5 < time.time() - t0 < 10.0, "the wait must end at its own limit"
+    assert kb.check_status() == 0                                        # read and cleared
+    T, H = 200, 2
+    q, k, v = (oracle.round16(oracle.randn(900 + i, T * H * 128), 0).reshape(T, H * 128) for i in range(3))
+    out = torch.empty(T, H * 128, device="cuda", dtype=torch.float32)
+    kb.attn_self(out, dev(q, "f16"), dev(k, "f16"), dev(v, "f16"), 1, T, H)
+    assert kb.check_status() == 0
+    assert_close(out.cpu().numpy(), oracle.attention(q, k, v, H), "attention after a reported time-out")
+
+
+@pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_headsplit_two_gpus_torchrun(built_lib):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
