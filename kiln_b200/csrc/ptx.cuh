@@ -182,19 +182,6 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ uint32_t cluster_nctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-    return r;
-}
-// read one float from the same shared-memory offset in CTA `rank` of this cluster
-__device__ __forceinline__ float dsmem_ld_f32(uint32_t local_saddr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_saddr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
 
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a cluster (ranks 2i and 2i+1) run one MMA of twice the height: each holds its 128 rows of A, half of the
