@@ -1,6 +1,7 @@
 // Implementation of the engine-facing op set over the C ABI (see gpu_ops.h for the reference citations).
 #include "gpu_ops.h"
 
+#include <chrono>
 #include <stdexcept>
 #include <string>
 
@@ -135,5 +136,16 @@ int kbh_linear16(void* y, int ldy, const void* x16, int T, const void* w16, int 
         if (a.epi == 4) kiln_b200::linear16_heads((__half*)a.y, a.ldy, (const __half*)a.x, a.T, W, a.nw, a.c, a.s, a.rope_T, a.eps);
         else kiln_b200::linear16(a.y, a.ldy, (const __half*)a.x, a.T, W, (kiln_b200::Epi16)a.epi, a.gate);
     }, &a);
+}
+// Host cost of enqueueing one fp16 cross-attention call through the C ABI (argument checks, four tensor-map encodes, one
+// launch), in microseconds: wall clock around n back-to-back calls that are not waited for, then one synchronise.
+double kbh_enqueue_cost_us(void* out, const void* q, const void* k, const void* v, int Tq, int Tk, int npad, int H, int n) {
+    const int ld = H * 128;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < n; i++)
+        if (kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, npad, H, ld, ld, ld, ld, KB_F16, KB_F16, 1e-6f, nullptr, 0, nullptr) != KB_OK) return -1.0;
+    const auto t1 = std::chrono::steady_clock::now();
+    cudaStreamSynchronize(nullptr);
+    return std::chrono::duration<double, std::micro>(t1 - t0).count() / n;
 }
 }

@@ -94,3 +94,19 @@ def test_linear16_epilogues_and_heads(shim):
     assert_close(y.float().cpu().numpy(), oracle.linear_heads16(x, w, H, bits, cos, sin), "shim linear16_heads")
     assert shim.kbh_linear16(P(y), N, P(dx), M, P(dw), 192, K, 1, None, None, None, None, 0, f(0), err, 256) == -1
     assert b"eligible" in err.value
+
+
+def test_enqueue_cost_from_cpp(shim):
+    """Host cost of one call from C++ (no Python in the loop): printed with -s; the bound only guards against regressions
+    of an order of magnitude (a DiT step makes ~100 calls of 30-150 us of device time each)."""
+    Tq, Tk, H = 1536, 64, 16
+    q = torch.randn(Tq, H * 128, device="cuda").half()
+    k = torch.randn(Tk, H * 128, device="cuda").half()
+    v = torch.randn(Tk, H * 128, device="cuda").half()
+    out = torch.empty_like(q)
+    shim.kbh_enqueue_cost_us.restype = ctypes.c_double
+    shim.kbh_enqueue_cost_us.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5
+    shim.kbh_enqueue_cost_us(P(out), P(q), P(k), P(v), Tq, Tk, 0, H, 20)                  # warm-up
+    us = shim.kbh_enqueue_cost_us(P(out), P(q), P(k), P(v), Tq, Tk, 0, H, 200)
+    print(f"\nhost cost per kb_attn_cross call from C++: {us:.2f} us (200 calls, device time ~8 us each)")
+    assert 0 < us < 100
