@@ -156,6 +156,8 @@ int check_out(const void* p, int ld, int H, int out_dtype) {
 // Collects the tensors one launch of the pre-pass stages.
 struct PrepBatch {
     PrepParams pp = {};
+    // words the pre-pass clears on the way (arrival counters / flags the attention kernel expects at zero)
+    void zero(unsigned int* ptr, int n) { pp.zero_ptr = ptr; pp.zero_n = n; }
     void add(void* out, int ld_out, const void* in, int ld_in, int rows, int T, const void* w, const float* c, const float* s) {
         PrepSeg& sg = pp.seg[pp.nseg++];
         sg.in = in; sg.out = out; sg.w = static_cast<const __nv_bfloat16*>(w); sg.cos_t = c; sg.sin_t = s;
@@ -166,7 +168,11 @@ struct PrepBatch {
 };
 
 int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtype, cudaStream_t stream) {
-    if (pb.pp.blocks == 0) return KB_OK;
+    if (pb.pp.blocks == 0) {
+        // nothing to stage: the words still have to be cleared before the attention kernel starts
+        if (pb.pp.zero_n > 0 && cudaMemsetAsync(pb.pp.zero_ptr, 0, (size_t)pb.pp.zero_n * sizeof(unsigned int), stream) != cudaSuccess) return KB_ERR_CUDA;
+        return KB_OK;
+    }
     ProfScope ps(st, KB_PROF_NORM_ROPE, stream);
     const unsigned grid = pb.pp.blocks;
 #define KB_PREP(IN, OUT) qk_prep_kernel<IN, OUT><<<grid, 256, 0, stream>>>(pb.pp)
@@ -191,13 +197,14 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
     // persistent kernel: one CTA per SM (its shared memory and TMEM fill an SM) walks the work items
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
-    cfg.gridDim = dim3((unsigned)(p.n_items < sm_count ? p.n_items : sm_count), 1, 1);
+    cfg.gridDim = dim3((unsigned)((p.split || p.n_items >= sm_count) ? sm_count : p.n_items), 1, 1);
     cfg.dynamicSmemBytes = ATTN_SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = 0;
-    if (MODE == MODE_NAG) {
-        // the CTAs holding the heads of one query tile wait for each other: all CTAs must be resident at once
+    if (MODE == MODE_NAG || p.split) {
+        // the CTAs holding the heads of one query tile (NAG) or the parts of a cut item (split) wait for each other:
+        // all CTAs must be resident at once
         attr[0].id = cudaLaunchAttributeCooperative;
         attr[0].val.cooperative = 1;
         cfg.attrs = attr;
@@ -254,6 +261,27 @@ struct PeerSpec {
     int n_peers, col0;
 };
 
+constexpr int MAX_HEADS = 4096;   // keeps every byte count below in range
+
+// fp16 staging bytes of one attention call (the part of the workspace the pre-pass writes)
+size_t staging_bytes(size_t rows_q, size_t rows_k, int n_ctx, int H, int dtype, bool norm_q, bool norm_k) {
+    const bool conv = dtype != KB_F16;
+    size_t n = 0;
+    if (conv || norm_q) n += align256(rows_q * H * 128 * 2);
+    if (conv || norm_k) n += (size_t)n_ctx * align256(rows_k * H * 128 * 2);   // K of every context
+    if (conv) n += (size_t)n_ctx * align256(rows_k * H * 128 * 2);             // V of every context
+    return n;
+}
+
+// Balanced (item, key block) ranges per SM against whole items per SM, in key-block steps on the slowest SM.
+bool split_pays(int n_items, int nb, int sm_count) {
+    const long long steps = (long long)n_items * nb;
+    if (nb < 2 || steps < 2LL * sm_count) return false;
+    const long long whole = (long long)((n_items + sm_count - 1) / sm_count) * nb;
+    const long long balanced = (steps + sm_count - 1) / sm_count + 2;
+    return balanced < whole;
+}
+
 // shared body of self- and cross-attention: q [B*Tq], k/v [B*Tk]
 int attn_pair(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
               const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk, int npad, int H, int ld_q, int ld_k,
@@ -271,6 +299,9 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
         out = peers->out_peers[0];
     }
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
+    if (H > MAX_HEADS) return KB_ERR_SHAPE;
+    // the pre-pass reads norm weights and RoPE tables with 16-byte vector loads
+    if (!aligned16(qn_w) || !aligned16(kn_w) || !aligned16(rope_cos) || !aligned16(rope_sin)) return KB_ERR_ALIGN;
     int rc;
     if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k, ld_k, H, dtype)) || (rc = check_mat(v, ld_v, H, dtype)) ||
         (rc = check_out(out, ld_o, H, out_dtype)))
@@ -290,16 +321,29 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     if (stage_k) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, k, ld_k, B * Tk, Tk, kn_w, rope_cos, rope_sin); kk = d; ldk = H * 128; }
     if (stage_v) { void* d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, v, ld_v, B * Tk, Tk, nullptr, nullptr, nullptr); vv = d; ldv = H * 128; }
     if (sg.overflow) return KB_ERR_WORKSPACE;
-    if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
-    CUtensorMap tq, tk, tv;
-    if ((rc = make_tmap(&tq, qq, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, Tk, H, B, ldk)) || (rc = make_tmap(&tv, vv, Tk, H, B, ldv)))
-        return rc;
     AttnParams p = {};
     p.out = out; p.ldo = ld_o; p.Tq = Tq; p.H = H; p.B = B;
     p.Tk[0] = Tk; p.Tk[1] = 0; p.npad[0] = npad; p.npad[1] = 0;
     p.n_items = ((Tq + 2 * BM - 1) / (2 * BM)) * H * B;
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
+    // Balanced schedule: worth it when equal (item, key block) ranges per SM beat whole items per SM by more than the
+    // cost of writing and merging the cut items' partial results (about two key blocks), and the workspace has room for
+    // those partial results; otherwise every CTA takes whole items.
+    if (split_pays(p.n_items, (Tk + BN - 1) / BN, st->sm_count) && workspace && aligned16(workspace)) {
+        Stage trial = sg;
+        float* part = static_cast<float*>(trial.take_bytes((size_t)st->sm_count * PART_CTA_BYTES));
+        unsigned int* flags = static_cast<unsigned int*>(trial.take_bytes((size_t)st->sm_count * 2 * sizeof(unsigned int)));   // one per SM and stream
+        if (!trial.overflow) {
+            sg = trial;
+            p.split = 1; p.part = part; p.part_flag = flags;
+            pb.zero(flags, st->sm_count * 2);
+        }
+    }
+    if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
+    CUtensorMap tq, tk, tv;
+    if ((rc = make_tmap(&tq, qq, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, Tk, H, B, ldk)) || (rc = make_tmap(&tv, vv, Tk, H, B, ldv)))
+        return rc;
     if (peers) {
         p.n_peers = peers->n_peers;
         p.col0 = peers->col0;
@@ -339,14 +383,18 @@ int kb_init(void) {
 }
 
 size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int n_ctx, int H, int dtype, int norm_q, int norm_k) {
-    const bool conv = dtype != KB_F16;
-    size_t n = 0;
-    if (conv || norm_q) n += align256((size_t)rows_q * H * 128 * 2);
-    if (conv || norm_k) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);   // K of every context
-    if (conv) n += (size_t)n_ctx * align256((size_t)rows_k * H * 128 * 2);             // V of every context
+    if (rows_q < 0 || rows_k < 0 || H <= 0 || H > MAX_HEADS || n_ctx < 1) return 0;
+    size_t n = staging_bytes((size_t)rows_q, (size_t)rows_k, n_ctx, H, dtype, norm_q != 0, norm_k != 0);
     if (n_ctx == 2) {                                                                  // NAG: per-head norm partials and arrival counters
         const size_t n_qt = ((size_t)rows_q + 127) / 128;
         n += align256(n_qt * H * 256 * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+    } else {
+        // room for the balanced schedule's partial results (one slot and one flag per SM); a smaller workspace still works,
+        // the call then runs whole items per SM
+        int sms = 148;
+        DeviceState* st;
+        if (get_state(&st) == KB_OK) sms = st->sm_count;
+        n += align256((size_t)sms * PART_CTA_BYTES) + align256((size_t)sms * 2 * sizeof(unsigned int));
     }
     return n;
 }
@@ -373,6 +421,7 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (Tq <= 0 || Tk_pos <= 0 || Tk_neg <= 0 || H <= 0 || npad_pos < 0 || npad_neg < 0) return KB_ERR_ARG;
     if (H > 64) return KB_ERR_SHAPE;                   // the heads of a query tile run on H different SMs at once
+    if (!aligned16(qn_w)) return KB_ERR_ALIGN;         // read with 16-byte vector loads by the pre-pass
     int rc;
     if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k_pos, ld_kv, H, dtype)) || (rc = check_mat(v_pos, ld_kv, H, dtype)) ||
         (rc = check_mat(k_neg, ld_kv, H, dtype)) || (rc = check_mat(v_neg, ld_kv, H, dtype)) || (rc = check_out(out, ld_o, H, out_dtype)))
@@ -386,8 +435,8 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     float* nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * 256 * sizeof(float)));
     unsigned int* nag_flag = static_cast<unsigned int*>(sg.take_bytes((size_t)n_qt * sizeof(unsigned int)));
     if (sg.overflow) return KB_ERR_WORKSPACE;
-    if (cudaMemsetAsync(nag_flag, 0, (size_t)n_qt * sizeof(unsigned int), stream) != cudaSuccess) return KB_ERR_CUDA;
     PrepBatch pb;
+    pb.zero(nag_flag, n_qt);                           // cleared by the pre-pass, or by a memset when nothing is staged
     pb.pp.H = H; pb.pp.eps = eps;
     const void* qq = q;
     const void* kv[4] = {k_pos, v_pos, k_neg, v_neg};
@@ -429,6 +478,7 @@ int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, 
     if (out_dtype == KB_F32 && in_dtype != KB_F32) return KB_ERR_ARG;
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
     if (!aligned16(out) || !aligned16(in) || (ld_out & (out_dtype == KB_F32 ? 3 : 7)) || (ld_in & (in_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (!aligned16(w_bf16) || !aligned16(rope_cos) || !aligned16(rope_sin)) return KB_ERR_ALIGN;   // 16-byte vector loads
     if (ld_out < H * 128 || ld_in < H * 128) return KB_ERR_SHAPE;
     DeviceState* st;
     int rc;
@@ -728,8 +778,10 @@ int kb_attn_self_static(void* out, const void* q, const void* k, const void* v, 
                         const float* rope_cos, const float* rope_sin, int B, int T, int H, int ld_q, int ld_k, int ld_v, int ld_o,
                         int dtype, int out_dtype, float eps, void* stream) {
     if (!valid_in_dtype(dtype) || B <= 0 || T <= 0 || H <= 0) return KB_ERR_ARG;
+    if (H > MAX_HEADS) return KB_ERR_SHAPE;
     if ((long long)B * T > (long long)KB_STATIC_SCRATCH_BYTES) return KB_ERR_STATIC_SCRATCH;   // keeps the size arithmetic in range
-    const size_t need = kb_attn_workspace_bytes(B * T, B * T, 1, H, dtype, qn_w || rope_cos, kn_w || rope_cos);
+    // only the staging copies must fit; what is left of the array serves the balanced schedule when it is enough for it
+    const size_t need = staging_bytes((size_t)B * T, (size_t)B * T, 1, H, dtype, qn_w || rope_cos, kn_w || rope_cos);
     if (need > (size_t)KB_STATIC_SCRATCH_BYTES) return KB_ERR_STATIC_SCRATCH;
     void* scratch = nullptr;
     int rc;

@@ -7,26 +7,44 @@
 // all-zero keys joining the softmax analytically (engine/src/tcflash.cuh:136-147), fp32 statistics,
 // base-2 exponent with the scale log2(e)/sqrt(128) (engine/src/tcflash.cuh:164).
 //
-// The kernel is PERSISTENT: one CTA per SM walks a list of work items, so TMEM allocation, barrier
-// set-up and the TMA/MMA pipeline fill are paid once, and the loads of the next item run under the
-// epilogue of the current one. One item runs TWO softmax streams that ping-pong on the tensor core:
-//   MODE_PAIR : item = two 128-row query tiles of one (batch, head) against one K/V sequence
-//               (self-attention and plain cross-attention);
-//   MODE_NAG  : item = one 128-row query tile of one head against TWO K/V sequences (positive and
-//               negative context), followed by the NAG combine of engine/src/dit.cu:295-324 in the
-//               epilogue. The combine needs per-token L1 norms over ALL heads: the CTAs that hold the
-//               heads of one query tile (adjacent items, so they run at the same time) publish their
-//               partial norms in a small global scratch, bump a per-tile counter and wait, bounded,
-//               for the other heads. Nothing but the blended result is written as output.
+// The kernel is PERSISTENT: one CTA per SM walks a list of work segments, so TMEM allocation, barrier
+// set-up and the TMA/MMA pipeline fill are paid once, and the loads of the next segment run under the
+// epilogue of the current one. A segment runs TWO softmax streams that share the tensor core:
+//   MODE_PAIR : two 128-row query tiles of one (batch, head) against a range of 128-key blocks of one
+//               K/V sequence (self-attention and plain cross-attention);
+//   MODE_NAG  : one 128-row query tile of one head against TWO K/V sequences (positive and negative
+//               context), followed by the NAG combine of engine/src/dit.cu:295-324 in the epilogue.
+//               The combine needs per-token L1 norms over ALL heads: the CTAs that hold the heads of
+//               one query tile (adjacent items, so they run at the same time) publish their partial
+//               norms in a small global scratch, bump a per-tile counter and wait, bounded, for the
+//               other heads. Nothing but the blended result is written as output.
 //
-// Warp roles (384 threads): warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1 (warp w
-// owns TMEM lanes 32*(w%4)..+31, one query row per thread), warp 8 issues MMAs (one lane), warp 9
-// issues TMA loads (one lane), warps 10-11 idle.
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i overwrites the first
-// 64 columns of S_i as packed fp16 pairs.
-// (Tried and dropped: 64-key half blocks with two S buffers per stream to decouple softmax and MMA
-// latency. An S MMA with N = 64 reads as many shared-memory bytes per FLOP for its A operand as it
-// saves on B, runs at half rate, and the kernel got 1.5x slower.)
+// Warp roles (384 threads): warps 0-3 / 4-7: softmax of stream 0 / 1 (warp w owns TMEM lanes 32*(w%4)..+31,
+// one query row per thread), warps 8 / 10 issue the MMAs of stream 0 / 1 (one lane each), warp 9 issues TMA loads
+// (one lane), warp 11 idle.
+//
+// TMEM (512 columns): R [0,128) P0 [128,192) P1 [192,256) O0 [256,384) O1 [384,512).
+// R is ONE score staging area shared by both streams: an S = Q K^T lands there, the stream's softmax threads
+// read it into registers at once and hand R back. P (fp16 pairs, 64 columns) has its own place per stream.
+// With P written over S (the usual layout) a stream's next S cannot be issued before its own P*V has
+// consumed P, so its cycle is  softmax + P*V + S + two hand-offs  and two streams keep the tensor core ~58 % busy.
+// Here the next S of a stream does not depend on its P: the softmax threads ask for it while they are still
+// in their exponentials (`s_req`), it runs on the tensor core under the rest of that softmax, and the
+// threads go from one block straight into the next; P*V follows whenever P is complete.
+//
+// Balanced schedule (MODE_PAIR, `split`). Items x key blocks rarely divide by the SM count (4096 tokens:
+// 256 items on 148 SMs = 1.73 rounds). With `split` every CTA takes an equal, contiguous range of
+// (item, key block) steps. An item cut by a range boundary is finished by the CTA that holds its FIRST blocks
+// (always the last thing that CTA does); the CTAs holding its later blocks (always the first thing they do)
+// write their unnormalised (m, l, O) to a global scratch and raise a flag; the finisher waits (bounded) and
+// merges. All CTAs are resident (cooperative launch), so nothing the finisher waits for can be queued behind it.
+//
+// (Tried and dropped: 64-key half blocks with two S buffers per stream: an S MMA with N = 64 reads as many
+// shared-memory bytes per FLOP for its A operand as it saves on B and runs at half rate, 1.5x slower. Both
+// warpgroups on one stream's block with half of the keys per thread: the exponentials are bound by the
+// 16-per-clock MUFU unit whatever the thread count, and the two softmaxes can then no longer overlap, 12 % slower.
+// 2^x by polynomial on the FMA pipe for part of the scores: packed f32x2 instructions issue at half rate on B200
+// (measured: 2 cycles per warp instruction), so the polynomial costs more pipe time than the MUFU it saves.)
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -61,6 +79,10 @@ constexpr uint32_t ST_TIMEOUT = 1u;
 
 constexpr int MAX_PEERS = 8;
 
+// Scratch one CTA needs for the partial result of a cut item: per stream O[128 columns][128 rows], m[128], l[128] (fp32)
+constexpr int PART_STREAM_FLOATS = HD * BM + 2 * BM;
+constexpr size_t PART_CTA_BYTES = 2 * (size_t)PART_STREAM_FLOATS * sizeof(float);
+
 struct AttnParams {
     void* out;          // [B*Tq, ldo]
     int ldo;
@@ -78,12 +100,19 @@ struct AttnParams {
     float nag_s, nag_tau, nag_alpha;
     float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][H][2][128]: per head |Z+|_1 and |g|_1 of each row
     unsigned int* nag_flag;  // MODE_NAG [ceil(Tq/128)] arrival counters, zero before the launch
+    int split;          // MODE_PAIR: balanced (item, key block) ranges per CTA with partial results merged
+    float* part;        // split: [gridDim.x] slots of PART_CTA_BYTES
+    unsigned int* part_flag;  // split: [gridDim.x][2 streams], zero before the launch; 1 = slot written
     uint32_t* status;   // device word, OR-ed with ST_* on failure
 };
 
 // barrier slots inside the control block
-enum { BAR_QFULL = 0, BAR_QEMPTY = 2, BAR_SFULL = 4, BAR_PFULL = 6, BAR_ODONE = 8, BAR_OFREE = 10, BAR_KVFULL = 12,
-       BAR_KVEMPTY = 12 + NSTAGE, BAR_COUNT = 12 + 2 * NSTAGE };
+enum { BAR_QFULL = 0, BAR_QEMPTY = 2, BAR_SFULL = 4, BAR_SREQ = 6, BAR_PFULL = 8, BAR_PEMPTY = 10, BAR_ODONE = 12, BAR_OFREE = 14,
+       BAR_SFREE = 16, BAR_KVFULL = 20, BAR_KVEMPTY = 20 + NSTAGE, BAR_COUNT = 20 + 2 * NSTAGE };
+// when a stream asks for its next S: 0 = before its exponentials, 1 = after the first half of them, 2 = with P (no overlap)
+#ifndef KB_SREQ_AT
+#define KB_SREQ_AT 1
+#endif
 
 // full-CTA barrier usable from divergent role branches (same id and count everywhere)
 __device__ __forceinline__ void cta_sync() { named_bar_sync(2, ATTN_THREADS); }
@@ -114,41 +143,94 @@ __device__ __forceinline__ void store32(OutT* dst, const float (&v)[32]) {
     }
 }
 
-// One work item: which rows, head and batch element, and how many 128-key blocks each stream runs
-// (0 = the stream does not exist in this item).
-struct Item {
+// One work segment: which rows, head and batch element, and which 128-key blocks [jb, je[i]) each stream runs
+// (je[i] <= jb: the stream does not exist in this segment). nb = blocks of the whole item (MODE_PAIR).
+struct Seg {
     int q0, h, b, qt;
-    int nblk[2];
+    int jb, je[2], nb;
 };
 
+// Every role of a CTA walks the same segment list.
 template <int MODE>
-__device__ __forceinline__ Item decode_item(int w, const AttnParams& p) {
-    Item it;
-    if (MODE == MODE_PAIR) {
-        const int nqp = (p.Tq + 2 * BM - 1) / (2 * BM);       // query-tile pairs per (batch, head), fastest: K/V reuse in L2
-        const int qp = w % nqp, hb = w / nqp;
-        it.h = hb % p.H;
-        it.b = hb / p.H;
-        it.q0 = qp * 2 * BM;
-        it.qt = qp;
-        it.nblk[0] = (p.Tk[0] + BN - 1) / BN;
-        it.nblk[1] = (it.q0 + BM < p.Tq) ? it.nblk[0] : 0;
-    } else {
-        it.h = w % p.H;                                       // heads fastest: the heads of a query tile run side by side
-        it.qt = w / p.H;
-        it.b = 0;
-        it.q0 = it.qt * BM;
-        it.nblk[0] = (p.Tk[0] + BN - 1) / BN;
-        it.nblk[1] = (p.Tk[1] + BN - 1) / BN;
+struct SegIter {
+    long long s, s_end;     // split: steps (item * nb + block) of this CTA
+    int w, nb;
+    const AttnParams& p;
+    __device__ __forceinline__ SegIter(const AttnParams& p_) : p(p_) {
+        nb = (p.Tk[0] + BN - 1) / BN;
+        w = blockIdx.x;
+        s = s_end = 0;
+        if (MODE == MODE_PAIR && p.split) {
+            const long long n = (long long)p.n_items * nb;
+            s = n * blockIdx.x / gridDim.x;
+            s_end = n * (blockIdx.x + 1) / gridDim.x;
+        }
     }
-    return it;
+    __device__ __forceinline__ bool next(Seg& o) {
+        int item, jb, je;
+        if (MODE == MODE_PAIR && p.split) {
+            if (s >= s_end) return false;
+            item = (int)(s / nb);
+            jb = (int)(s % nb);
+            const long long rem = s_end - s;
+            je = (rem < (long long)(nb - jb)) ? jb + (int)rem : nb;
+            s += je - jb;
+        } else {
+            if (w >= p.n_items) return false;
+            item = w;
+            jb = 0;
+            je = nb;
+            w += gridDim.x;
+        }
+        o.jb = jb;
+        o.nb = nb;
+        if (MODE == MODE_PAIR) {
+            const int nqp = (p.Tq + 2 * BM - 1) / (2 * BM);       // query-tile pairs per (batch, head), fastest: K/V reuse in L2
+            const int qp = item % nqp, hb = item / nqp;
+            o.h = hb % p.H;
+            o.b = hb / p.H;
+            o.q0 = qp * 2 * BM;
+            o.qt = qp;
+            o.je[0] = je;
+            o.je[1] = (o.q0 + BM < p.Tq) ? je : jb;
+        } else {
+            o.h = item % p.H;                                     // heads fastest: the heads of a query tile run side by side
+            o.qt = item / p.H;
+            o.b = 0;
+            o.q0 = o.qt * BM;
+            o.je[0] = (p.Tk[0] + BN - 1) / BN;
+            o.je[1] = (p.Tk[1] + BN - 1) / BN;
+        }
+        return true;
+    }
+};
+
+// K/V ring bookkeeping. The loader fills ring entries in a fixed order and every consumer counts the same way:
+//   MODE_PAIR segment: K(jb), then per key block V(j), K(j+1): K(j) is entry 2(j-jb), V(j) entry 2(j-jb)+1 of the segment;
+//   MODE_NAG item: K0(0), K1(0), then per block j and stream i (0 first): V_i(j), K_i(j+1).
+// nag_entry returns the entry of V_i(j) within the item (K_i(j+1), when it exists, is the next one).
+__device__ __forceinline__ int nag_entry(int i, int j, int L0, int L1) {
+    int e = (L0 > 0) + (L1 > 0);
+    const int L[2] = {L0, L1};
+#pragma unroll
+    for (int ii = 0; ii < 2; ii++) {
+        if (L[ii] <= 0) continue;
+        const int full = j < L[ii] ? j : L[ii];                  // blocks of stream ii before block j
+        e += 2 * full - (j >= L[ii] ? 1 : 0);                     // two entries per block, the last block only its V
+        if (ii < i && j < L[ii]) e += 1 + (j + 1 < L[ii] ? 1 : 0);   // stream 0's entries of block j come first
+    }
+    return e;
+}
+__device__ __forceinline__ int seg_entries(int mode, int jb, const int (&je)[2]) {
+    if (mode == MODE_PAIR) return 2 * (je[0] - jb);
+    return (je[0] > 0 ? 2 * je[0] : 0) + (je[1] > 0 ? 2 * je[1] : 0);
 }
 
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
-                const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const __grid_constant__ AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
@@ -161,6 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
     volatile uint32_t* const warp_ok = reinterpret_cast<volatile uint32_t*>(ctrl + 264);   // [8] per softmax warp
     volatile uint32_t* const wg_stop = reinterpret_cast<volatile uint32_t*>(ctrl + 296);   // [2] per softmax warpgroup
+    volatile uint32_t* const wg_here = reinterpret_cast<volatile uint32_t*>(ctrl + 304);   // [2] per softmax warpgroup
     float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 5 x 128 floats x 2
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
@@ -169,7 +252,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (tid == 0) {
         for (int i = 0; i < BAR_COUNT; i++) {
             uint32_t count = 1;
-            if (i >= BAR_PFULL && i < BAR_PFULL + 2) count = 4;             // one arrival per softmax warp
+            if (i >= BAR_SREQ && i < BAR_SREQ + 2) count = 4;               // one arrival per softmax warp of the stream
+            if (i >= BAR_PFULL && i < BAR_PFULL + 2) count = 4;
+            if (i == BAR_SFREE) count = 4;
+            if (i >= BAR_KVEMPTY && i < BAR_KVEMPTY + NSTAGE) count = MODE == MODE_PAIR ? 2 : 1;   // PAIR: both streams use every K/V tile
             if (i >= BAR_OFREE && i < BAR_OFREE + 2) count = MODE == MODE_NAG ? 8 : 4;   // NAG: both warpgroups read both O
             mbar_init(bar(i), count);
         }
@@ -200,29 +286,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int i = warp >> 2;                                   // stream = warpgroup
         const int t = tid & 127;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + (uint32_t)(i * 128);
+        const uint32_t tR = tmem_base + lane_base;                                  // score staging, shared by both streams
+        const uint32_t tP = tmem_base + lane_base + 128u + (uint32_t)(i * 64);
         const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(i * 128);
         const float c = p.scale_log2;
-        uint32_t sf_cnt = 0, od_cnt = 0;                           // uses of s_full[i] / o_done[i] so far (phase parity)
+        uint32_t sf_cnt = 0, od_cnt = 0, pe_cnt = 0;               // uses of s_full[i] / o_done[i] / p_empty[i] so far (phase parity)
+        uint32_t ring0 = 0;                                        // K/V ring entries of all earlier segments
 
-        for (int w = blockIdx.x; w < p.n_items; w += gridDim.x) {
-            const Item it = decode_item<MODE>(w, p);
-            const int nb = it.nblk[i];
+        SegIter<MODE> iter(p);
+        Seg it;
+        while (iter.next(it)) {
+            const int jb = it.jb, je = it.je[i];
             const int Tk = p.Tk[MODE == MODE_NAG ? i : 0];
+            const int j_last = (Tk + BN - 1) / BN - 1;             // the block that may be ragged
             float row_m = -INFINITY, row_l = 0.f;
             bool ok = true;
-            for (int j = 0; j < nb; ++j) {
+            // this stream's K/V ring entries: a slot goes back to the loader when the MMAs that read it are done, which the
+            // softmax threads see anyway (S done: s_full; P*V done: p_empty / o_done) - a plain arrive by one thread instead
+            // of a tcgen05.commit by the MMA warp, each of which costs the tensor pipe ~100 cycles (measured)
+            const bool two = MODE == MODE_PAIR && it.je[1] > jb;
+            auto release = [&](uint32_t entry) {
+                if (t == 0) {
+                    mbar_arrive(bar(BAR_KVEMPTY + (ring0 + entry) % NSTAGE));
+                    if (MODE == MODE_PAIR && !two) mbar_arrive(bar(BAR_KVEMPTY + (ring0 + entry) % NSTAGE));   // stream 1 is absent: its share too
+                }
+            };
+            auto k_entry = [&](int j) { return (uint32_t)(MODE == MODE_PAIR ? 2 * (j - jb) : (j == 0 ? (i == 1 && it.je[0] > 0 ? 1 : 0) : nag_entry(i, j - 1, it.je[0], it.je[1]) + 1)); };
+            auto v_entry = [&](int j) { return (uint32_t)(MODE == MODE_PAIR ? 2 * (j - jb) + 1 : nag_entry(i, j, it.je[0], it.je[1])); };
+            for (int j = jb; j < je; ++j) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), sf_cnt & 1u, abort_flag));
                 ++sf_cnt;
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
-                for (int q = 0; q < 4; q++) tmem_ld32(tS + 32u * q, s[q]);
+                for (int q = 0; q < 4; q++) tmem_ld32(tR + 32u * q, s[q]);
                 tmem_wait_ld();
 #pragma unroll
                 for (int q = 0; q < 4; q++) reg_fence32(s[q]);
-                if (j == nb - 1 && (Tk & (BN - 1))) {              // ragged last block: keys >= Tk score -inf
+                // the scores are in registers: the staging area may take the next S (of the other stream, normally)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_SFREE));
+                release(k_entry(j));                               // S_i(j) is complete: this stream is done with K(j)
+                if (j == j_last && (Tk & (BN - 1))) {              // ragged last block: keys >= Tk score -inf
                     const int valid = Tk - j * BN;
 #pragma unroll
                     for (int q = 0; q < 4; q++)
@@ -239,18 +346,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     mx3 = max3(mx3, __uint_as_float(s[3][e]), __uint_as_float(s[3][e + 1]));
                 }
                 const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-                if (j == 0) {
+                if (KB_SREQ_AT == 0 && j + 1 < je) { __syncwarp(); if (lane == 0) mbar_arrive(bar(BAR_SREQ + i)); }
+                // The previous P*V of this stream reads P_i and writes O_i: it must be complete before either is touched.
+                // That wait sits as late as possible: before the first store of P, or before a rescale of O.
+                bool pv_done = false;
+                auto wait_pv = [&]() {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PEMPTY + i), (pe_cnt & 1u) ^ 1u, abort_flag));
+                    ++pe_cnt;
+                    tc_fence_after();
+                    pv_done = true;
+                    if (ok && j > jb) release(v_entry(j - 1));     // P_i(j-1) V(j-1) is complete: this stream is done with V(j-1)
+                };
+                if (j == jb) {
                     row_m = mx;
                 } else {
                     // Keep a stale maximum while the new one is less than 2^8 above it: P stays <= 256, which
                     // fp16 and the fp32 sums hold exactly as well, and O needs no rescale.
                     const bool need = (mx - row_m) * c > 8.f;
                     if (__any_sync(0xffffffffu, need)) {
+                        wait_pv();
+                        if (!ok) break;
                         const float mn = fmaxf(row_m, mx);
                         const float a = ex2((row_m - mn) * c);
                         row_l *= a;
                         row_m = mn;
-                        // The commit that completed S_i(j) was issued after PV_i(j-1), so O_i is quiescent here.
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             uint32_t o[32];
@@ -287,8 +406,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         unpack2(p2, p0, p1);
                         pk[e] = pack16<DT_F16>(p0, p1);
                     }
-                    tmem_st32(tS + 32u * q, pk);                   // P: key pair (2c, 2c+1) in column c
+                    if (q == 0) {
+                        reg_fence32(pk);                           // the first half is computed before the wait below, not after it
+                        if (!pv_done) wait_pv();
+                        if (!ok) break;
+                    }
+                    tmem_st32(tP + 32u * q, pk);                   // P: key pair (2c, 2c+1) in column c
+                    if (q == 0) {
+                        // Ask for the next S of this stream now: it runs on the tensor core under the second half of the
+                        // exponentials. The register fences keep that second half from being scheduled ahead of the request.
+                        if (KB_SREQ_AT == 1 && j + 1 < je) { __syncwarp(); if (lane == 0) mbar_arrive(bar(BAR_SREQ + i)); }
+                        reg_fence32(s[2]);
+                        reg_fence32(s[3]);
+                    }
                 }
+                if (!ok) break;
                 float sum0, sum1, sum2, sum3;
                 unpack2(sum2a, sum0, sum1);
                 unpack2(sum2b, sum2, sum3);
@@ -296,37 +428,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(BAR_PFULL + i));
+                if (lane == 0) {
+                    if (KB_SREQ_AT == 2 && j + 1 < je) mbar_arrive(bar(BAR_SREQ + i));
+                    mbar_arrive(bar(BAR_PFULL + i));
+                }
             }
-            if (ok && nb > 0) {
+            const bool mine = je > jb;                                         // this stream exists in the segment
+            if (ok && mine) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), od_cnt & 1u, abort_flag));
                 tc_fence_after();
+                if (ok) release(v_entry(je - 1));                              // the last P*V is complete: done with its V
             }
-            if (nb > 0) ++od_cnt;
+            if (mine) ++od_cnt;
+            ring0 += (uint32_t)seg_entries(MODE, jb, it.je);
 
-            // ---------------------------------------------------------------- epilogue of the item
+            // ---------------------------------------------------------------- epilogue of the segment
             if (MODE == MODE_PAIR) {
-                if (nb > 0) {
+                if (mine) {
                     // Make `ok` uniform over the stream's four warps before barriers only they take part in; this
                     // barrier is reached unconditionally, so a warp that gave up cannot leave the others waiting.
                     if (lane == 0) warp_ok[warp] = ok ? 1u : 0u;
                     named_bar_sync(3 + i, 128);
                     const int w0 = warp & 4;
                     ok = (warp_ok[w0] & warp_ok[w0 + 1] & warp_ok[w0 + 2] & warp_ok[w0 + 3]) != 0u;
-                    if (ok) {
-                        const float mc = row_m * p.scale_log2;
-                        float scale = 1.f, l = row_l;
-                        if (p.npad[0]) {                                     // engine/src/tcflash.cuh:140-144
-                            const float mn = fmaxf(mc, 0.f);
-                            scale = exp2f(mc - mn);
-                            l = l * scale + (float)p.npad[0] * exp2f(-mn);
-                        }
-                        const float inv = scale / l;
-                        if constexpr (sizeof(OutT) == 2) {
-                            // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream
-                            // has completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
-                            constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
-                            uint8_t* const stage = smem + i * TILE_BYTES;
+                    const float M = row_m * c;                                 // running maximum in log2 units
+                    if (jb > 0) {
+                        // later blocks of a cut item: the unnormalised result goes to this CTA's scratch slot,
+                        // column-major (coalesced over rows), and the stream's flag is raised
+                        float* const slot = p.part + (size_t)blockIdx.x * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS;
+                        if (ok) {
+                            slot[HD * BM + t] = M;
+                            slot[HD * BM + BM + t] = row_l;
 #pragma unroll
                             for (int q = 0; q < 4; q++) {
                                 uint32_t o[32];
@@ -334,72 +466,148 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 tmem_wait_ld();
                                 reg_fence32(o);
 #pragma unroll
-                                for (int cc = 0; cc < 4; cc++) {             // 16-byte chunk 4q + cc of the row, XOR-swizzled against bank conflicts
-                                    uint4 pk;
-                                    pk.x = pack16<ODT>(__uint_as_float(o[8 * cc + 0]) * inv, __uint_as_float(o[8 * cc + 1]) * inv);
-                                    pk.y = pack16<ODT>(__uint_as_float(o[8 * cc + 2]) * inv, __uint_as_float(o[8 * cc + 3]) * inv);
-                                    pk.z = pack16<ODT>(__uint_as_float(o[8 * cc + 4]) * inv, __uint_as_float(o[8 * cc + 5]) * inv);
-                                    pk.w = pack16<ODT>(__uint_as_float(o[8 * cc + 6]) * inv, __uint_as_float(o[8 * cc + 7]) * inv);
-                                    // the tile's own layout: two 128-byte-swizzled [128][64] halves (what TMA stores)
-                                    *reinterpret_cast<uint4*>(stage + (q >> 1) * HALF_BYTES + t * 128 + ((((4 * q + cc) & 7) ^ (t & 7)) << 4)) = pk;
-                                }
-                            }
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next item's P*V may start
-                            if (p.n_peers == 0) {
-                                // one bulk tensor store per half; rows past Tq are clipped by the tensor map
-                                fence_proxy_async_smem();
-                                named_bar_sync(3 + i, 128);                  // the staged tile is complete
-                                if (t == 0) {
-                                    tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0 + i * BM, it.b);
-                                    tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0 + i * BM, it.b);
-                                    tma_store_commit();
-                                    tma_store_wait_read();                   // the staging space may be overwritten
-                                }
-                            } else {
-                                named_bar_sync(3 + i, 128);                  // the staged tile is complete
-                                // head-split runs: each warp copies 32 rows out as whole 256-byte rows to every peer buffer
-                                // (all shared-memory reads first, then the stores)
-                                const int lr0 = 32 * (warp & 3);
-                                const int row0 = it.q0 + i * BM + lr0;
-                                const int nrow = p.Tq - row0;                // rows of this warp that exist (warp-uniform)
-                                uint2 vals[32];
-#pragma unroll
-                                for (int rr = 0; rr < 32; rr++)
-                                    vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
-                                                                               ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
-                                const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
-                                for (int pe = 0; pe < p.n_peers; pe++) {
-                                    OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
-#pragma unroll
-                                    for (int rr = 0; rr < 32; rr++)
-                                        if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
-                                }
-                                __threadfence_system();                      // the tile is visible to every GPU before the arrival
-                                named_bar_sync(3 + i, 128);                  // every warp is done with the staging tile
-                                if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
-                            }
-                        } else {
-                            const int row = it.q0 + i * BM + t;
-                            OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)it.h * HD;
-#pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                uint32_t o[32];
-                                float v[32];
-                                tmem_ld32(tO + 32u * q, o);
-                                tmem_wait_ld();
-                                reg_fence32(o);
-#pragma unroll
-                                for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * inv;
-                                if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                                for (int e = 0; e < 32; e++) slot[(size_t)(q * 32 + e) * BM + t] = __uint_as_float(o[e]);
                             }
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
+                            if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
                         }
-                        // the Q tile (and the staging space in it) may be overwritten by the next item's Q
-                        if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
+                        __threadfence();
+                        named_bar_sync(3 + i, 128);                            // every thread's stores are ordered before the flag
+                        if (ok && t == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.part_flag + 2 * blockIdx.x + i), "r"(1u) : "memory");
+                    } else {
+                        // CTAs after this one whose range starts inside this item hold the rest of it
+                        int n_rest = 0;
+                        if (p.split && je < it.nb) {
+                            const long long n = (long long)p.n_items * it.nb, item_end = iter.s - je + it.nb;   // iter.s: this segment's end
+                            for (int cc = blockIdx.x + 1; cc < (int)gridDim.x && n * cc / gridDim.x < item_end; cc++) n_rest++;
+                        }
+                        if (n_rest > 0) {
+                            if (t == 0) {
+                                bool here = true;
+                                const uint64_t t0 = globaltimer_ns();
+                                for (int r = 1; r <= n_rest && here; r++) {
+                                    for (;;) {
+                                        uint32_t seen;
+                                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.part_flag + 2 * (blockIdx.x + r) + i) : "memory");
+                                        if (seen) break;
+                                        if (*abort_flag) { here = false; break; }
+                                        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; here = false; break; }
+                                        __nanosleep(64);
+                                    }
+                                }
+                                wg_here[i] = here ? 1u : 0u;
+                            }
+                            named_bar_sync(3 + i, 128);
+                            ok = ok && wg_here[i] != 0u;
+                        }
+                        if (ok) {
+                            // statistics of all parts first, then one pass over the columns
+                            float Mf = M;
+                            for (int r = 1; r <= n_rest; r++)
+                                Mf = fmaxf(Mf, __ldcg(p.part + (size_t)(blockIdx.x + r) * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS + HD * BM + t));
+                            const float a_mine = ex2(M - Mf);
+                            float l = row_l * a_mine;
+                            for (int r = 1; r <= n_rest; r++) {
+                                const float* slot = p.part + (size_t)(blockIdx.x + r) * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS;
+                                l += __ldcg(slot + HD * BM + BM + t) * ex2(__ldcg(slot + HD * BM + t) - Mf);
+                            }
+                            float scale = 1.f;
+                            if (p.npad[0]) {                                   // engine/src/tcflash.cuh:140-144
+                                const float mn = fmaxf(Mf, 0.f);
+                                scale = exp2f(Mf - mn);
+                                l = l * scale + (float)p.npad[0] * exp2f(-mn);
+                            }
+                            const float inv = scale / l;
+                            const float k_mine = a_mine * inv;
+                            // one 32-column chunk of the merged, normalised row
+                            auto chunk = [&](int q, float (&v)[32]) {
+                                uint32_t o[32];
+                                tmem_ld32(tO + 32u * q, o);
+                                tmem_wait_ld();
+                                reg_fence32(o);
+#pragma unroll
+                                for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * k_mine;
+                                for (int r = 1; r <= n_rest; r++) {
+                                    const float* slot = p.part + (size_t)(blockIdx.x + r) * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS;
+                                    const float k_r = ex2(__ldcg(slot + HD * BM + t) - Mf) * inv;
+#pragma unroll
+                                    for (int e = 0; e < 32; e++) v[e] += __ldcg(slot + (size_t)(q * 32 + e) * BM + t) * k_r;
+                                }
+                            };
+                            if constexpr (sizeof(OutT) == 2) {
+                                // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream
+                                // has completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
+                                constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+                                uint8_t* const stage = smem + i * TILE_BYTES;
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    float v[32];
+                                    chunk(q, v);
+#pragma unroll
+                                    for (int cc = 0; cc < 4; cc++) {           // 16-byte chunk 4q + cc of the row, XOR-swizzled against bank conflicts
+                                        uint4 pk;
+                                        pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
+                                        pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
+                                        pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
+                                        pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
+                                        // the tile's own layout: two 128-byte-swizzled [128][64] halves (what TMA stores)
+                                        *reinterpret_cast<uint4*>(stage + (q >> 1) * HALF_BYTES + t * 128 + ((((4 * q + cc) & 7) ^ (t & 7)) << 4)) = pk;
+                                    }
+                                }
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next segment's P*V may start
+                                if (p.n_peers == 0) {
+                                    // one bulk tensor store per half; rows past Tq are clipped by the tensor map
+                                    fence_proxy_async_smem();
+                                    named_bar_sync(3 + i, 128);                  // the staged tile is complete
+                                    if (t == 0) {
+                                        tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0 + i * BM, it.b);
+                                        tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0 + i * BM, it.b);
+                                        tma_store_commit();
+                                        tma_store_wait_read();                   // the staging space may be overwritten
+                                    }
+                                } else {
+                                    named_bar_sync(3 + i, 128);                  // the staged tile is complete
+                                    // head-split runs: each warp copies 32 rows out as whole 256-byte rows to every peer buffer
+                                    // (all shared-memory reads first, then the stores)
+                                    const int lr0 = 32 * (warp & 3);
+                                    const int row0 = it.q0 + i * BM + lr0;
+                                    const int nrow = p.Tq - row0;                // rows of this warp that exist (warp-uniform)
+                                    uint2 vals[32];
+#pragma unroll
+                                    for (int rr = 0; rr < 32; rr++)
+                                        vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                                   ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                                    const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                                    for (int pe = 0; pe < p.n_peers; pe++) {
+                                        OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                                        for (int rr = 0; rr < 32; rr++)
+                                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                                    }
+                                    __threadfence_system();                      // the tile is visible to every GPU before the arrival
+                                    named_bar_sync(3 + i, 128);                  // every warp is done with the staging tile
+                                    if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
+                                }
+                            } else {
+                                const int row = it.q0 + i * BM + t;
+                                OutT* dst = reinterpret_cast<OutT*>(p.out) + ((size_t)it.b * p.Tq + (size_t)row) * (size_t)p.ldo + (size_t)it.h * HD;
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    float v[32];
+                                    chunk(q, v);
+                                    if (row < p.Tq) store32<OutT>(dst + 32 * q, v);
+                                }
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
+                            }
+                            // the Q tile (and the staging space in it) may be overwritten by the next segment's Q
+                            if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
+                        }
                     }
                 }
             } else {
@@ -458,19 +666,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (tid == 0) {
                     // arrive, then wait (bounded) for the other heads of this query tile: they are adjacent work items
                     // and therefore in flight on other SMs now (the launch is cooperative: all CTAs are resident)
-                    atomicAdd(p.nag_flag + it.qt, 1u);
+                    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + it.qt), "r"(1u) : "memory");
                     const uint64_t t0 = globaltimer_ns();
                     uint32_t seen = 0;
                     for (;;) {
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
                         if (seen >= (uint32_t)p.H || *abort_flag) break;
                         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
-                        __nanosleep(64);
+                        __nanosleep(32);
                     }
-                    wg_stop[0] = (seen >= (uint32_t)p.H) ? 0u : 1u;
+                    wg_here[0] = (seen >= (uint32_t)p.H) ? 1u : 0u;
                 }
                 named_bar_sync(1, 256);
-                const bool all_here = wg_stop[0] == 0u;
+                const bool all_here = wg_here[0] != 0u;
                 float tot = 0.f;
                 if (all_here)
                     for (int hh = 0; hh < p.H; hh++) tot += __ldcg(gpart + (size_t)hh * 256 + wg * 128 + t);   // head order: same sum everywhere
@@ -481,7 +689,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
                 const bool go = ok && all_here;                               // uniform over the 256 softmax threads
                 if constexpr (sizeof(OutT) == 2) {
-                    // blend into the (never loaded in this mode) second Q tile, then whole 256-byte rows go out
+                    // blend into the (never loaded in this mode) second Q tile, then one bulk tensor store per half
                     constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
                     uint8_t* const stage = smem + TILE_BYTES;
                     if (go) {
@@ -517,7 +725,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         fence_proxy_async_smem();
                     }
                     named_bar_sync(1, 256);
-                    if (go && tid == 0) {                                     // one bulk tensor store per half; rows past Tq are clipped
+                    if (go && tid == 0) {                                     // rows past Tq are clipped by the tensor map
                         tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0, 0);
                         tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0, 0);
                         tma_store_commit();
@@ -550,7 +758,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                 }
             }
-            // leave the item loop together once any role has given up (uniform per warpgroup; in NAG mode per CTA)
+            // leave the segment loop together once any role has given up (uniform per warpgroup; in NAG mode per CTA)
             if (MODE == MODE_PAIR) {
                 if (t == 0) wg_stop[i] = *abort_flag;
                 named_bar_sync(3 + i, 128);
@@ -568,108 +776,126 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
         cta_sync();
     } else {
-        setmaxnreg_dec<88>();
-        if (warp == 8) {
-            // ------------------------------------------------------------------ MMA issue (one lane)
+        setmaxnreg_dec<88>();   // 384 x 168 registers at launch = 256 x 208 + 128 x 88: a larger value here would leave the increase above waiting forever
+        if (warp == 8 || warp == 10) {
+            // ------------------------------------------------------------------ MMA issue: one warp (one lane) per stream
+            // Two issuing threads, because one thread's waits, fences and commits between two batches of eight MMAs take
+            // longer than the tensor core's instruction queue lasts: with a single issuer the pipe drained between batches
+            // and paid its start-up latency every time (measured: ~850 cycles per batch against 520 back to back).
+            // Now one thread's bookkeeping runs under the other's MMAs.
+            const int i = (warp - 8) >> 1;
             if (lane == 0) {
                 // Operands are fp16 throughout (bf16/fp32 inputs are staged as fp16 by the pre-pass): with bf16
                 // P the 2^-9 rounding of each weight alone costs ~1e-3 relative error on outputs that are sums
                 // of random-sign terms, and tcgen05 does not take an fp16 A with a bf16 B.
                 constexpr uint32_t IDESC_S = idesc_f16(0, 0, 0, 0, BM, BN);   // S = Q K^T, both K-major
                 constexpr uint32_t IDESC_PV = idesc_f16(0, 0, 0, 1, BM, HD);  // O += P V, V is MN-major (rows = keys)
-                uint32_t ring = 0;                                            // ring slot being consumed (same order as the loader)
-                uint32_t qf_cnt[2] = {0, 0}, pf_cnt[2] = {0, 0}, of_cnt[2] = {0, 0};
+                // descriptor words: the high word is common to every tile here (stride between 8-row groups 1024 bytes, 128-byte
+                // swizzle), the low word is the tile's base plus a constant per k step
+                constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+                const uint32_t q_lo = smem_desc_lo(sQ + (MODE == MODE_NAG ? 0 : i) * TILE_BYTES, 16);
+                const uint32_t tO = tmem_base + 256u + (uint32_t)(i * 128), tP = tmem_base + 128u + (uint32_t)(i * 64);
+                uint32_t ring = 0;                                            // ring slot index, counted exactly as the loader counts
+                uint32_t n_s = 0;                                             // S products issued so far by BOTH warps (they share the staging area in turn)
+                uint32_t qf_cnt = 0, pf_cnt = 0, of_cnt = 0, sr_cnt = 0;
                 bool good = true;
                 auto kv_wait = [&](uint32_t idx) { return mbar_wait(bar(BAR_KVFULL + idx % NSTAGE), (idx / NSTAGE) & 1u, abort_flag); };
                 auto kv_addr = [&](uint32_t idx) { return sKV + (idx % NSTAGE) * TILE_BYTES; };
-                auto kv_release = [&](uint32_t idx) { tc_commit(bar(BAR_KVEMPTY + idx % NSTAGE)); };
-                auto q_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_QFULL + i), qf_cnt[i] & 1u, abort_flag); ++qf_cnt[i]; return r; };
-                auto p_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_PFULL + i), pf_cnt[i] & 1u, abort_flag); ++pf_cnt[i]; tc_fence_after(); return r; };
-                // O_i (and, in NAG mode, both O) of the previous item has been read out; passes at once for the first item
-                auto o_free_wait = [&](int i) { const bool r = mbar_wait(bar(BAR_OFREE + i), (of_cnt[i] & 1u) ^ 1u, abort_flag); ++of_cnt[i]; tc_fence_after(); return r; };
-                auto issue_S = [&](int i, uint32_t k_saddr) {
-                    const uint32_t q_saddr = sQ + (MODE == MODE_NAG ? 0 : i) * TILE_BYTES;
+                auto q_wait = [&]() { const bool r = mbar_wait(bar(BAR_QFULL + (MODE == MODE_NAG ? 0 : i)), qf_cnt & 1u, abort_flag); ++qf_cnt; return r; };
+                auto p_wait = [&]() { const bool r = mbar_wait(bar(BAR_PFULL + i), pf_cnt & 1u, abort_flag); ++pf_cnt; tc_fence_after(); return r; };
+                auto sreq_wait = [&]() { const bool r = mbar_wait(bar(BAR_SREQ + i), sr_cnt & 1u, abort_flag); ++sr_cnt; return r; };
+                // O_i (in NAG mode both O) of the previous segment has been read out; passes at once for the first one
+                auto o_free_wait = [&]() { const bool r = mbar_wait(bar(BAR_OFREE + i), (of_cnt & 1u) ^ 1u, abort_flag); ++of_cnt; tc_fence_after(); return r; };
+                // S = Q_i K^T into the shared staging area as its g-th user, once user g-1 has read its scores out (at once for g = 0)
+                auto issue_S = [&](uint32_t g, uint32_t k_saddr) {
+                    if (!mbar_wait(bar(BAR_SFREE), (g & 1u) ^ 1u, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t blo = smem_desc_lo(k_saddr, 16);
+                    mma_ss_w<0>(tmem_base, q_lo, blo, DESC_HI, IDESC_S);
 #pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {
-                        const uint32_t off = (uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u;
-                        mma_ss(tmem_base + (uint32_t)(i * 128), smem_desc_sw128(q_saddr + off, 16, 1024),
-                               smem_desc_sw128(k_saddr + off, 16, 1024), IDESC_S, kk > 0);
+                    for (int kk = 1; kk < 8; kk++) {
+                        const uint32_t off = ((uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
+                        mma_ss_w<1>(tmem_base, q_lo + off, blo + off, DESC_HI, IDESC_S);
                     }
                     tc_commit(bar(BAR_SFULL + i));
+                    return true;
                 };
-                auto issue_PV = [&](int i, uint32_t v_saddr, int j, int Tk) {
+                // O_i (+)= P_i V; P_i may be overwritten and O_i rescaled once these MMAs are done
+                auto issue_PV = [&](uint32_t v_saddr, int j, int Tk, bool first) {
                     const int valid = min(BN, Tk - j * BN);
                     const int nkk = (valid + 15) >> 4;                        // 16 keys per MMA; P is 0 past `valid`
-                    for (int kk = 0; kk < nkk; kk++)
-                        mma_ts(tmem_base + 256u + (uint32_t)(i * 128), tmem_base + (uint32_t)(i * 128) + (uint32_t)(kk * 8),
-                               smem_desc_sw128(v_saddr + (uint32_t)kk * 2048u, HALF_BYTES, 1024), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                    const uint32_t blo = smem_desc_lo(v_saddr, HALF_BYTES);
+                    if (first) mma_ts_w<0>(tO, tP, blo, DESC_HI, IDESC_PV);
+                    else mma_ts_w<1>(tO, tP, blo, DESC_HI, IDESC_PV);
+#pragma unroll
+                    for (int kk = 1; kk < 8; kk++)
+                        if (kk < nkk) mma_ts_w<1>(tO, tP + (uint32_t)(kk * 8), blo + (uint32_t)(kk * 128), DESC_HI, IDESC_PV);
+                    tc_commit(bar(BAR_PEMPTY + i));
                 };
-                for (int w = blockIdx.x; w < p.n_items && good; w += gridDim.x) {
-                    const Item it = decode_item<MODE>(w, p);
+                SegIter<MODE> iter(p);
+                Seg it;
+                while (good && iter.next(it)) {
                     if (MODE == MODE_PAIR) {
-                        const int nb = it.nblk[0];
-                        const bool two = it.nblk[1] > 0;
-                        good = q_wait(0) && kv_wait(ring);
-                        if (!good) break;
-                        issue_S(0, kv_addr(ring));
-                        if (two) {
-                            good = q_wait(1);
+                        // ring order (loader): K(jb), then per block V(j), K(j+1). A K/V tile serves both streams; its slot is handed
+                        // back by the softmax threads once they have seen the MMAs on it complete.
+                        const int jb = it.jb, je = it.je[0];
+                        const bool two = it.je[1] > jb;
+                        const bool mine = i == 0 || two;
+                        const uint32_t per_blk = two ? 2u : 1u;               // S products per key block, in the order stream 0, stream 1
+                        if (mine) {
+                            good = q_wait() && kv_wait(ring) && issue_S(n_s + (uint32_t)i, kv_addr(ring));
                             if (!good) break;
-                            issue_S(1, kv_addr(ring));
                         }
-                        kv_release(ring);
                         ++ring;
-                        for (int j = 0; j < nb && good; ++j) {
-                            const uint32_t nv = ring, nk = ring + 1;
-                            const bool more = j + 1 < nb;
-                            good = kv_wait(nv) && (j > 0 || o_free_wait(0)) && p_wait(0);
-                            if (!good) break;
-                            issue_PV(0, kv_addr(nv), j, p.Tk[0]);
-                            if (!more) tc_commit(bar(BAR_ODONE + 0));
-                            if (more) {
-                                good = kv_wait(nk);
-                                if (!good) break;
-                                issue_S(0, kv_addr(nk));
-                            }
-                            if (two) {
-                                good = (j > 0 || o_free_wait(1)) && p_wait(1);
-                                if (!good) break;
-                                issue_PV(1, kv_addr(nv), j, p.Tk[0]);
-                                if (!more) tc_commit(bar(BAR_ODONE + 1));
-                            }
-                            kv_release(nv);
-                            ++ring;
-                            if (more) {
-                                if (two) issue_S(1, kv_addr(nk));
-                                kv_release(nk);
-                                ++ring;
-                            }
-                        }
-                    } else {
-                        good = q_wait(0);
-                        for (int i = 0; i < 2 && good; i++) {
-                            good = kv_wait(ring);
-                            if (good) { issue_S(i, kv_addr(ring)); kv_release(ring); ++ring; }
-                        }
-                        const int nmax = max(it.nblk[0], it.nblk[1]);
-                        for (int j = 0; j < nmax && good; ++j) {
-                            for (int i = 0; i < 2 && good; i++) {
-                                if (j >= it.nblk[i]) continue;
-                                good = kv_wait(ring) && (j > 0 || o_free_wait(i)) && p_wait(i);
-                                if (!good) break;
-                                issue_PV(i, kv_addr(ring), j, p.Tk[i]);
-                                if (j + 1 == it.nblk[i]) tc_commit(bar(BAR_ODONE + i));
-                                kv_release(ring);
-                                ++ring;
-                                if (j + 1 < it.nblk[i]) {
-                                    good = kv_wait(ring);
+                        for (int j = jb; j < je && good; ++j) {
+                            const uint32_t nv = ring, nk = ring + 1;          // V(j), K(j+1)
+                            const bool more = j + 1 < je;
+                            if (mine) {
+                                if (more) {
+                                    good = sreq_wait() && kv_wait(nk) && issue_S(n_s + per_blk * (uint32_t)(j + 1 - jb) + (uint32_t)i, kv_addr(nk));
                                     if (!good) break;
-                                    issue_S(i, kv_addr(ring));
-                                    kv_release(ring);
-                                    ++ring;
                                 }
+                                good = kv_wait(nv) && (j > jb || o_free_wait()) && p_wait();
+                                if (!good) break;
+                                issue_PV(kv_addr(nv), j, p.Tk[0], j == jb);
+                                if (!more) tc_commit(bar(BAR_ODONE + i));
+                            }
+                            ring += more ? 2u : 1u;
+                        }
+                        n_s += per_blk * (uint32_t)(je - jb);
+                    } else {
+                        // ring order (loader): K0(0), K1(0), then per block j and stream: V_i(j), K_i(j+1). Every tile belongs to
+                        // one stream. Staging-area order: S0(0), S1(0), then S_i(j+1) in the same (j, i) order.
+                        good = q_wait();
+                        uint32_t g = n_s;
+                        for (int ii = 0; ii < 2 && good; ii++) {
+                            if (it.je[ii] <= 0) continue;
+                            if (ii == i) {
+                                good = kv_wait(ring) && issue_S(g, kv_addr(ring));
+                            }
+                            ++ring;
+                            ++g;
+                        }
+                        const int nmax = max(it.je[0], it.je[1]);
+                        for (int j = 0; j < nmax && good; ++j) {
+                            for (int ii = 0; ii < 2 && good; ii++) {
+                                if (j >= it.je[ii]) continue;
+                                const bool more = j + 1 < it.je[ii];
+                                if (ii == i) {
+                                    if (more) {                               // ring: V_i(j), then K_i(j+1)
+                                        good = sreq_wait() && kv_wait(ring + 1) && issue_S(g, kv_addr(ring + 1));
+                                        if (!good) break;
+                                    }
+                                    good = kv_wait(ring) && (j > 0 || o_free_wait()) && p_wait();
+                                    if (!good) break;
+                                    issue_PV(kv_addr(ring), j, p.Tk[i], j == 0);
+                                    if (!more) tc_commit(bar(BAR_ODONE + i));
+                                }
+                                ring += more ? 2u : 1u;
+                                if (more) ++g;
                             }
                         }
+                        n_s = g;
                     }
                 }
             }
@@ -680,14 +906,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 uint32_t n = 0;
                 uint32_t qe_cnt[2] = {0, 0};
                 bool good = true;
-                Item it = {};
+                Seg it = {};
                 // one 128x128 tile = two 64-column boxes, each landing as a 128-byte-swizzled [128][64] half
                 auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0, int bb) {
                     tma_load_3d(dst, tm, mbar, it.h * HD, row0, bb);
                     tma_load_3d(dst + HALF_BYTES, tm, mbar, it.h * HD + 64, row0, bb);
                 };
                 auto load_q = [&](int i) {
-                    // the previous item's S MMAs (and its output staging in the same space) are done with this tile
+                    // the previous segment's S MMAs (and its output staging in the same space) are done with this tile
                     good = mbar_wait(bar(BAR_QEMPTY + i), (qe_cnt[i] & 1u) ^ 1u, abort_flag);
                     ++qe_cnt[i];
                     if (!good) return;
@@ -702,27 +928,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     load_tile(sKV + st * TILE_BYTES, tm, bar(BAR_KVFULL + st), row0, MODE == MODE_NAG ? 0 : it.b);
                     ++n;
                 };
-                for (int w = blockIdx.x; w < p.n_items && good; w += gridDim.x) {
-                    it = decode_item<MODE>(w, p);
+                SegIter<MODE> iter(p);
+                while (good && iter.next(it)) {
                     load_q(0);
                     if (!good) break;
                     if (MODE == MODE_PAIR) {
-                        const int nb = it.nblk[0];
-                        if (nb > 0) load_kv(&tmK0, 0);
-                        if (good && it.nblk[1] > 0) load_q(1);
-                        for (int j = 0; j < nb && good; ++j) {
+                        const int jb = it.jb, je = it.je[0];
+                        load_kv(&tmK0, jb * BN);
+                        if (good && it.je[1] > jb) load_q(1);
+                        for (int j = jb; j < je && good; ++j) {
                             load_kv(&tmV0, j * BN);
-                            if (good && j + 1 < nb) load_kv(&tmK0, (j + 1) * BN);
+                            if (good && j + 1 < je) load_kv(&tmK0, (j + 1) * BN);
                         }
                     } else {
-                        if (it.nblk[0] > 0) load_kv(&tmK0, 0);
-                        if (good && it.nblk[1] > 0) load_kv(&tmK1, 0);
-                        const int nmax = max(it.nblk[0], it.nblk[1]);
+                        if (it.je[0] > 0) load_kv(&tmK0, 0);
+                        if (good && it.je[1] > 0) load_kv(&tmK1, 0);
+                        const int nmax = max(it.je[0], it.je[1]);
                         for (int j = 0; j < nmax && good; ++j) {
                             for (int i = 0; i < 2 && good; i++) {
-                                if (j >= it.nblk[i]) continue;
+                                if (j >= it.je[i]) continue;
                                 load_kv(i ? &tmV1 : &tmV0, j * BN);
-                                if (good && j + 1 < it.nblk[i]) load_kv(i ? &tmK1 : &tmK0, (j + 1) * BN);
+                                if (good && j + 1 < it.je[i]) load_kv(i ? &tmK1 : &tmK0, (j + 1) * BN);
                             }
                         }
                     }

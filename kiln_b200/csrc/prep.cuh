@@ -110,6 +110,8 @@ struct PrepParams {
     int nseg, H;
     float eps;
     unsigned blocks;             // total thread blocks
+    unsigned int* zero_ptr;      // optional: zero_n words the first thread block clears (counters and flags that the
+    int zero_n;                  // attention kernel launched next on the stream expects at zero)
 };
 
 // Measured on B200: a plain one-16-byte-load-per-thread conversion runs at the speed of a device copy
@@ -121,6 +123,8 @@ constexpr int PREP_ITEMS_PER_BLOCK = 16;   // 256 threads / 16 lanes
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
 qk_prep_kernel(const __grid_constant__ PrepParams pp) {
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < pp.zero_n; i += 256) pp.zero_ptr[i] = 0u;
     int si = 0;
 #pragma unroll
     for (int i = 1; i < 5; i++)

@@ -335,3 +335,123 @@ def test_argument_errors(kb):
     assert kb.check_status() == 0
     with pytest.raises(kb.KilnError):
         kb.attn_cross(t, t, t, t, 256, 0, 0, 2)
+
+
+# ---------------------------------------------------------------- the exact variants the benchmark step times
+def _bits(w):
+    return (w.view(np.uint32) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("T,B,Hp,Wp", [(4096, 1, 64, 64), (3456, 2, 48, 72)])
+def test_self_benchmark_variant_bf16_in_bf16_out_norm_rope(kb, T, B, Hp, Wp):
+    """kb_attn_self exactly as bench.py calls it: bf16 Q/K/V as thirds of one buffer, per-head Q/K RMSNorm, 3D RoPE,
+    bf16 OUTPUT (staged in shared memory and written by TMA stores), full size; also the same call with fp16 output.
+    Both sizes take the balanced schedule (items cut across SMs, partial results merged)."""
+    H, kind = 16, "bf16"
+    D = H * 128
+    big = seeded(21, B * T, 3 * D, kind)
+    q, k, v = (np.ascontiguousarray(big[:, i * D:(i + 1) * D]) for i in range(3))
+    wq = oracle.round16(1 + 0.02 * oracle.randn(7, 128), 1)
+    wk = oracle.round16(1 + 0.02 * oracle.randn(8, 128), 1)
+    c, s = oracle.cosmos_rope(Hp, Wp)
+    dbig = dev(big, kind)
+    ws = _ws(kb, B * T, B * T, H, kind, norm=True)
+    kn = _norm_rope_ref(k, _bits(wk), H, T, c, s)
+    refs = []
+    for b in range(B):
+        rows = sample_rows(T, 24, seed=b)
+        qn_rows = _norm_rope_ref(q[b * T:(b + 1) * T], _bits(wq), H, T, c, s)[rows]
+        refs.append((rows + b * T, oracle.attention(qn_rows, kn[b * T:(b + 1) * T], v[b * T:(b + 1) * T], H)))
+    pick = np.concatenate([r for r, _ in refs])
+    ref = np.concatenate([x for _, x in refs])
+    for out_dt in (torch.bfloat16, torch.float16):
+        out = torch.full((B * T, D), float("nan"), device="cuda", dtype=out_dt)
+        kb.attn_self(out, dbig[:, :D], dbig[:, D:2 * D], dbig[:, 2 * D:], B, T, H, qn_w=dev(wq).bfloat16(), kn_w=dev(wk).bfloat16(),
+                     rope_cos=dev(c), rope_sin=dev(s), workspace=ws)
+        assert kb.check_status() == 0
+        o = out.float().cpu().numpy()
+        assert not np.isnan(o).any()
+        if out_dt == torch.bfloat16:
+            assert_close_bf16_storage(o[pick], ref, f"benchmark self T={T} B={B} bf16 out")
+        else:
+            assert_close(o[pick], ref, f"benchmark self T={T} B={B} fp16 out")
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+@pytest.mark.parametrize("Tq,Tp,Tn,s", [(130, 512, 512, 5.0), (300, 333, 45, 6.0), (1536, 512, 512, 6.0), (1536, 333, 45, 5.0),
+                                         (4096, 512, 512, 5.0), (4096, 333, 45, 5.0)])
+def test_nag_benchmark_variant_qnorm_16bit_out(kb, kind, Tq, Tp, Tn, s):
+    """kb_attn_nag exactly as bench.py calls it: fused Q RMSNorm (qn_w), 16-bit inputs, 16-BIT OUTPUT (blend staged in
+    shared memory, TMA stores), H = 16, full 512-key contexts (npad = 0) and ragged ones with analytic padding."""
+    H, L = 16, 512
+    q = seeded(31, Tq, H * 128, kind)
+    kp, vp, kn, vn = (seeded(sd, L, H * 128, kind) for sd in (32, 33, 34, 35))
+    wq = oracle.round16(1 + 0.02 * oracle.randn(36, 128), 1)
+    rows = sample_rows(Tq, 40)
+    qn = oracle.rmsnorm(q, _bits(wq), H)[rows]
+    ref, _ = _nag_ref(qn, kp, vp, Tp, L - Tp, kn, vn, Tn, L - Tn, s, 2.5, 0.25, H)
+    ws = torch.empty(kb.workspace_bytes(Tq, L, H, DT[kind], True, False, n_ctx=2), dtype=torch.uint8, device="cuda")
+    for out_dt in (DT[kind], torch.float32):
+        out = torch.full((Tq, H * 128), float("nan"), device="cuda", dtype=out_dt)
+        kb.attn_nag(out, dev(q, kind), dev(kp, kind), dev(vp, kind), Tp, L - Tp, dev(kn, kind), dev(vn, kind), Tn, L - Tn, s, 2.5, 0.25, Tq, H,
+                    qn_w=dev(wq).bfloat16(), workspace=ws)
+        assert kb.check_status() == 0
+        o = out.float().cpu().numpy()
+        assert not np.isnan(o).any()
+        what = f"benchmark NAG Tq={Tq} Tp={Tp} Tn={Tn} s={s} {kind} out={out_dt}"
+        if out_dt == torch.bfloat16:
+            assert_close_bf16_storage(o[rows], ref, what)
+        else:
+            assert_close(o[rows], ref, what)
+
+
+@pytest.mark.parametrize("T,H,B,kind", [(1536, 16, 1, "f16"), (2000, 3, 1, "bf16"), (4096, 2, 1, "bf16"), (900, 5, 3, "f16")])
+def test_balanced_schedule_equals_whole_items(kb, T, H, B, kind):
+    """The balanced (item, key block) schedule, taken when the workspace has room for partial results, against the
+    whole-items schedule of the same call without that room, and against the oracle: items cut across two or more SMs
+    (2 heads x 4096 tokens: an item spans five SMs), ragged token counts, a batch."""
+    q, k, v = (seeded(s, B * T, H * 128, kind) for s in (41, 42, 43))
+    dq, dk, dv = dev(q, kind), dev(k, kind), dev(v, kind)
+    full = torch.empty(kb.workspace_bytes(B * T, B * T, H, DT[kind]), dtype=torch.uint8, device="cuda")
+    stage_only = kb.workspace_bytes(B * T, B * T, H, DT[kind]) - kb.workspace_bytes(0, 0, H, DT[kind])
+    small = full[:stage_only] if stage_only else None
+    outs = []
+    for ws in (full, small):
+        o = torch.full((B * T, H * 128), float("nan"), device="cuda", dtype=torch.float32)
+        kb.attn_self(o, dq, dk, dv, B, T, H, workspace=ws)
+        assert kb.check_status() == 0
+        outs.append(o.cpu().numpy())
+    # a part that starts in the middle of the keys takes its own running maximum, so its fp16 weights P = 2^(s - m) round
+    # differently from the whole-item run's: agreement to a fraction of the tolerance, not to the bit
+    assert np.abs(outs[0] - outs[1]).max() <= 5e-4
+    for b in range(B):
+        rows = sample_rows(T, 24, seed=b)
+        sl = slice(b * T, (b + 1) * T)
+        assert_close(outs[0][sl][rows], oracle.attention(q[sl][rows], k[sl], v[sl], H), f"balanced schedule T={T} H={H} b={b}")
+    again = torch.empty(B * T, H * 128, device="cuda", dtype=torch.float32)
+    kb.attn_self(again, dq, dk, dv, B, T, H, workspace=full)
+    assert kb.check_status() == 0
+    assert np.array_equal(again.cpu().numpy(), outs[0])     # merge order is fixed: bit-identical repeat
+
+
+def test_alignment_of_weights_and_tables_is_an_error_code(kb):
+    """Norm weights and RoPE tables are read with 16-byte vector loads: a pointer that is not 16-byte aligned must come
+    back as KB_ERR_ALIGN from the host-side checks; nothing is launched."""
+    L = kb.lib()
+    t = torch.zeros(256, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(256, device="cuda", dtype=torch.bfloat16)
+    tab = torch.zeros(256 * 64 + 8, device="cuda", dtype=torch.float32)
+    ws = torch.empty(8 << 20, dtype=torch.uint8, device="cuda")
+    P = lambda x, off=0: ctypes.c_void_p(x.data_ptr() + off)
+    self_args = lambda qn, kn, c, s: (P(t), P(t), P(t), P(t), qn, kn, c, s, 1, 256, 2, 256, 256, 256, 256, 1, 1, 1e-6, P(ws), ws.numel(), None)
+    assert L.kb_attn_self(*self_args(P(w, 2), None, None, None)) == -2
+    assert L.kb_attn_self(*self_args(None, P(w, 8), None, None)) == -2
+    assert L.kb_attn_self(*self_args(None, None, P(tab, 4), P(tab))) == -2
+    assert L.kb_attn_self(*self_args(None, None, P(tab), P(tab, 8))) == -2
+    assert L.kb_attn_self(*self_args(P(w), P(w, 16), P(tab), P(tab, 32))) == 0
+    assert L.kb_attn_nag(P(t), P(t), P(w, 2), P(t), P(t), 10, 0, P(t), P(t), 10, 0, 5.0, 2.5, 0.25, 256, 2, 256, 256, 256, 1, 1, 1e-6,
+                         P(ws), ws.numel(), None) == -2
+    assert L.kb_qk_prep(P(t), 256, 1, P(t), 256, 1, 256, 2, 256, P(w, 2), 1e-6, None, None, None) == -2
+    assert L.kb_qk_prep(P(t), 256, 1, P(t), 256, 1, 256, 2, 256, None, 1e-6, P(tab, 4), P(tab), None) == -2
+    assert L.kb_attn_self(P(t), P(t), P(t), P(t), None, None, None, None, 1, 1, 5000, 256, 256, 256, 256, 1, 1, 1e-6, P(ws), ws.numel(), None) == -3
+    assert kb.check_status() == 0

@@ -1,0 +1,121 @@
+"""Live pin: when the reference's own kernels are built (oracle/_ref/libkiln_ref.so, compiled from the reference
+tree by oracle/build.py --ref), run them again on the fixture inputs and require (1) that they reproduce the
+committed fixtures, so the pin does not rest on the committed file alone, and (2) that this library's kernels agree
+with what the reference kernels return now. Skipped where the reference library was not built."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from golden_inputs import gen
+from util_gpu import assert_close, dev
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "oracle", "_ref", "libkiln_ref.so")
+P = lambda t: ctypes.c_void_p(t.data_ptr())
+f = ctypes.c_float
+
+
+@pytest.fixture(scope="module")
+def R():
+    if not os.path.exists(REF):
+        pytest.skip("the reference kernels are not built here (oracle/build.py --ref)")
+    return ctypes.CDLL(REF)
+
+
+@pytest.fixture(scope="module")
+def kb(built_lib):
+    import kiln_b200
+    assert kiln_b200.lib().kb_init() == 0
+    return kiln_b200
+
+
+@pytest.mark.parametrize("case", gen.ATTN_CASES, ids=[c[0] for c in gen.ATTN_CASES])
+def test_reference_attention_kernels_reproduce_fixture_and_match_ours(R, kb, golden, case):
+    name, Tq, Tk, npad, H = case
+    q, k, v = gen.attn_inputs(case)
+    ld = H * 128
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    o = torch.zeros(Tq, ld, device="cuda")
+    assert R.kref_ref_attn(P(o), P(dq), P(dk), P(dv), Tq, Tk, H, ld, npad) == 0
+    o16 = torch.zeros(Tq, ld, device="cuda", dtype=torch.float16)
+    assert R.kref_tfa_f16(P(o16), ld, P(dq), ld, P(dk), ld, P(dv), ld, Tq, Tk, H, npad) == 0
+    torch.cuda.synchronize()
+    ref_now, tfa_now = o.cpu().numpy(), o16.cpu().numpy()
+    np.testing.assert_allclose(ref_now, golden[f"{name}/ref_attn"], rtol=0, atol=1e-6)     # same kernel, same GPU family: equal up to libm
+    assert np.array_equal(tfa_now, golden[f"{name}/tfa_f16"])
+    ours = torch.zeros(Tq, ld, device="cuda", dtype=torch.float32)
+    kb.attn_cross(ours, dq.half(), dk.half(), dv.half(), Tq, Tk, npad, H)
+    ours16 = torch.zeros(Tq, ld, device="cuda", dtype=torch.float16)
+    kb.attn_cross(ours16, dq.half(), dk.half(), dv.half(), Tq, Tk, npad, H)
+    assert kb.check_status() == 0
+    assert_close(ours.cpu().numpy(), ref_now, f"{name}: kb_attn_cross vs live ref_attn")
+    assert_close(ours16.float().cpu().numpy(), tfa_now.astype(np.float32), f"{name}: kb_attn_cross fp16 vs live tfa::k_flash")
+
+
+def test_reference_norm_rope_nag_reproduce_fixture_and_match_ours(R, kb, golden):
+    x, w_bits, H = gen.norm_inputs()
+    dx = dev(x)
+    dw = torch.from_numpy(w_bits.view(np.int16)).cuda()
+    y = torch.zeros_like(dx)
+    assert R.kref_rmsnorm(P(y), P(dx), P(dw), x.shape[0] * H, 128, f(1e-6)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), golden["rmsnorm/out"])
+    ours = torch.empty_like(dx)
+    kb.qk_prep(ours, dx, x.shape[0], H, x.shape[0], w=dw.view(torch.bfloat16))
+    np.testing.assert_allclose(ours.cpu().numpy(), y.cpu().numpy(), rtol=2e-6, atol=1e-6)
+
+    x, Hp, Wp, H = gen.rope_inputs()
+    c = np.zeros((Hp * Wp, 64), np.float32)
+    s = np.zeros_like(c)
+    R.kref_cosmos_rope(c.ctypes.data_as(ctypes.c_void_p), s.ctypes.data_as(ctypes.c_void_p), Hp, Wp)
+    assert np.array_equal(c, golden["rope/cos"]) and np.array_equal(s, golden["rope/sin"])
+    oc, os_ = oracle.cosmos_rope(Hp, Wp)
+    assert np.array_equal(oc, c) and np.array_equal(os_, s)                                   # the table the benchmark builds
+    dx = dev(x)
+    assert R.kref_rope_half(P(dx), Hp * Wp, H, 128, P(dev(c)), P(dev(s))) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dx.cpu().numpy(), golden["rope/out"])
+    ours = torch.empty_like(dx)
+    kb.qk_prep(ours, dev(x), x.shape[0], H, Hp * Wp, rope_cos=dev(c), rope_sin=dev(s))
+    np.testing.assert_allclose(ours.cpu().numpy(), dx.cpu().numpy(), rtol=2e-6, atol=1e-6)
+
+    zp, zn = gen.nag_inputs()
+    for i, (sc, tau, alpha) in enumerate(gen.NAG_PARAMS):
+        a, n = dev(zp), dev(zn)
+        assert R.kref_nag_f32(P(a), P(n), gen.NAG_T, gen.NAG_DIM, f(sc), f(tau), f(alpha)) == 0
+        a16, n16 = dev(zp).half(), dev(zn).half()
+        assert R.kref_nag_f16(P(a16), P(n16), gen.NAG_T, gen.NAG_DIM, f(sc), f(tau), f(alpha)) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(a.cpu().numpy(), golden[f"nag/f32_{i}"])
+        assert np.array_equal(a16.cpu().numpy(), golden[f"nag/f16_{i}"])
+        mine = dev(zp)
+        kb.nag_combine(mine, dev(zn), sc, tau, alpha)
+        np.testing.assert_allclose(mine.cpu().numpy(), a.cpu().numpy(), rtol=2e-5, atol=1e-6)
+    assert kb.check_status() == 0
+
+
+def test_fused_nag_attention_vs_reference_unfused_sequence(R, kb):
+    """The engine's sequence on its fp16-activation path (engine/src/dit.cu:476-487): attention16 to the positive context,
+    attention16 to the negative one, k_nag<__half> in place -- run with the reference's kernels -- against kb_attn_nag."""
+    Tq, H, L, Tp, Tn = 520, 16, 512, 333, 45
+    ld = H * 128
+    q = oracle.round16(oracle.randn(51, Tq * ld), 0).reshape(Tq, ld)
+    ctx = [oracle.round16(oracle.randn(52 + i, L * ld), 0).reshape(L, ld) for i in range(4)]
+    dq, dctx = dev(q), [dev(x) for x in ctx]
+    a16 = torch.zeros(Tq, ld, device="cuda", dtype=torch.float16)
+    n16 = torch.zeros(Tq, ld, device="cuda", dtype=torch.float16)
+    assert R.kref_tfa_f16(P(a16), ld, P(dq), ld, P(dctx[0]), ld, P(dctx[1]), ld, Tq, Tp, H, L - Tp) == 0
+    assert R.kref_tfa_f16(P(n16), ld, P(dq), ld, P(dctx[2]), ld, P(dctx[3]), ld, Tq, Tn, H, L - Tn) == 0
+    assert R.kref_nag_f16(P(a16), P(n16), Tq, ld, f(5.0), f(2.5), f(0.25)) == 0
+    torch.cuda.synchronize()
+    out = torch.zeros(Tq, ld, device="cuda", dtype=torch.float16)
+    ws = torch.empty(kb.workspace_bytes(Tq, L, H, torch.float16, n_ctx=2), dtype=torch.uint8, device="cuda")
+    kb.attn_nag(out, dq.half(), dctx[0].half(), dctx[1].half(), Tp, L - Tp, dctx[2].half(), dctx[3].half(), Tn, L - Tn, 5.0, 2.5, 0.25, Tq, H,
+                workspace=ws)
+    assert kb.check_status() == 0
+    assert_close(out.float().cpu().numpy(), a16.float().cpu().numpy(), "kb_attn_nag vs reference attention16 x2 + k_nag")

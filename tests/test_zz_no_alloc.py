@@ -3,6 +3,7 @@
 a fixed 32 MiB array inside the library, so this test checks, through the C ABI, that
   * two calls in a row (the second must not be disturbed by what the first left in the array) give what
     kb_attn_self gives with a caller-owned workspace, within the suite's tolerance;
+  * the call leaves the driver's free-memory figure where it was (nothing was allocated behind the caller's back);
   * a problem that does not fit the array is refused with KB_ERR_STATIC_SCRATCH and launches nothing.
 This file sorts last on purpose: a run that stops at the first failure has then run everything else."""
 import ctypes
@@ -53,7 +54,31 @@ def test_static_scratch_matches_workspace_entry_point_twice(built_lib):
         assert not np.isnan(out).any()
         e_max, e_rel, _ = errors(out, ref)
         assert e_max <= TOL_MAX_ABS and e_rel <= TOL_MEAN_REL, f"static vs workspace entry point: max_abs {e_max:.3e} mean_rel {e_rel:.3e}"
-        assert np.array_equal(out, ref)          # same kernels on the same bytes: the two entry points agree exactly
+        assert np.array_equal(out, ref)          # same kernels, same schedule (whole items per SM at these sizes), same bytes
+
+
+def test_static_scratch_call_allocates_nothing(built_lib):
+    """Free device memory as the driver reports it is the same before and after a call (all tensors exist beforehand,
+    the entry point was used before, and nothing else allocates in between)."""
+    import kiln_b200 as kb
+    L = kb.lib()
+    assert L.kb_init() == 0
+    T, H = 768, 16
+    ld = H * 128
+    q, k, v = (dev(seeded(300 + i, T, ld, "bf16"), "bf16") for i in range(3))
+    w = dev(1 + 0.02 * oracle.randn(303, 128)).to(torch.bfloat16)
+    c, s = (dev(a) for a in oracle.cosmos_rope(24, 32))
+    out = torch.empty(T, ld, device="cuda", dtype=torch.bfloat16)
+    call = lambda: L.kb_attn_self_static(P(out), P(q), P(k), P(v), P(w), P(w), P(c), P(s), 1, T, H, ld, ld, ld, ld, kb.KB_BF16, kb.KB_BF16, 1e-6, None)
+    assert call() == 0                             # first use on this device: looks up the array's address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert call() == 0
+    assert call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert kb.check_status() == 0
 
 
 def test_static_scratch_refuses_oversize(built_lib):
@@ -72,4 +97,6 @@ def test_static_scratch_refuses_oversize(built_lib):
     th = torch.zeros(T, H * 128, device="cuda", dtype=torch.float16)
     oh = torch.empty_like(th)
     assert L.kb_attn_self_static(P(oh), P(th), P(th), P(th), None, None, None, None, 1, T, H, 2048, 2048, 2048, 2048, kb.KB_F16, kb.KB_F16, 1e-6, None) == 0
+    # a head count that would overflow the size arithmetic is refused before anything is computed from it
+    assert L.kb_attn_self_static(P(oh), P(th), P(th), P(th), None, None, None, None, 1, 16, 1 << 24, 2048, 2048, 2048, 2048, kb.KB_F16, kb.KB_F16, 1e-6, None) == -3
     assert kb.check_status() == 0
