@@ -151,6 +151,31 @@ int kb_attn_push(void* const* out_peers, unsigned long long* const* ctr_peers, i
                  const float* rope_cos, const float* rope_sin,
                  int B, int Tq, int Tk, int npad, int H_local, int ld_q, int ld_k, int ld_v, int ld_o,
                  int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes, void* stream);
+/* Head-split NAG: kb_attn_nag over the local heads of one GPU. The per-token norms of the combine span all heads of the
+ * model, so every thread block stores its head's two norms per row (2 floats per token and head, engine/src/dit.cu:295-324
+ * computes them over the full row) into the exchange area of EVERY GPU (part_peers, plain peer stores) and bumps every
+ * GPU's per-query-tile counter (flag_peers); it then waits, bounded, until its own GPU's counter shows all heads_total
+ * heads of the tile, blends in fp32 exactly as the single-GPU kernel does, and stores the finished tile into every GPU's
+ * output buffer at column col0 (then bumps ctr_peers as kb_attn_push does). Only final tiles and 8 bytes per token and
+ * head cross NVLink. All GPUs must make the matching call (it is a collective). `self` = this GPU's index in the peer
+ * arrays, h0 = its first head, epoch = 1, 2, 3 ... = how many times this exchange area has been used including this call
+ * (its counters only grow and are never cleared, so a fast GPU's arrivals for the next call cannot be lost); an exchange
+ * area is kb_nag_exchange_bytes(Tq, heads_total) bytes of zero-initialised peer-visible memory: the norms first, the
+ * counters after them. A call may follow the previous one only when every GPU has finished that previous kernel
+ * (kb_bump_counters / kb_wait_arrivals carry that hand-shake between streams of different GPUs). */
+int kb_attn_nag_push(void* const* out_peers, unsigned long long* const* ctr_peers, float* const* part_peers, unsigned int* const* flag_peers,
+                     int n_peers, int self, int col0, int h0, int heads_total, unsigned epoch,
+                     const void* q, const void* qn_w, const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
+                     const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg, float scale, float tau, float alpha,
+                     int Tq, int H_local, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t kb_nag_exchange_bytes(int Tq, int heads_total);
+/* Buffer reuse across GPUs. Nothing above stops a fast GPU from pushing call n+1 into a buffer that a slow GPU is still
+ * reading for call n. The hand-shake: when a GPU is done with a buffer it enqueues kb_bump_counters on the "released"
+ * counters of that buffer on every GPU (one system-scope add each, ordered after everything enqueued before it on the
+ * stream); before a GPU pushes use n+1 it enqueues kb_wait_arrivals on its OWN released counter with target n * n_gpus.
+ * Counters only grow. */
+int kb_bump_counters(unsigned long long* const* ctr_peers, int n_peers, void* stream);
 unsigned long long kb_push_arrivals_per_call(int B, int Tq, int H_local, int n_peers);
 int kb_wait_arrivals(const unsigned long long* ctr, unsigned long long target, void* stream);
 

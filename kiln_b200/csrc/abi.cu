@@ -413,31 +413,59 @@ int kb_attn_cross(void* out, const void* q, const void* qn_w, const void* k, con
                      eps, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
-int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
-                const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg, float scale, float tau, float alpha, int Tq,
-                int H, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
-                size_t workspace_bytes, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// Head split of the NAG kernel: where the norms of all heads and the output tiles go on every GPU
+struct NagPeerSpec {
+    void* const* out_peers;
+    unsigned long long* const* ctr_peers;
+    float* const* part_peers;
+    unsigned int* const* flag_peers;
+    int n_peers, self, col0, h0, heads_total;
+    unsigned int epoch;
+};
+
+static int nag_impl(void* out, const void* q, const void* qn_w, const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
+                    const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg, float scale, float tau, float alpha, int Tq,
+                    int H, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream, const NagPeerSpec* peers) {
     if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (Tq <= 0 || Tk_pos <= 0 || Tk_neg <= 0 || H <= 0 || npad_pos < 0 || npad_neg < 0) return KB_ERR_ARG;
     if (H > 64) return KB_ERR_SHAPE;                   // the heads of a query tile run on H different SMs at once
     if (!aligned16(qn_w)) return KB_ERR_ALIGN;         // read with 16-byte vector loads by the pre-pass
+    if (peers) {
+        if (peers->n_peers < 1 || peers->n_peers > MAX_PEERS || peers->self < 0 || peers->self >= peers->n_peers || peers->col0 < 0 ||
+            (peers->col0 & 7) || peers->h0 < 0 || peers->heads_total < peers->h0 + H || peers->epoch == 0 || out_dtype == KB_F32)
+            return KB_ERR_ARG;
+        if (ld_o < peers->col0 + H * 128) return KB_ERR_SHAPE;
+        for (int i = 0; i < peers->n_peers; i++) {
+            if (!peers->out_peers[i] || !peers->ctr_peers[i] || !peers->part_peers[i] || !peers->flag_peers[i]) return KB_ERR_ARG;
+            if (!aligned16(peers->out_peers[i])) return KB_ERR_ALIGN;
+        }
+        out = peers->out_peers[peers->self];
+    }
     int rc;
     if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k_pos, ld_kv, H, dtype)) || (rc = check_mat(v_pos, ld_kv, H, dtype)) ||
-        (rc = check_mat(k_neg, ld_kv, H, dtype)) || (rc = check_mat(v_neg, ld_kv, H, dtype)) || (rc = check_out(out, ld_o, H, out_dtype)))
+        (rc = check_mat(k_neg, ld_kv, H, dtype)) || (rc = check_mat(v_neg, ld_kv, H, dtype)) || (rc = check_out(out, ld_o, peers ? 0 : H, out_dtype)))
         return rc;
     DeviceState* st;
     if ((rc = get_state(&st))) return rc;
     const bool conv = dtype != KB_F16;
-    if (!workspace || !aligned16(workspace)) return KB_ERR_WORKSPACE;   // always: the cross-head norm exchange lives there
-    Stage sg{static_cast<char*>(workspace), workspace_bytes};
     const int n_qt = (Tq + BM - 1) / BM;
-    float* nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * 256 * sizeof(float)));
-    unsigned int* nag_flag = static_cast<unsigned int*>(sg.take_bytes((size_t)n_qt * sizeof(unsigned int)));
-    if (sg.overflow) return KB_ERR_WORKSPACE;
+    Stage sg{static_cast<char*>(workspace), workspace_bytes};
     PrepBatch pb;
-    pb.zero(nag_flag, n_qt);                           // cleared by the pre-pass, or by a memset when nothing is staged
     pb.pp.H = H; pb.pp.eps = eps;
+    float* nag_part = nullptr;
+    unsigned int* nag_flag = nullptr;
+    if (!peers) {
+        if (!workspace || !aligned16(workspace)) return KB_ERR_WORKSPACE;   // always: the cross-head norm exchange lives there
+        nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * 256 * sizeof(float)));
+        nag_flag = static_cast<unsigned int*>(sg.take_bytes((size_t)n_qt * sizeof(unsigned int)));
+        if (sg.overflow) return KB_ERR_WORKSPACE;
+        pb.zero(nag_flag, n_qt);                       // cleared by the pre-pass, or by a memset when nothing is staged
+    } else {
+        if ((conv || qn_w) && (!workspace || !aligned16(workspace))) return KB_ERR_WORKSPACE;
+        nag_part = peers->part_peers[peers->self];     // the exchange lives in the peer-visible buffers; their counters only grow
+        nag_flag = peers->flag_peers[peers->self];
+    }
     const void* qq = q;
     const void* kv[4] = {k_pos, v_pos, k_neg, v_neg};
     const int kv_rows[4] = {Tk_pos, Tk_pos, Tk_neg, Tk_neg};
@@ -463,11 +491,28 @@ int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, c
     p.Tk[0] = Tk_pos; p.Tk[1] = Tk_neg; p.npad[0] = npad_pos; p.npad[1] = npad_neg;
     p.n_items = n_qt * H;
     p.nag_part = nag_part; p.nag_flag = nag_flag;
+    p.nag_heads = H; p.nag_h0 = 0; p.nag_epoch = 1;
+    if (peers) {
+        p.n_peers = peers->n_peers; p.col0 = peers->col0;
+        p.nag_heads = peers->heads_total; p.nag_h0 = peers->h0; p.nag_epoch = peers->epoch;
+        for (int i = 0; i < peers->n_peers; i++) {
+            p.out_peers[i] = peers->out_peers[i]; p.ctr_peers[i] = peers->ctr_peers[i];
+            p.nag_part_peers[i] = peers->part_peers[i]; p.nag_flag_peers[i] = peers->flag_peers[i];
+        }
+    }
     p.scale_log2 = SCALE_LOG2;
     p.nag_s = scale; p.nag_tau = tau; p.nag_alpha = alpha;
     p.status = st->status;
     ProfScope ps(st, KB_PROF_NAG, stream);
     return launch_attn<MODE_NAG>(out_dtype, tq, tk0, tv0, tk1, tv1, p, st->sm_count, stream);
+}
+
+int kb_attn_nag(void* out, const void* q, const void* qn_w, const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos,
+                const void* k_neg, const void* v_neg, int Tk_neg, int npad_neg, float scale, float tau, float alpha, int Tq,
+                int H, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps, void* workspace,
+                size_t workspace_bytes, void* stream_) {
+    return nag_impl(out, q, qn_w, k_pos, v_pos, Tk_pos, npad_pos, k_neg, v_neg, Tk_neg, npad_neg, scale, tau, alpha, Tq, H, ld_q, ld_kv,
+                    ld_o, dtype, out_dtype, eps, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_), nullptr);
 }
 
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype, int rows, int H, int T,
@@ -728,6 +773,32 @@ int kb_attn_push(void* const* out_peers, unsigned long long* const* ctr_peers, i
     PeerSpec ps{out_peers, ctr_peers, n_peers, col0};
     return attn_pair(nullptr, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, Tq, Tk, npad, H_local, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype, eps,
                      workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &ps);
+}
+
+int kb_attn_nag_push(void* const* out_peers, unsigned long long* const* ctr_peers, float* const* part_peers, unsigned int* const* flag_peers,
+                     int n_peers, int self, int col0, int h0, int heads_total, unsigned epoch, const void* q, const void* qn_w,
+                     const void* k_pos, const void* v_pos, int Tk_pos, int npad_pos, const void* k_neg, const void* v_neg, int Tk_neg,
+                     int npad_neg, float scale, float tau, float alpha, int Tq, int H_local, int ld_q, int ld_kv, int ld_o, int dtype,
+                     int out_dtype, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!out_peers || !ctr_peers || !part_peers || !flag_peers) return KB_ERR_ARG;
+    NagPeerSpec ps{out_peers, ctr_peers, part_peers, flag_peers, n_peers, self, col0, h0, heads_total, epoch};
+    return nag_impl(nullptr, q, qn_w, k_pos, v_pos, Tk_pos, npad_pos, k_neg, v_neg, Tk_neg, npad_neg, scale, tau, alpha, Tq, H_local, ld_q,
+                    ld_kv, ld_o, dtype, out_dtype, eps, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), &ps);
+}
+
+size_t kb_nag_exchange_bytes(int Tq, int heads_total) {
+    if (Tq <= 0 || heads_total <= 0) return 0;
+    const size_t n_qt = ((size_t)Tq + 127) / 128;
+    return align256(n_qt * heads_total * 256 * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+}
+
+int kb_bump_counters(unsigned long long* const* ctr_peers, int n_peers, void* stream) {
+    if (!ctr_peers || n_peers < 1 || n_peers > MAX_PEERS) return KB_ERR_ARG;
+    BumpList bl = {};
+    for (int i = 0; i < n_peers; i++) { if (!ctr_peers[i]) return KB_ERR_ARG; bl.ctr[i] = ctr_peers[i]; }
+    bl.n = n_peers;
+    bump_counters_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(bl);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 unsigned long long kb_push_arrivals_per_call(int B, int Tq, int H_local, int n_peers) {

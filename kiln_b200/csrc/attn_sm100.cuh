@@ -44,7 +44,12 @@
 // warpgroups on one stream's block with half of the keys per thread: the exponentials are bound by the
 // 16-per-clock MUFU unit whatever the thread count, and the two softmaxes can then no longer overlap, 12 % slower.
 // 2^x by polynomial on the FMA pipe for part of the scores: packed f32x2 instructions issue at half rate on B200
-// (measured: 2 cycles per warp instruction), so the polynomial costs more pipe time than the MUFU it saves.)
+// (measured: 2 cycles per warp instruction), so the polynomial costs more pipe time than the MUFU it saves.
+// Exponentials against the stale maximum with the block maximum tracked on the side and a redo on overflow: the extra
+// instructions in the exponential loop cost more than the ~400-cycle maximum phase they remove, 12 % slower.
+// Strict turns of the two streams at their exponential phase, so that one stream's MUFU work runs under the other's
+// MUFU-free work: a warpgroup alone runs its exponentials at ~24 cycles per score pair, not the 16 MUFU allows, so two
+// overlapping exponential phases use MUFU better than two exclusive ones, 15 % slower.)
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -98,8 +103,16 @@ struct AttnParams {
     int npad[2];
     float scale_log2;   // log2(e) / sqrt(128)
     float nag_s, nag_tau, nag_alpha;
-    float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][H][2][128]: per head |Z+|_1 and |g|_1 of each row
-    unsigned int* nag_flag;  // MODE_NAG [ceil(Tq/128)] arrival counters, zero before the launch
+    float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][nag_heads][2][128]: per head |Z+|_1 and |g|_1 of each row
+    unsigned int* nag_flag;  // MODE_NAG [ceil(Tq/128)] arrival counters: a tile is complete at nag_epoch * nag_heads
+    // The per-token norms span ALL heads of the model. Single GPU: nag_heads = H, nag_h0 = 0, nag_epoch = 1 and the counters
+    // are zeroed before the launch. Head split: this GPU holds heads [nag_h0, nag_h0 + H) of nag_heads; every CTA stores its
+    // head's two norms per row into the scratch of EVERY GPU (nag_part_peers) and bumps every GPU's counter
+    // (nag_flag_peers), so each GPU blends with the norms over all heads; the counters only grow (nag_epoch-th call).
+    int nag_heads, nag_h0;
+    unsigned int nag_epoch;
+    float* nag_part_peers[MAX_PEERS];
+    unsigned int* nag_flag_peers[MAX_PEERS];
     int split;          // MODE_PAIR: balanced (item, key block) ranges per CTA with partial results merged
     float* part;        // split: [gridDim.x] slots of PART_CTA_BYTES
     unsigned int* part_flag;  // split: [gridDim.x][2 streams], zero before the launch; 1 = slot written
@@ -659,29 +672,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 f_part[(wg * 2 + 1) * 128 + t] = lg;
                 named_bar_sync(1, 256);
                 // publish this head's norms: warpgroup 0 writes |Z+|_1, warpgroup 1 writes |g|_1 (fixed order: deterministic)
-                float* const gpart = p.nag_part + ((size_t)it.qt * p.H) * 256;   // [H][2][128] of this query tile
-                gpart[(size_t)it.h * 256 + wg * 128 + t] = f_part[(0 * 2 + wg) * 128 + t] + f_part[(1 * 2 + wg) * 128 + t];
-                __threadfence();
+                const size_t tile_off = ((size_t)it.qt * p.nag_heads) * 256;        // [nag_heads][2][128] of this query tile
+                const size_t mine_off = tile_off + (size_t)(p.nag_h0 + it.h) * 256 + wg * 128 + t;
+                const float my_norm = f_part[(0 * 2 + wg) * 128 + t] + f_part[(1 * 2 + wg) * 128 + t];
+                const uint32_t target = p.nag_epoch * (uint32_t)p.nag_heads;
+                if (p.n_peers == 0) {
+                    p.nag_part[mine_off] = my_norm;
+                    __threadfence();
+                } else {
+                    for (int pe = 0; pe < p.n_peers; pe++) p.nag_part_peers[pe][mine_off] = my_norm;   // plain stores over NVLink
+                    __threadfence_system();
+                }
                 named_bar_sync(1, 256);
                 if (tid == 0) {
-                    // arrive, then wait (bounded) for the other heads of this query tile: they are adjacent work items
-                    // and therefore in flight on other SMs now (the launch is cooperative: all CTAs are resident)
-                    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + it.qt), "r"(1u) : "memory");
-                    const uint64_t t0 = globaltimer_ns();
+                    // arrive, then wait (bounded) for the other heads of this query tile. On one GPU they are adjacent work
+                    // items and therefore in flight on other SMs now (the launch is cooperative: all CTAs are resident); under
+                    // head split the other GPUs run the same launch and walk the query tiles in the same order.
                     uint32_t seen = 0;
+                    if (p.n_peers == 0) {
+                        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + it.qt), "r"(1u) : "memory");
+                    } else {
+                        for (int pe = 0; pe < p.n_peers; pe++)
+                            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.nag_flag_peers[pe] + it.qt), "r"(1u) : "memory");
+                    }
+                    const uint64_t t0 = globaltimer_ns();
                     for (;;) {
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
-                        if (seen >= (uint32_t)p.H || *abort_flag) break;
+                        if (p.n_peers == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
+                        else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
+                        if (seen >= target || *abort_flag) break;
                         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
                         __nanosleep(32);
                     }
-                    wg_here[0] = (seen >= (uint32_t)p.H) ? 1u : 0u;
+                    wg_here[0] = (seen >= target) ? 1u : 0u;
                 }
                 named_bar_sync(1, 256);
                 const bool all_here = wg_here[0] != 0u;
                 float tot = 0.f;
                 if (all_here)
-                    for (int hh = 0; hh < p.H; hh++) tot += __ldcg(gpart + (size_t)hh * 256 + wg * 128 + t);   // head order: same sum everywhere
+                    for (int hh = 0; hh < p.nag_heads; hh++) tot += __ldcg(p.nag_part + tile_off + (size_t)hh * 256 + wg * 128 + t);   // head order: same sum everywhere
                 f_part[wg * 128 + t] = tot;                                 // [2 norms][128] (the column-half partials were consumed above)
                 named_bar_sync(1, 256);
                 const float ratio = f_part[128 + t] / fmaxf(f_part[t], 1e-12f);
@@ -725,11 +753,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         fence_proxy_async_smem();
                     }
                     named_bar_sync(1, 256);
-                    if (go && tid == 0) {                                     // rows past Tq are clipped by the tensor map
-                        tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0, 0);
-                        tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0, 0);
-                        tma_store_commit();
-                        tma_store_wait_read();                                // before the next item blends into this space
+                    if (p.n_peers == 0) {
+                        if (go && tid == 0) {                                 // rows past Tq are clipped by the tensor map
+                            tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0, 0);
+                            tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0, 0);
+                            tma_store_commit();
+                            tma_store_wait_read();                            // before the next item blends into this space
+                        }
+                    } else {
+                        // head split: each of the eight warps copies 16 rows out as whole 256-byte rows to every GPU's buffer
+                        if (go) {
+                            const int lr0 = 16 * warp;
+                            const int row0 = it.q0 + lr0;
+                            const int nrow = p.Tq - row0;                     // rows of this warp that exist (warp-uniform)
+                            uint2 vals[16];
+#pragma unroll
+                            for (int rr = 0; rr < 16; rr++)
+                                vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                           ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                            const size_t off = (size_t)row0 * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                            for (int pe = 0; pe < p.n_peers; pe++) {
+                                OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                                for (int rr = 0; rr < 16; rr++)
+                                    if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                            }
+                            __threadfence_system();                           // the tile is visible to every GPU before the arrival
+                        }
+                        named_bar_sync(1, 256);                               // every warp is done with the staging tile
+                        if (go && tid < p.n_peers) atomicAdd_system(p.ctr_peers[tid], 1ull);
                     }
                 } else {
                     const int row = it.q0 + t;

@@ -76,4 +76,17 @@ __global__ void wait_arrivals_kernel(const unsigned long long* ctr, unsigned lon
     }
 }
 
+// One thread per listed counter adds 1 with system scope after a system-scope fence: "this GPU has finished what came
+// before this kernel on its stream" - the release side of the buffer-reuse protocol of head-split runs.
+struct BumpList {
+    unsigned long long* ctr[8];
+    int n;
+};
+__global__ void bump_counters_kernel(const BumpList bl) {
+    if ((int)threadIdx.x < bl.n) {
+        __threadfence_system();
+        atomicAdd_system(bl.ctr[threadIdx.x], 1ull);
+    }
+}
+
 }  // namespace kb

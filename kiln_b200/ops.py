@@ -68,6 +68,13 @@ def lib():
         L.kb_ipc_close.argtypes = [vp]
         L.kb_attn_push.restype = i
         L.kb_attn_push.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i, i, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_attn_nag_push.restype = i
+        L.kb_attn_nag_push.argtypes = [ctypes.POINTER(vp)] * 4 + [i, i, i, i, i, ctypes.c_uint, vp, vp, vp, vp, i, i, vp, vp, i, i, f, f, f,
+                                       i, i, i, i, i, i, i, f, vp, sz, vp]
+        L.kb_nag_exchange_bytes.restype = sz
+        L.kb_nag_exchange_bytes.argtypes = [i, i]
+        L.kb_bump_counters.restype = i
+        L.kb_bump_counters.argtypes = [ctypes.POINTER(vp), i, vp]
         L.kb_push_arrivals_per_call.restype = ull
         L.kb_push_arrivals_per_call.argtypes = [i, i, i, i]
         L.kb_wait_arrivals.restype = i
@@ -165,6 +172,25 @@ def attn_push(out_ptrs, ctr_ptrs, col0, q, k, v, B, Tq, Tk, npad, H_local, ld_o,
     wp, wb = _ws(workspace)
     _check(lib().kb_attn_push(outs, ctrs, n, col0, _ptr(q), _ptr(k), _ptr(v), _ptr(qn_w), _ptr(kn_w), _ptr(rope_cos), _ptr(rope_sin),
                               B, Tq, Tk, npad, H_local, _ld(q), _ld(k), _ld(v), ld_o, _dt(q), out_dtype, eps, wp, wb, _stream()), "kb_attn_push")
+
+
+def attn_nag_push(out_ptrs, ctr_ptrs, part_ptrs, flag_ptrs, self_index, col0, h0, heads_total, epoch, q, k_pos, v_pos, Tk_pos, npad_pos,
+                  k_neg, v_neg, Tk_neg, npad_neg, scale, tau, alpha, Tq, H_local, ld_o, out_dtype, qn_w=None, eps=1e-6, workspace=None):
+    """NAG cross-attention over the local heads with the norm exchange and the output tiles going to every peer
+    (device addresses; this GPU's own at index self_index). See kb_attn_nag_push."""
+    n = len(out_ptrs)
+    arr = lambda ptrs: (ctypes.c_void_p * n)(*ptrs)
+    wp, wb = _ws(workspace)
+    _check(lib().kb_attn_nag_push(arr(out_ptrs), arr(ctr_ptrs), arr(part_ptrs), arr(flag_ptrs), n, self_index, col0, h0, heads_total, epoch,
+                                  _ptr(q), _ptr(qn_w), _ptr(k_pos), _ptr(v_pos), Tk_pos, npad_pos, _ptr(k_neg), _ptr(v_neg), Tk_neg, npad_neg,
+                                  scale, tau, alpha, Tq, H_local, _ld(q), _ld(k_pos), ld_o, _dt(q), out_dtype, eps, wp, wb, _stream()),
+           "kb_attn_nag_push")
+
+
+def bump_counters(ctr_ptrs):
+    """Enqueue one system-scope add on each listed counter (device addresses), ordered after earlier work on the stream."""
+    n = len(ctr_ptrs)
+    _check(lib().kb_bump_counters((ctypes.c_void_p * n)(*ctr_ptrs), n, _stream()), "kb_bump_counters")
 
 
 def wait_arrivals(ctr_ptr, target):

@@ -31,13 +31,16 @@ def test_error_strings_and_sizes(built_lib):
     for code in range(0, -9, -1):
         assert L.kb_error_string(code).decode() not in ("", "unknown error")
     assert L.kb_error_string(-99).decode() == "unknown error"
-    # scratch = fp16 staging copies, 256-byte aligned: only what needs norm/RoPE for fp16 inputs, everything otherwise
+    # scratch = fp16 staging copies, 256-byte aligned (only what needs norm/RoPE for fp16 inputs, everything otherwise), plus,
+    # for single-context calls, room for the balanced schedule's partial results: per SM two streams of (128 x 128 + 2 x 128)
+    # floats and two flags (148 SMs are assumed where no device can be asked)
     F16, BF16, F32 = kiln_b200.KB_F16, kiln_b200.KB_BF16, kiln_b200.KB_F32
-    assert kiln_b200.workspace_bytes(4096, 4096, 16, F16, True, True) == 2 * 4096 * 2048 * 2
-    assert kiln_b200.workspace_bytes(4096, 4096, 16, BF16, True, True) == 3 * 4096 * 2048 * 2
-    assert kiln_b200.workspace_bytes(100, 7, 2, F16, True, False) == 100 * 256 * 2
-    assert kiln_b200.workspace_bytes(100, 7, 2, F16) == 0
-    assert kiln_b200.workspace_bytes(1, 1, 1, F16, True, True) == 512
+    split = 148 * 2 * (128 * 128 + 256) * 4 + 1280
+    assert kiln_b200.workspace_bytes(4096, 4096, 16, F16, True, True) == 2 * 4096 * 2048 * 2 + split
+    assert kiln_b200.workspace_bytes(4096, 4096, 16, BF16, True, True) == 3 * 4096 * 2048 * 2 + split
+    assert kiln_b200.workspace_bytes(100, 7, 2, F16, True, False) == 100 * 256 * 2 + split
+    assert kiln_b200.workspace_bytes(100, 7, 2, F16) == split
+    assert kiln_b200.workspace_bytes(1, 1, 1, F16, True, True) == 512 + split
     # NAG adds the cross-head norm exchange: [12 query tiles][16 heads][2][128] floats + 12 counters (256-byte aligned)
     assert kiln_b200.workspace_bytes(1536, 512, 16, F32, n_ctx=2) == (1536 + 4 * 512) * 2048 * 2 + 12 * 16 * 1024 + 256
     assert kiln_b200.workspace_bytes(1536, 512, 16, F16, n_ctx=2) == 12 * 16 * 1024 + 256
