@@ -10,8 +10,12 @@ FLOPs are algorithmic: 4*Tq*Tk*128*H per attention, the count the reference's ow
 Every block has its own buffers (28 x 109 MB), so consecutive launches never find their inputs in L2.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --all-configs                     # one JSON line per benchmark configuration (1 GPU)
+    python bench.py --case self|cross|nag|prep|linear|block [--tokens T] [--batch B] [--ctx L] [--valid V] [--dtype f16|bf16]
+                    [--norm] [--reps R] [--warm W]    # one kernel family a few times: what the profiler captures run
 
-N > 1 (under torchrun): one image per GPU, no communication on the data path ("weak" scaling).
+N > 1 (under torchrun): one image per GPU, no communication on the data path ("weak" scaling); the line then also carries
+a `headsplit` object: batch 1 with the 16 heads split over the N GPUs (fused push / norm exchange against local + ncclAllGather).
 --impl reference: the reference has no CPU implementation of this path, so the arm times the CPU
 restatement of its arithmetic (oracle/, OpenMP over all host cores) on a bounded sample of the
 same workload. One JSON line goes to stdout.
@@ -33,6 +37,24 @@ FLOP_CROSS = 4.0 * T * L * 128 * H
 FLOP_STEP = BLOCKS * (FLOP_SELF + 2 * FLOP_CROSS)
 WORKLOAD = "anima-dit attention step: 1024x1024 -> 4096 tokens, 16x128 heads, 28 blocks x (self-attn + Q/K RMSNorm + 3D RoPE, NAG cross-attn to 2x512-token contexts), bf16"
 METRIC = "attention TFLOP/s per DiT step (4096 tokens)"
+
+
+def cosmos_rope_table(Hp, Wp):
+    """cos/sin tables [Hp*Wp, 64] of the DiT's 3D RoPE for one image (engine/src/dit.cu:196-215): of the 64 rotation pairs
+    the first 22 belong to the time axis (identity for an image), 21 to the row and 21 to the column of the patch, with
+    frequencies 1 / (10000 * 4^(42/40))^(2j/42) in single precision."""
+    import numpy as np
+    dim_h, dim_t = 42, 44
+    theta = np.float32(10000.0 * 4.0 ** (dim_h / (dim_h - 2)))
+    hf = (np.float32(1.0) / np.power(theta, (2 * np.arange(dim_h // 2, dtype=np.float32)) / np.float32(dim_h))).astype(np.float32)
+    t = np.arange(Hp * Wp)
+    ang_h = (t // Wp).astype(np.float32)[:, None] * hf[None, :]
+    ang_w = (t % Wp).astype(np.float32)[:, None] * hf[None, :]
+    c = np.ones((Hp * Wp, 64), np.float32)
+    s = np.zeros((Hp * Wp, 64), np.float32)
+    c[:, dim_t // 2:dim_t // 2 + 21], s[:, dim_t // 2:dim_t // 2 + 21] = np.cos(ang_h), np.sin(ang_h)
+    c[:, dim_t // 2 + 21:], s[:, dim_t // 2 + 21:] = np.cos(ang_w), np.sin(ang_w)
+    return c, s
 
 
 def read_peaks():
@@ -92,6 +114,7 @@ def cpu_sample(seconds_target=12.0):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import numpy as np
     import oracle
+    oracle.set_threads(os.cpu_count() or 1)
     k = oracle.round16(oracle.randn(2, T * D), 1).reshape(T, D)
     v = oracle.round16(oracle.randn(3, T * D), 1).reshape(T, D)
     q = oracle.round16(oracle.randn(1, T * D), 1).reshape(T, D)
@@ -115,6 +138,7 @@ def run_reference(args):
         return
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle
+    oracle.set_threads(os.cpu_count() or 1)       # a launcher may have exported OMP_NUM_THREADS=1: the arm uses every host core
     k = oracle.round16(oracle.randn(2, T * D), 1).reshape(T, D)
     v = oracle.round16(oracle.randn(3, T * D), 1).reshape(T, D)
     q = oracle.round16(oracle.randn(1, T * D), 1).reshape(T, D)
@@ -163,9 +187,7 @@ def run_ours(args):
     def randn(*shape):
         return torch.randn(*shape, device=dev, generator=g, dtype=torch.float32).to(bf)
 
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import oracle
-    cos, sin = (torch.from_numpy(a).to(dev) for a in oracle.cosmos_rope(64, 64))
+    cos, sin = (torch.from_numpy(a).to(dev) for a in cosmos_rope_table(64, 64))
     blocks = []
     for _ in range(BLOCKS):
         qkv = randn(T, 3 * D)                       # Q, K, V as thirds of one buffer, like the engine's [R, 4D] scratch
@@ -192,51 +214,106 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local) if rank == 0 else None   # samples from warm-up to the end of the per-kernel pass
     for _ in range(max(args.warmup, 3)):
         step()
     assert kb.check_status() == 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    # ---- the timed region: exactly K steps between barriers, device time by CUDA events, max over ranks; repeated
+    # REPEATS times so that the line carries a spread, `value` is the median region
+    REPEATS = 5
+    sampler = ClockSampler(local) if rank == 0 else None
+    regions = []
+    for _ in range(REPEATS):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        regions.append(ms / args.steps)
+    clocks = sampler.stop() if sampler else None
     assert kb.check_status() == 0
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+    ms_per_step = statistics.median(regions)
     value = world * FLOP_STEP / (ms_per_step * 1e-3) / 1e12
 
-    # ---- roofline of the dominant kernel: per-launch CUDA events on the launch stream (library's ProfScope hooks),
-    # taken over a second pass of the same K steps so the event records do not perturb `value`
-    kb.prof_enable(True)
-    for _ in range(min(args.steps, 8192 // LAUNCHES_PER_STEP)):
-        step()
-    attn_ms, attn_n = kb.prof_read(kb.PROF_ATTENTION)
-    nag_ms, nag_n = kb.prof_read(kb.PROF_NAG)
-    prep_ms, prep_n = kb.prof_read(kb.PROF_NORM_ROPE)
-    kb.prof_enable(False)
-    clocks = sampler.stop() if sampler else None
+    # ---- roofline of the dominant kernel: per-launch CUDA events on the launch stream (library's ProfScope hooks), taken
+    # over a separate pass of the same steps that lasts at least 2 s, with its own clock record. The event pairs add a
+    # little to every launch, so avg_launch_us is slightly pessimistic against the launches inside `value`.
+    prof_sampler = ClockSampler(local) if rank == 0 else None
+    tot = {"attn": [0.0, 0], "nag": [0.0, 0], "prep": [0.0, 0]}
+    t_start, prof_steps = time.perf_counter(), 0
+    chunk = max(1, min(8192 // LAUNCHES_PER_STEP, 32))
+    while time.perf_counter() - t_start < 2.0 or prof_steps < args.steps:
+        kb.prof_enable(True)
+        for _ in range(chunk):
+            step()
+        for key, cat in (("attn", kb.PROF_ATTENTION), ("nag", kb.PROF_NAG), ("prep", kb.PROF_NORM_ROPE)):
+            ms_c, n_c = kb.prof_read(cat)
+            tot[key][0] += ms_c
+            tot[key][1] += n_c
+        kb.prof_enable(False)
+        prof_steps += chunk
+    prof_clocks = prof_sampler.stop() if prof_sampler else None
+    attn_ms, attn_n = tot["attn"]
+    nag_ms, nag_n = tot["nag"]
+    prep_ms, prep_n = tot["prep"]
     sustained, burst, hbm, src = read_peaks()
     achieved = FLOP_SELF / (attn_ms / attn_n * 1e-3) / 1e12
+    # which peak the run justifies: the burst figure when the SM clock stayed near its maximum with no power cap active
+    # (a short kernel at full clock), the sustained figure when the pass ran clock-limited like the seconds-long GEMM loop
+    mhz = (prof_clocks or {}).get("sm_mhz")
+    mhz_max = (prof_clocks or {}).get("sm_max_mhz")
+    at_burst_clock = bool(mhz and mhz_max and mhz >= 0.9 * mhz_max and "sw_power_cap" not in (prof_clocks or {}).get("reasons", []))
+    peak = burst if at_burst_clock else sustained
     roofline = {"bound": "tensor", "kernel": "attn_fwd_kernel<MODE_PAIR> (self-attention, 4096x4096x16 heads)", "achieved": achieved,
-                "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained, "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside a long step)",
-                "traffic": None, "avg_launch_us": attn_ms / attn_n * 1e3,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{src} {'bf16_tflops (burst): the pass ran at ' + str(mhz) + ' MHz, no power cap' if at_burst_clock else 'bf16_tflops_sustained: the pass ran clock- or power-limited'}",
+                "frac_burst": achieved / burst, "frac_sustained": achieved / sustained,
+                "traffic": None, "avg_launch_us": attn_ms / attn_n * 1e3, "launches_timed": attn_n, "pass_seconds": time.perf_counter() - t_start,
+                "time_x_sm_mhz": (attn_ms / attn_n * 1e3) * mhz if mhz else None, "clocks": prof_clocks,
                 "other_kernels": {"nag_attn_us": nag_ms / nag_n * 1e3, "nag_tflops": 2 * FLOP_CROSS / (nag_ms / nag_n * 1e-3) / 1e12,
                                   "staging_prepass_us": prep_ms / prep_n * 1e3}}
     traffic_file = os.path.join(ROOT, "profiles", "attn_pair_traffic.json")
     if os.path.exists(traffic_file):
         roofline["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch_T4096")
 
+    # ---- the metric's other token counts (1536 = 32x48 and 3456 = 48x72 patches): the same self-attention call, kernel
+    # time per launch from the same hooks (rotating input sets larger than L2)
+    other_tokens = {}
+    if rank == 0:
+        for (hp, wp) in ((32, 48), (48, 72)):
+            tt = hp * wp
+            c_t, s_t = (torch.from_numpy(a).to(dev) for a in cosmos_rope_table(hp, wp))
+            nset = max(2, int(200e6 // (tt * 3 * D * 2)) + 1)
+            sets = [randn(tt, 3 * D) for _ in range(nset)]
+            o_t = torch.empty(tt, D, device=dev, dtype=bf)
+            call = lambda i: kb.attn_self(o_t, sets[i % nset][:, :D], sets[i % nset][:, D:2 * D], sets[i % nset][:, 2 * D:], 1, tt, H,
+                                          qn_w=blocks[0]["wq"], kn_w=blocks[0]["wk"], rope_cos=c_t, rope_sin=s_t, workspace=ws)
+            for i in range(3):
+                call(i)
+            kb.prof_enable(True)
+            for i in range(40):
+                call(i)
+            k_ms, k_n = kb.prof_read(kb.PROF_ATTENTION)
+            p_ms, p_n = kb.prof_read(kb.PROF_NORM_ROPE)
+            kb.prof_enable(False)
+            us = k_ms / k_n * 1e3
+            other_tokens[str(tt)] = {"self_attn_kernel_us": us, "tflops": 4.0 * tt * tt * 128 * H / us / 1e6, "frac_burst": 4.0 * tt * tt * 128 * H / us / 1e6 / burst,
+                                     "staging_prepass_us": p_ms / p_n * 1e3, "ms_per_28_blocks": 28 * (us + p_ms / p_n * 1e3) / 1e3}
+            del sets
+        assert kb.check_status() == 0
+
     # ---- end to end through the C ABI with HOST buffers: every block's inputs come from pinned host memory and
     # both attention outputs go back to the host, inside the timed region; copies overlap compute on side streams
     NSLOT = 2
-    pin_in = [{k2: torch.empty_like(blocks[i][k2], device="cpu").pin_memory() for k2 in ("q2", "kp", "vp", "kn", "vn")} for i in range(NSLOT)]
+    # per step the host sends what changes per step: every block's Q/K/V and cross Q. The cross-attention K/V of the two text
+    # contexts stay resident on the GPU, as the engine caches them per image (engine/src/dit.cu:217-234).
+    pin_in = [{k2: torch.empty_like(blocks[i][k2], device="cpu").pin_memory() for k2 in ("q2",)} for i in range(NSLOT)]
     pin_qkv = [torch.empty(T, 3 * D, dtype=bf).pin_memory() for _ in range(NSLOT)]
     pin_out = [(torch.empty(T, D, dtype=bf).pin_memory(), torch.empty(T, D, dtype=bf).pin_memory()) for _ in range(NSLOT)]
     for i in range(NSLOT):
@@ -249,8 +326,7 @@ def run_ours(args):
         s = dict(blocks[i])
         s.update({"qkv": qkv, "q": qkv[:, :D], "k": qkv[:, D:2 * D], "v": qkv[:, 2 * D:], "a": torch.empty(T, D, device=dev, dtype=bf),
                   "a2": torch.empty(T, D, device=dev, dtype=bf)})
-        for k2 in ("q2", "kp", "vp", "kn", "vn"):
-            s[k2] = torch.empty_like(blocks[i][k2])
+        s["q2"] = torch.empty_like(blocks[i]["q2"])
         slots.append(s)
     h2d_bytes = BLOCKS * (pin_qkv[0].numel() + sum(t_.numel() for t_ in pin_in[0].values())) * 2
     d2h_bytes = BLOCKS * 2 * T * D * 2
@@ -295,15 +371,26 @@ def run_ours(args):
     assert kb.check_status() == 0
     e2e = {"value": world * FLOP_STEP / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
            "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
-           "note": "all 28 blocks' Q/K/V, cross Q and contexts copied from pinned host memory and both outputs copied back every step; PCIe-bound"}
+           "note": "all 28 blocks' Q/K/V and cross Q copied from pinned host memory and both outputs copied back every step (text-context K/V "
+                   "resident, as the engine caches them per image); bound by the host-to-device copy path (PCIe / host memory, shared by "
+                   "all ranks of a node): %.1f GB/s per GPU here" % ((h2d_bytes + d2h_bytes) / e2e_s / 1e9)}
 
+    hs_result = None
+    if world > 1 and H % world == 0:
+        # configuration 5B: batch 1, the 16 heads split over the GPUs (peer stores only; no TMA multicast anywhere)
+        from kiln_b200 import headsplit_bench
+        hs_result = headsplit_bench.measure(T, H, L, reps=20, check=True)
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": ms_per_step, "regions": {"n": REPEATS, "ms_per_step": regions, "spread": (max(regions) - min(regions)) / ms_per_step},
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "f16 tensor-core operands, f32 accumulate (bf16 in HBM)", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "images_per_gpu": 1, "flop_per_step_per_gpu": FLOP_STEP,
                            "l2": "28 distinct per-block buffer sets (3 GB) cycle through: inputs larger than L2"},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * LAUNCHES_PER_STEP, "roofline": roofline}
+                "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * LAUNCHES_PER_STEP, "roofline": roofline,
+                "other_token_counts": other_tokens}
+        if hs_result is not None:
+            line["headsplit"] = hs_result
         if world == 1:
             tf, cores, rows, secs = cpu_sample()
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -515,6 +602,154 @@ def run_all_configs(args):
         attention_case(f"self {T_} tokens bf16 (metric token count)", 1, T_, T_, T_, 0, 4.0 * T_ * T_ * 128 * H)
 
 
+# ------------------------------------------------------------------------------------------------ single cases
+def run_case(a):
+    """One kernel family a few times on seeded inputs, for profilers and quick timing: prints the average CUDA-event time per
+    call and the algorithmic TFLOP/s (4*Tq*Tk*128*H per attention, 2*M*N*K per linear layer). `cross` takes --valid real keys of
+    a --ctx padded context (zero-key padding, the engine's semantics); `block` is the self-attention half of a DiT block
+    (engine/src/dit.cu:461-471): q, k, v projections, attention, output projection into the fp32 residual stream, once with
+    the fused head epilogue feeding attention directly and once the way the engine orders it. Under ncu, select the kernel
+    with -k regex:attn_fwd_kernel (qk_prep_kernel, gemm16_kernel) and skip the warm-up launches with -s."""
+    import torch
+    import kiln_b200 as kb
+    assert kb.lib().kb_init() == 0
+    if a.case in ("linear", "block"):
+        return linear_cases(a)
+    dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
+    T, B, H, L = a.tokens, a.batch, a.heads, a.ctx
+    D = H * 128
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g).to(dt)
+    q, k, v = rn(B * T, D), rn(B * T, D), rn(B * T, D)
+    out = torch.empty(B * T, D, device="cuda", dtype=dt)
+    w = torch.ones(128, device="cuda", dtype=torch.bfloat16) if a.norm else None
+    cos = sin = None
+    if a.norm and a.case in ("self", "prep"):
+        side = int(round(T ** 0.5))
+        assert side * side == T, "--norm with RoPE wants a square token grid"
+        cos = torch.zeros(T, 64, device="cuda").uniform_(-1, 1, generator=g)
+        sin = torch.zeros(T, 64, device="cuda").uniform_(-1, 1, generator=g)
+    ws = torch.empty(max(16, kb.workspace_bytes(B * T, B * max(T, L), H, dt, True, True, n_ctx=2)), dtype=torch.uint8, device="cuda")
+    kp, vp, kn, vn = rn(L, D), rn(L, D), rn(L, D), rn(L, D)
+    if a.case == "self":
+        fn = lambda: kb.attn_self(out, q, k, v, B, T, H, qn_w=w, kn_w=w, rope_cos=cos, rope_sin=sin, workspace=ws)
+        flop = 4.0 * T * T * 128 * H * B
+    elif a.case == "cross":
+        V = a.valid if a.valid > 0 else L
+        fn = lambda: kb.attn_cross(out[:T], q[:T], kp, vp, T, V, L - V, H, qn_w=w, workspace=ws)
+        flop = 4.0 * T * V * 128 * H
+    elif a.case == "nag":
+        fn = lambda: kb.attn_nag(out[:T], q[:T], kp, vp, L, 0, kn, vn, L, 0, 5.0, 2.5, 0.25, T, H, qn_w=w, workspace=ws)
+        flop = 8.0 * T * L * 128 * H
+    else:
+        st = torch.empty(B * T, D, device="cuda", dtype=torch.float16)
+        fn = lambda: kb.qk_prep(st, q, B * T, H, T, w=w, rope_cos=cos, rope_sin=sin)
+        flop = 0.0
+    for _ in range(a.warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / a.reps * 1e3
+    assert kb.check_status() == 0
+    extra = f", {flop / us / 1e6:.1f} TFLOP/s" if flop else f", {B * T * D * (q.element_size() + 2) / us / 1e3:.0f} GB/s"
+    if a.case == "cross":
+        extra += f" (valid={a.valid if a.valid > 0 else L}), Q+O+K+V bytes {(2 * T + 2 * (a.valid if a.valid > 0 else L)) * D * 2 / us / 1e3:.0f} GB/s"
+    print(f"case={a.case} tokens={T} batch={B} heads={H} ctx={L} dtype={a.dtype} norm={a.norm}: {us:.1f} us/call" + extra)
+
+
+
+
+def _timed_us(fn, warm, reps):
+    import torch
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def linear_cases(a):
+    import torch
+    import kiln_b200 as kb
+    from kiln_b200 import ops
+    T, H = a.tokens, a.heads
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2)
+    rn = lambda r, c, amp=1.0: (torch.randn(r, c, device="cuda", generator=g) * amp).half()
+    hw = torch.ones(128, device="cuda", dtype=torch.bfloat16)
+    cos = torch.zeros(T, 64, device="cuda").uniform_(-1, 1, generator=g)
+    sin = torch.zeros(T, 64, device="cuda").uniform_(-1, 1, generator=g)
+    if a.case == "linear":
+        M, N, K = T, a.n, a.k
+        epi = {"f32": ops.EPI_F32, "f16": ops.EPI_F16, "gelu16": ops.EPI_GELU16, "resid": ops.EPI_RESID, "heads16": ops.EPI_HEADS16}[a.epi]
+        nset = 4                                            # distinct operand sets so that weights do not stay in L2 between calls
+        xs, wts = [rn(M, K) for _ in range(nset)], [rn(N, K, 0.02) for _ in range(nset)]
+        c = torch.zeros(M, N, device="cuda", dtype=torch.float32 if epi in (ops.EPI_F32, ops.EPI_RESID) else torch.float16)
+        kw = dict(head_w=hw, rope_cos=cos, rope_sin=sin) if epi == ops.EPI_HEADS16 else {}
+        it = [0]
+
+        def fn():
+            it[0] = (it[0] + 1) % nset
+            ops.linear16(c, xs[it[0]], wts[it[0]], epi, **kw)
+        us = _timed_us(fn, a.warm, a.reps)
+        assert kb.check_status() == 0
+        print(f"case=linear M={M} N={N} K={K} epi={a.epi}: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
+        if a.cublas and epi == ops.EPI_F16:                 # the library GEMM on the same operands, for scale
+
+            def mm():
+                it[0] = (it[0] + 1) % nset
+                torch.matmul(xs[it[0]], wts[it[0]].T, out=c)
+            us = _timed_us(mm, a.warm, a.reps)
+            print(f"  cuBLAS (torch.matmul) fp16: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
+        return
+    D = H * 128
+    x = rn(T, D)
+    wq, wk, wv, wo = (rn(D, D, 0.02) for _ in range(4))
+    resid = torch.zeros(T, D, device="cuda", dtype=torch.float32)
+    gate = torch.ones(D, device="cuda")
+    q16, k16, v16, o16 = (torch.empty(T, D, device="cuda", dtype=torch.float16) for _ in range(4))
+    q32, k32, v32 = (torch.empty(T, D, device="cuda", dtype=torch.float32) for _ in range(3))
+    ws = torch.empty(max(16, kb.workspace_bytes(T, T, H, torch.float32, True, True)), dtype=torch.uint8, device="cuda")
+
+    def fused():
+        ops.linear16(q16, x, wq, ops.EPI_HEADS16, head_w=hw, rope_cos=cos, rope_sin=sin)
+        ops.linear16(k16, x, wk, ops.EPI_HEADS16, head_w=hw, rope_cos=cos, rope_sin=sin)
+        ops.linear16(v16, x, wv, ops.EPI_F16)
+        kb.attn_self(o16, q16, k16, v16, 1, T, H)
+        ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
+
+    def fused_one_launch():
+        ops.linear16_qkv([q16, k16, v16], x, [wq, wk, wv], head_ws=(hw, hw, None), rope_on=(True, True, False), rope_cos=cos, rope_sin=sin)
+        kb.attn_self(o16, q16, k16, v16, 1, T, H)
+        ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
+
+    def engine_order():
+        ops.linear16(q32, x, wq, ops.EPI_F32)
+        ops.linear16(k32, x, wk, ops.EPI_F32)
+        ops.linear16(v32, x, wv, ops.EPI_F32)
+        kb.attn_self(o16, q32, k32, v32, 1, T, H, qn_w=hw, kn_w=hw, rope_cos=cos, rope_sin=sin, workspace=ws)
+        ops.linear16(resid, o16, wo, ops.EPI_RESID, gate=gate)
+
+    flop = 4.0 * T * T * 128 * H + 4 * 2.0 * T * D * D
+    for name, fn in (("q, k, v in one launch", fused_one_launch), ("fused head epilogue", fused), ("engine order", engine_order)):
+        us = _timed_us(fn, a.warm, a.reps)
+        assert kb.check_status() == 0
+        print(f"case=block tokens={T} heads={H} [{name}]: {us:.1f} us/block-half, {flop / us / 1e6:.1f} TFLOP/s")
+
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -522,8 +757,24 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--all-configs", action="store_true", help="one JSON line per benchmark configuration (1 GPU) instead of the benchmark line")
+    ap.add_argument("--case", default=None, choices=["self", "cross", "nag", "prep", "linear", "block"], help="run one kernel family a few times (for profilers)")
+    ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--epi", default="f16", choices=["f32", "f16", "gelu16", "resid", "heads16"])
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--ctx", type=int, default=512)
+    ap.add_argument("--valid", type=int, default=0, help="cross: real keys of the padded context (0 = all)")
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
+    ap.add_argument("--norm", action="store_true", help="Q/K RMSNorm (+ RoPE for self) through the staging pre-pass")
+    ap.add_argument("--cublas", action="store_true", help="linear: also time torch.matmul on the same operands")
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--warm", type=int, default=2)
     args = ap.parse_args()
-    if args.all_configs:
+    if args.case:
+        run_case(args)
+    elif args.all_configs:
         run_all_configs(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -153,10 +153,10 @@ int kb_attn_push(void* const* out_peers, unsigned long long* const* ctr_peers, i
                  int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes, void* stream);
 /* Head-split NAG: kb_attn_nag over the local heads of one GPU. The per-token norms of the combine span all heads of the
  * model, so every thread block stores its head's two norms per row (2 floats per token and head, engine/src/dit.cu:295-324
- * computes them over the full row) into the exchange area of EVERY GPU (part_peers, plain peer stores) and bumps every
+ * computes them over the full row; here per half of the head's columns) into the exchange area of EVERY GPU (part_peers, plain peer stores) and bumps every
  * GPU's per-query-tile counter (flag_peers); it then waits, bounded, until its own GPU's counter shows all heads_total
  * heads of the tile, blends in fp32 exactly as the single-GPU kernel does, and stores the finished tile into every GPU's
- * output buffer at column col0 (then bumps ctr_peers as kb_attn_push does). Only final tiles and 8 bytes per token and
+ * output buffer at column col0 (then bumps ctr_peers as kb_attn_push does). Only final tiles and 16 bytes per token and
  * head cross NVLink. All GPUs must make the matching call (it is a collective). `self` = this GPU's index in the peer
  * arrays, h0 = its first head, epoch = 1, 2, 3 ... = how many times this exchange area has been used including this call
  * (its counters only grow and are never cleared, so a fast GPU's arrivals for the next call cannot be lost); an exchange
@@ -170,6 +170,7 @@ int kb_attn_nag_push(void* const* out_peers, unsigned long long* const* ctr_peer
                      int Tq, int H_local, int ld_q, int ld_kv, int ld_o, int dtype, int out_dtype, float eps,
                      void* workspace, size_t workspace_bytes, void* stream);
 size_t kb_nag_exchange_bytes(int Tq, int heads_total);
+size_t kb_nag_exchange_counter_offset(int Tq, int heads_total);   /* where the counters start inside an exchange area */
 /* Buffer reuse across GPUs. Nothing above stops a fast GPU from pushing call n+1 into a buffer that a slow GPU is still
  * reading for call n. The hand-shake: when a GPU is done with a buffer it enqueues kb_bump_counters on the "released"
  * counters of that buffer on every GPU (one system-scope add each, ordered after everything enqueued before it on the
@@ -187,6 +188,11 @@ int kb_wait_arrivals(const unsigned long long* ctr, unsigned long long target, v
 int kb_qk_prep(void* out, int ld_out, int out_dtype, const void* in, int ld_in, int in_dtype,
                int rows, int H, int T, const void* w_bf16, float eps,
                const float* rope_cos, const float* rope_sin, void* stream);
+
+/* Device address (on the current device) of 128 bf16 ones: the `w_bf16` of a norm without weight. The engine's rmsnorm
+ * normalises with weight 1 when it is given no weight (engine/src/kernels.cu:650-673); here a null weight means "no norm",
+ * so a caller that wants the engine's behaviour passes this. NULL on failure. */
+const void* kb_unit_norm_weight(void);
 
 /* The projections either side of attention: C = epilogue(A[M,K] * W[N,K]^T), A and W fp16 row-major
  * (row strides lda, ldw in elements), fp32 accumulation. Replaces the engine's fp16-activation GEMM

@@ -65,8 +65,8 @@ EncodeTiledFn g_encode = nullptr;
 std::mutex g_mu;
 
 template <typename K>
-int set_smem(K kernel) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) return KB_ERR_CUDA;
+int set_smem(K kernel, int bytes) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return KB_ERR_CUDA;
     return KB_OK;
 }
 
@@ -92,12 +92,12 @@ int init_device(DeviceState& st, int dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     int rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>))) return rc;
-    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>, ATTN_SMEM_PAIR))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>, ATTN_SMEM_PAIR))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>, ATTN_SMEM_PAIR))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __half>, ATTN_SMEM_NAG))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, __nv_bfloat16>, ATTN_SMEM_NAG))) return rc;
+    if ((rc = set_smem(attn_fwd_kernel<MODE_NAG, float>, ATTN_SMEM_NAG))) return rc;
     if ((rc = set_gemm_smem<EPI_F32>()) || (rc = set_gemm_smem<EPI_F16>()) || (rc = set_gemm_smem<EPI_GELU16>()) ||
         (rc = set_gemm_smem<EPI_RESID>()) || (rc = set_gemm_smem<EPI_HEADS16>()))
         return rc;
@@ -198,7 +198,7 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
     cfg.gridDim = dim3((unsigned)((p.split || p.n_items >= sm_count) ? sm_count : p.n_items), 1, 1);
-    cfg.dynamicSmemBytes = ATTN_SMEM;
+    cfg.dynamicSmemBytes = MODE == MODE_NAG ? ATTN_SMEM_NAG : ATTN_SMEM_PAIR;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = 0;
@@ -262,6 +262,7 @@ struct PeerSpec {
 };
 
 constexpr int MAX_HEADS = 4096;   // keeps every byte count below in range
+constexpr size_t NAG_NORM_FLOATS = 512;   // per (query tile, head): [2 column halves][|Z+|_1, |g|_1][128 rows]
 
 // fp16 staging bytes of one attention call (the part of the workspace the pre-pass writes)
 size_t staging_bytes(size_t rows_q, size_t rows_k, int n_ctx, int H, int dtype, bool norm_q, bool norm_k) {
@@ -373,7 +374,7 @@ const char* kb_error_string(int code) {
     }
 }
 
-int kb_version(void) { return 100; }
+int kb_version(void) { return 110; }
 
 
 
@@ -387,7 +388,7 @@ size_t kb_attn_workspace_bytes(int rows_q, int rows_k, int n_ctx, int H, int dty
     size_t n = staging_bytes((size_t)rows_q, (size_t)rows_k, n_ctx, H, dtype, norm_q != 0, norm_k != 0);
     if (n_ctx == 2) {                                                                  // NAG: per-head norm partials and arrival counters
         const size_t n_qt = ((size_t)rows_q + 127) / 128;
-        n += align256(n_qt * H * 256 * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+        n += align256(n_qt * H * NAG_NORM_FLOATS * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
     } else {
         // room for the balanced schedule's partial results (one slot and one flag per SM); a smaller workspace still works,
         // the call then runs whole items per SM
@@ -457,7 +458,7 @@ static int nag_impl(void* out, const void* q, const void* qn_w, const void* k_po
     unsigned int* nag_flag = nullptr;
     if (!peers) {
         if (!workspace || !aligned16(workspace)) return KB_ERR_WORKSPACE;   // always: the cross-head norm exchange lives there
-        nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * 256 * sizeof(float)));
+        nag_part = static_cast<float*>(sg.take_bytes((size_t)n_qt * H * NAG_NORM_FLOATS * sizeof(float)));
         nag_flag = static_cast<unsigned int*>(sg.take_bytes((size_t)n_qt * sizeof(unsigned int)));
         if (sg.overflow) return KB_ERR_WORKSPACE;
         pb.zero(nag_flag, n_qt);                       // cleared by the pre-pass, or by a memset when nothing is staged
@@ -789,7 +790,12 @@ int kb_attn_nag_push(void* const* out_peers, unsigned long long* const* ctr_peer
 size_t kb_nag_exchange_bytes(int Tq, int heads_total) {
     if (Tq <= 0 || heads_total <= 0) return 0;
     const size_t n_qt = ((size_t)Tq + 127) / 128;
-    return align256(n_qt * heads_total * 256 * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+    return align256(n_qt * heads_total * NAG_NORM_FLOATS * sizeof(float)) + align256(n_qt * sizeof(unsigned int));
+}
+
+size_t kb_nag_exchange_counter_offset(int Tq, int heads_total) {
+    if (Tq <= 0 || heads_total <= 0) return 0;
+    return align256((((size_t)Tq + 127) / 128) * heads_total * NAG_NORM_FLOATS * sizeof(float));
 }
 
 int kb_bump_counters(unsigned long long* const* ctr_peers, int n_peers, void* stream) {
@@ -861,6 +867,20 @@ int kb_attn_self_static(void* out, const void* q, const void* k, const void* v, 
     // attention kernel's TMA loads read it, and rows past the end are never read (the tensor maps bound them).
     return attn_pair(out, q, k, v, qn_w, kn_w, rope_cos, rope_sin, B, T, T, 0, H, ld_q, ld_k, ld_v, ld_o, dtype, out_dtype, eps, scratch,
                      (size_t)KB_STATIC_SCRATCH_BYTES, static_cast<cudaStream_t>(stream));
+}
+
+// 128 bf16 ones in the library's device image: the weight of an RMSNorm "without weight" (the engine's rmsnorm takes a null
+// weight and still normalises: w ? bf(w[i]) : 1, engine/src/kernels.cu:650-673)
+#define KB_R8(x) x, x, x, x, x, x, x, x
+static __device__ __align__(16) unsigned short g_unit_weight[128] = {KB_R8(KB_R8(0x3f80)), KB_R8(KB_R8(0x3f80))};
+#undef KB_R8
+
+const void* kb_unit_norm_weight(void) {
+    DeviceState* st;
+    if (get_state(&st) != KB_OK) return nullptr;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_unit_weight) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
 }
 
 size_t kb_selfcheck_workspace_bytes(void) { return (size_t)4 << 20; }

@@ -76,8 +76,24 @@ constexpr int NSTAGE = 4;               // K/V ring depth
 #endif
 constexpr int POLY_PAIRS = KB_POLY_PAIRS; // of every 8 score pairs, this many take 2^x on the FMA pipe instead of MUFU
 constexpr int ATTN_THREADS = 384;
-constexpr int CTRL_BYTES = 8192;
-constexpr int ATTN_SMEM = 2 * TILE_BYTES + NSTAGE * TILE_BYTES + CTRL_BYTES + 1024;  // + alignment slack
+// Registers per thread after the warpgroups re-divide the 384 x 168 the block starts with: 256 softmax threads x 224 + 128
+// threads of the MMA / TMA / helper warps x 56 = 64512 exactly (a larger second number would leave the softmax warps'
+// increase waiting forever). At 224 the softmax code compiles without a spill, which matters more than usual here: with
+// 227 KB of the SM's 256 KB configured as shared memory there is almost no L1 left, so every spill access is an L2 round trip.
+#ifndef KB_SOFTMAX_REGS
+#define KB_SOFTMAX_REGS 224
+#endif
+constexpr int SOFTMAX_REGS = KB_SOFTMAX_REGS, OTHER_REGS = (ATTN_THREADS * 168 - 256 * SOFTMAX_REGS) / 128;
+static_assert(256 * SOFTMAX_REGS + 128 * OTHER_REGS == ATTN_THREADS * 168 && OTHER_REGS % 8 == 0 && OTHER_REGS >= 24, "register split");
+// Shared memory (dynamic, 1024-byte aligned): MODE_PAIR: Q0, Q1 (each doubles as the output staging of its stream), K/V ring,
+// 1 KB of barriers and shared words. MODE_NAG: Q, two tiles holding the previous item's unblended g and Z+ as fp16 (see the
+// NAG epilogue), K/V ring, 3 KB control block (barriers, words, 2.5 KB of epilogue scratch): exactly the 227 KB a thread
+// block may have.
+constexpr int CTRL_BYTES_PAIR = 1024, CTRL_BYTES_NAG = 3072;
+constexpr int ATTN_TILES_PAIR = 2 + NSTAGE, ATTN_TILES_NAG = 3 + NSTAGE;
+constexpr int ATTN_SMEM_PAIR = ATTN_TILES_PAIR * TILE_BYTES + CTRL_BYTES_PAIR;
+constexpr int ATTN_SMEM_NAG = ATTN_TILES_NAG * TILE_BYTES + CTRL_BYTES_NAG;
+static_assert(ATTN_SMEM_NAG <= 232448, "shared memory per thread block on sm_100");
 
 // error bits written to the status word
 constexpr uint32_t ST_TIMEOUT = 1u;
@@ -103,7 +119,7 @@ struct AttnParams {
     int npad[2];
     float scale_log2;   // log2(e) / sqrt(128)
     float nag_s, nag_tau, nag_alpha;
-    float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][nag_heads][2][128]: per head |Z+|_1 and |g|_1 of each row
+    float* nag_part;    // MODE_NAG scratch [ceil(Tq/128)][nag_heads][2 column halves][2][128]: per head and half of its columns |Z+|_1 and |g|_1 of each row
     unsigned int* nag_flag;  // MODE_NAG [ceil(Tq/128)] arrival counters: a tile is complete at nag_epoch * nag_heads
     // The per-token norms span ALL heads of the model. Single GPU: nag_heads = H, nag_h0 = 0, nag_epoch = 1 and the counters
     // are zeroed before the launch. Head split: this GPU holds heads [nag_h0, nag_h0 + H) of nag_heads; every CTA stores its
@@ -121,7 +137,7 @@ struct AttnParams {
 
 // barrier slots inside the control block
 enum { BAR_QFULL = 0, BAR_QEMPTY = 2, BAR_SFULL = 4, BAR_SREQ = 6, BAR_PFULL = 8, BAR_PEMPTY = 10, BAR_ODONE = 12, BAR_OFREE = 14,
-       BAR_SFREE = 16, BAR_KVFULL = 20, BAR_KVEMPTY = 20 + NSTAGE, BAR_COUNT = 20 + 2 * NSTAGE };
+       BAR_SFREE = 16, BAR_PARKED = 17, BAR_NORMS = 18, BAR_KVFULL = 20, BAR_KVEMPTY = 20 + NSTAGE, BAR_COUNT = 20 + 2 * NSTAGE };
 // when a stream asks for its next S: 0 = before its exponentials, 1 = after the first half of them, 2 = with P (no overlap)
 #ifndef KB_SREQ_AT
 #define KB_SREQ_AT 1
@@ -244,20 +260,26 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
                 const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const __grid_constant__ AttnParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
-    uint8_t* const smem = smem_raw + (base - raw);
-    const uint32_t sQ = base;                                     // 2 tiles
-    const uint32_t sKV = base + 2 * TILE_BYTES;                   // NSTAGE tiles
-    uint8_t* const ctrl = smem + 2 * TILE_BYTES + NSTAGE * TILE_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];         // 128-byte swizzle wants 1024-byte aligned tiles
+    const uint32_t base = smem_u32(smem_raw);
+    uint8_t* const smem = smem_raw;
+    if (base & 1023u) {                                           // never seen; without it every tile would be garbage
+        if (threadIdx.x == 0) atomicOr(p.status, ST_TIMEOUT);
+        return;
+    }
+    constexpr int N_FRONT = MODE == MODE_NAG ? 3 : 2;             // tiles in front of the K/V ring
+    const uint32_t sQ = base;
+    const uint32_t sKV = base + N_FRONT * TILE_BYTES;             // NSTAGE tiles
+    uint8_t* const ctrl = smem + (N_FRONT + NSTAGE) * TILE_BYTES;
     const uint32_t bars = sKV + NSTAGE * TILE_BYTES;              // BAR_COUNT x 8 bytes
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
     volatile uint32_t* const warp_ok = reinterpret_cast<volatile uint32_t*>(ctrl + 264);   // [8] per softmax warp
     volatile uint32_t* const wg_stop = reinterpret_cast<volatile uint32_t*>(ctrl + 296);   // [2] per softmax warpgroup
-    volatile uint32_t* const wg_here = reinterpret_cast<volatile uint32_t*>(ctrl + 304);   // [2] per softmax warpgroup
-    float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // NAG scratch: 5 x 128 floats x 2
+    volatile uint32_t* const wg_here = reinterpret_cast<volatile uint32_t*>(ctrl + 304);   // [2] per softmax warpgroup; NAG: [1] = warp 11's norm totals are good
+    volatile uint32_t* const sm_item = reinterpret_cast<volatile uint32_t*>(ctrl + 312);   // [1] NAG: query tile of the item just parked
+    volatile uint32_t* const sm_store = reinterpret_cast<volatile uint32_t*>(ctrl + 316);  // [3] NAG: {a blended tile waits in the Q tile, its head, its first row}
+    float* const fbuf = reinterpret_cast<float*>(ctrl + 512);     // MODE_NAG epilogue scratch: 1/l of both streams [2][128], norm totals [2][128]
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -273,6 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_init(bar(i), count);
         }
         *abort_flag = 0u;
+        sm_store[0] = 0u;
         mbar_fence_init();
         fence_proxy_async_smem();
     }
@@ -294,7 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // register budget of the branch is known at compile time; the final full-CTA barrier is therefore
     // written as the same bar.sync id from both branches.
     if (warp < 8) {
-        setmaxnreg_inc<208>();
+        setmaxnreg_inc<SOFTMAX_REGS>();
         // ------------------------------------------------------------------ softmax, one row per thread
         const int i = warp >> 2;                                   // stream = warpgroup
         const int t = tid & 127;
@@ -305,6 +328,106 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float c = p.scale_log2;
         uint32_t sf_cnt = 0, od_cnt = 0, pe_cnt = 0;               // uses of s_full[i] / o_done[i] / p_empty[i] so far (phase parity)
         uint32_t ring0 = 0;                                        // K/V ring entries of all earlier segments
+
+        // MODE_NAG, 16-bit output: the item parked in shared memory, waiting for its blend
+        bool pend_valid = false, pend_go = false;
+        int pend_h = 0, pend_q0 = 0;
+        float pend_tp = 0.f, pend_tg = 0.f;                        // its |Z+|_1 and |g|_1 over all heads, this thread's row
+        uint32_t norms_cnt = 0;                                    // parked items whose norms have been taken over so far
+        float* const f_tot = fbuf + 256;                           // [2][128] norm totals of the parked item, written by warp 11
+        constexpr int NORM_STRIDE = 512;                           // floats per (query tile, head) in the norm scratch
+        // one thread waits (bounded) until all heads of query tile qt have published their norms; result in wg_here[0]
+        auto nag_wait_norms = [&](int qt) {
+            if (tid == 0) {
+                const uint32_t target = p.nag_epoch * (uint32_t)p.nag_heads;
+                const uint64_t t0 = globaltimer_ns();
+                uint32_t seen = 0;
+                for (;;) {
+                    if (p.n_peers == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + qt) : "memory");
+                    else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + qt) : "memory");
+                    if (seen >= target || *abort_flag) break;
+                    if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
+                    __nanosleep(32);
+                }
+                wg_here[0] = (seen >= target) ? 1u : 0u;
+            }
+            named_bar_sync(1, 256);
+        };
+        // The parked item, in two steps. Step one (blend = false): take over the norms of all heads that warp 11 has summed
+        // into shared memory during the main loop. Step two (blend = true): blend the parked tiles in place and start the
+        // store. Every barrier inside depends only on pend_valid and n_peers, which all 256 threads agree on.
+        auto nag_finish = [&](bool blend) {
+            if (MODE != MODE_NAG || sizeof(OutT) != 2 || !pend_valid) return;
+            if (!blend) {
+                const bool got = __all_sync(0xffffffffu, mbar_wait(bar(BAR_NORMS), norms_cnt & 1u, abort_flag));
+                ++norms_cnt;
+                pend_go = got && wg_here[1] != 0u;
+                pend_tp = f_tot[t];
+                pend_tg = f_tot[128 + t];
+                return;
+            }
+            constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
+            const int wg = warp >> 2;
+            // The blend below writes into the Q tile: both streams' MMAs of the current item must be complete first (each
+            // warpgroup has waited for its own stream's last P*V only, and the streams may differ in length).
+            named_bar_sync(1, 256);
+            const float ratio = pend_tg / fmaxf(pend_tp, 1e-12f);
+            const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
+            const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
+            // The blended tile goes into the Q tile, which is dead here (every S MMA of the current item has completed and the
+            // loader is only told so once the store below has read it): the parking tiles are free for the current item at once.
+            uint8_t* const stage = smem;
+            if (pend_go) {
+                uint8_t* const to = stage + wg * HALF_BYTES + t * 128;
+                const uint8_t* const tg = smem + TILE_BYTES + wg * HALF_BYTES + t * 128;
+                const uint8_t* const tz = smem + 2 * TILE_BYTES + wg * HALF_BYTES + t * 128;
+#pragma unroll
+                for (int cc = 0; cc < 8; cc++) {
+                    const uint4 g4 = *reinterpret_cast<const uint4*>(tg + ((cc ^ (t & 7)) << 4));
+                    const uint4 z4 = *reinterpret_cast<const uint4*>(tz + ((cc ^ (t & 7)) << 4));
+                    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, zw[4] = {z4.x, z4.y, z4.z, z4.w};
+                    uint32_t ow[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&gw[e]));
+                        const float2 zf = __half22float2(*reinterpret_cast<const __half2*>(&zw[e]));
+                        ow[e] = pack16<ODT>(ag * gf.x + ap * zf.x, ag * gf.y + ap * zf.y);
+                    }
+                    *reinterpret_cast<uint4*>(to + ((cc ^ (t & 7)) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                }
+                if (p.n_peers == 0) fence_proxy_async_smem();
+            }
+            named_bar_sync(1, 256);                                           // the blended tile is complete, the parking tiles are read out
+            if (p.n_peers == 0) {
+                // the loader warp stores the tile (bulk tensor store, rows past Tq clipped by the tensor map) before it loads the
+                // next Q into the same space: nobody here waits for the store to read the tile
+                if (tid == 0) { sm_store[1] = (uint32_t)pend_h; sm_store[2] = (uint32_t)pend_q0; sm_store[0] = pend_go ? 1u : 0u; }
+            } else {
+                // head split: each of the eight warps copies 16 rows out as whole 256-byte rows to every GPU's buffer
+                if (pend_go) {
+                    const int lr0 = 16 * warp;
+                    const int row0 = pend_q0 + lr0;
+                    const int nrow = p.Tq - row0;                             // rows of this warp that exist (warp-uniform)
+                    uint2 vals[16];
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++)
+                        vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                   ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                    const size_t off = (size_t)row0 * (size_t)p.ldo + (size_t)(p.col0 + pend_h * HD) + (size_t)lane * 4;
+                    for (int pe = 0; pe < p.n_peers; pe++) {
+                        OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                        for (int rr = 0; rr < 16; rr++)
+                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                    }
+                    __threadfence_system();                                   // the tile is visible to every GPU before the arrival
+                }
+                named_bar_sync(1, 256);                                       // every warp is done with the parked tile
+                if (pend_go && tid < p.n_peers) atomicAdd_system(p.ctr_peers[tid], 1ull);
+                if (tid == 0) sm_store[0] = 0u;
+            }
+            pend_valid = false;
+        };
 
         SegIter<MODE> iter(p);
         Seg it;
@@ -447,6 +570,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             }
             const bool mine = je > jb;                                         // this stream exists in the segment
+            nag_finish(false);                                                 // the parked item's norms, fetched under the wait below
             if (ok && mine) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), od_cnt & 1u, abort_flag));
                 tc_fence_after();
@@ -625,12 +749,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             } else {
                 // NAG combine (engine/src/dit.cu:295-324) on Z+ = O0/l0 and Z- = O1/l1 straight from TMEM.
+                // The clamp factor of a token needs |Z+|_1 and |g|_1 over ALL heads, i.e. from up to nag_heads other thread
+                // blocks: publish this head's norms, get the others'. 16-bit outputs do not wait for that exchange: the item's
+                // unblended g and Z+ are parked as fp16 tiles in shared memory, TMEM is handed back, the next item runs, and
+                // the parked item is blended and stored one item later, when the other heads' norms have long arrived.
                 float* const f_inv = fbuf;             // [2][128]  1/l per stream
-                float* const f_part = fbuf + 256;      // [2 column halves][2 norms][128]; later [2 norms][128] totals
-                const int wg = i;                      // warpgroup 0 also finishes |Z+|_1, warpgroup 1 |g|_1
+                const int wg = i;                      // warpgroup wg takes head columns [64 wg, 64 wg + 64) of both outputs
                 const uint32_t tOp = tmem_base + lane_base + 256u + (uint32_t)(wg * 64);
                 const uint32_t tOn = tmem_base + lane_base + 384u + (uint32_t)(wg * 64);
                 const float s = p.nag_s, sm1 = p.nag_s - 1.f;
+                constexpr bool DEFER = sizeof(OutT) == 2;
+                if constexpr (DEFER) {
+                    if (tid == 0 && !pend_valid) sm_store[0] = 0u;        // nothing parked (first item): the Q tile is simply free
+                    nag_finish(true);                                     // the parked item: blend into the Q tile
+                    // every S MMA of the current item has completed and the blended tile (if any) is staged: the loader may
+                    // store it and load the next Q
+                    if (tid == 0 && ok) mbar_arrive(bar(BAR_QEMPTY + 0));
+                }
                 {
                     const float mc = row_m * p.scale_log2;
                     float scale = 1.f, l = row_l;
@@ -645,12 +780,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tc_fence_before();
                 named_bar_sync(1, 256);                                   // both streams' O and 1/l are final
                 ok = (warp_ok[0] & warp_ok[1] & warp_ok[2] & warp_ok[3] & warp_ok[4] & warp_ok[5] & warp_ok[6] & warp_ok[7]) != 0u;
-                if (t == 0 && wg == 0 && ok) mbar_arrive(bar(BAR_QEMPTY + 0));   // every S MMA of the item has completed
+                if (!DEFER && tid == 0 && ok) mbar_arrive(bar(BAR_QEMPTY + 0));   // every S MMA of the item has completed: the next Q may load
                 const float ip = f_inv[t], in = f_inv[128 + t];
                 float lp = 0.f, lg = 0.f;
-                // warpgroup wg takes head columns [64 wg, 64 wg + 64) of both outputs
                 if (ok) {
                     tc_fence_after();
+                    // DEFER: g and Z+ of this item are parked as two [128][128] fp16 tiles in the layout TMA stores (two
+                    // 128-byte-swizzled halves), straight from the registers of this pass
+                    uint8_t* const tg = smem + TILE_BYTES + wg * HALF_BYTES + t * 128;
+                    uint8_t* const tz = smem + 2 * TILE_BYTES + wg * HALF_BYTES + t * 128;
 #pragma unroll
                     for (int q = 0; q < 2; q++) {
                         uint32_t a[32], n[32];
@@ -660,133 +798,77 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         reg_fence32(a);
                         reg_fence32(n);
 #pragma unroll
-                        for (int e = 0; e < 32; e++) {
-                            const float pv = __uint_as_float(a[e]) * ip;
-                            const float nv = __uint_as_float(n[e]) * in;
-                            lp += fabsf(pv);
-                            lg += fabsf(pv * s - nv * sm1);
-                        }
-                    }
-                }
-                f_part[(wg * 2 + 0) * 128 + t] = lp;
-                f_part[(wg * 2 + 1) * 128 + t] = lg;
-                named_bar_sync(1, 256);
-                // publish this head's norms: warpgroup 0 writes |Z+|_1, warpgroup 1 writes |g|_1 (fixed order: deterministic)
-                const size_t tile_off = ((size_t)it.qt * p.nag_heads) * 256;        // [nag_heads][2][128] of this query tile
-                const size_t mine_off = tile_off + (size_t)(p.nag_h0 + it.h) * 256 + wg * 128 + t;
-                const float my_norm = f_part[(0 * 2 + wg) * 128 + t] + f_part[(1 * 2 + wg) * 128 + t];
-                const uint32_t target = p.nag_epoch * (uint32_t)p.nag_heads;
-                if (p.n_peers == 0) {
-                    p.nag_part[mine_off] = my_norm;
-                    __threadfence();
-                } else {
-                    for (int pe = 0; pe < p.n_peers; pe++) p.nag_part_peers[pe][mine_off] = my_norm;   // plain stores over NVLink
-                    __threadfence_system();
-                }
-                named_bar_sync(1, 256);
-                if (tid == 0) {
-                    // arrive, then wait (bounded) for the other heads of this query tile. On one GPU they are adjacent work
-                    // items and therefore in flight on other SMs now (the launch is cooperative: all CTAs are resident); under
-                    // head split the other GPUs run the same launch and walk the query tiles in the same order.
-                    uint32_t seen = 0;
-                    if (p.n_peers == 0) {
-                        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + it.qt), "r"(1u) : "memory");
-                    } else {
-                        for (int pe = 0; pe < p.n_peers; pe++)
-                            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.nag_flag_peers[pe] + it.qt), "r"(1u) : "memory");
-                    }
-                    const uint64_t t0 = globaltimer_ns();
-                    for (;;) {
-                        if (p.n_peers == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
-                        else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + it.qt) : "memory");
-                        if (seen >= target || *abort_flag) break;
-                        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
-                        __nanosleep(32);
-                    }
-                    wg_here[0] = (seen >= target) ? 1u : 0u;
-                }
-                named_bar_sync(1, 256);
-                const bool all_here = wg_here[0] != 0u;
-                float tot = 0.f;
-                if (all_here)
-                    for (int hh = 0; hh < p.nag_heads; hh++) tot += __ldcg(p.nag_part + tile_off + (size_t)hh * 256 + wg * 128 + t);   // head order: same sum everywhere
-                f_part[wg * 128 + t] = tot;                                 // [2 norms][128] (the column-half partials were consumed above)
-                named_bar_sync(1, 256);
-                const float ratio = f_part[128 + t] / fmaxf(f_part[t], 1e-12f);
-                const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
-                const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
-                const bool go = ok && all_here;                               // uniform over the 256 softmax threads
-                if constexpr (sizeof(OutT) == 2) {
-                    // blend into the (never loaded in this mode) second Q tile, then one bulk tensor store per half
-                    constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
-                    uint8_t* const stage = smem + TILE_BYTES;
-                    if (go) {
+                        for (int cc = 0; cc < 4; cc++) {                      // 16-byte chunk 4q + cc of this thread's 128-byte half row
+                            uint32_t gw[4], zw[4];
 #pragma unroll
-                        for (int q = 0; q < 2; q++) {
-                            uint32_t a[32], n[32];
-                            tmem_ld32(tOp + 32u * q, a);
-                            tmem_ld32(tOn + 32u * q, n);
-                            tmem_wait_ld();
-                            reg_fence32(a);
-                            reg_fence32(n);
-                            float v[32];
-#pragma unroll
-                            for (int e = 0; e < 32; e++) {
-                                const float pv = __uint_as_float(a[e]) * ip;
-                                const float nv = __uint_as_float(n[e]) * in;
-                                v[e] = ag * (pv * s - nv * sm1) + ap * pv;
+                            for (int e = 0; e < 4; e++) {
+                                const int k = 8 * cc + 2 * e;
+                                const float pv0 = __uint_as_float(a[k]) * ip, pv1 = __uint_as_float(a[k + 1]) * ip;
+                                const float g0 = pv0 * s - __uint_as_float(n[k]) * in * sm1, g1 = pv1 * s - __uint_as_float(n[k + 1]) * in * sm1;
+                                lp += fabsf(pv0) + fabsf(pv1);
+                                lg += fabsf(g0) + fabsf(g1);
+                                gw[e] = pack16<DT_F16>(g0, g1);
+                                zw[e] = pack16<DT_F16>(pv0, pv1);
                             }
-#pragma unroll
-                            for (int cc = 0; cc < 4; cc++) {                   // 16-byte chunk 8 wg + 4 q + cc of the row
-                                uint4 pk;
-                                pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
-                                pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
-                                pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
-                                pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
-                                // warpgroup wg fills the 128-byte-swizzled [128][64] half wg of the tile (what TMA stores)
-                                *reinterpret_cast<uint4*>(stage + wg * HALF_BYTES + t * 128 + (((4 * q + cc) ^ (t & 7)) << 4)) = pk;
+                            if constexpr (DEFER) {
+                                *reinterpret_cast<uint4*>(tg + (((4 * q + cc) ^ (t & 7)) << 4)) = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                                *reinterpret_cast<uint4*>(tz + (((4 * q + cc) ^ (t & 7)) << 4)) = make_uint4(zw[0], zw[1], zw[2], zw[3]);
                             }
                         }
+                    }
+                    if constexpr (DEFER) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) { mbar_arrive(bar(BAR_OFREE + 0)); mbar_arrive(bar(BAR_OFREE + 1)); }   // both O read out
-                        fence_proxy_async_smem();
                     }
-                    named_bar_sync(1, 256);
-                    if (p.n_peers == 0) {
-                        if (go && tid == 0) {                                 // rows past Tq are clipped by the tensor map
-                            tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0, 0);
-                            tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0, 0);
-                            tma_store_commit();
-                            tma_store_wait_read();                            // before the next item blends into this space
-                        }
-                    } else {
-                        // head split: each of the eight warps copies 16 rows out as whole 256-byte rows to every GPU's buffer
-                        if (go) {
-                            const int lr0 = 16 * warp;
-                            const int row0 = it.q0 + lr0;
-                            const int nrow = p.Tq - row0;                     // rows of this warp that exist (warp-uniform)
-                            uint2 vals[16];
-#pragma unroll
-                            for (int rr = 0; rr < 16; rr++)
-                                vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
-                                                                           ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
-                            const size_t off = (size_t)row0 * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
-                            for (int pe = 0; pe < p.n_peers; pe++) {
-                                OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
-#pragma unroll
-                                for (int rr = 0; rr < 16; rr++)
-                                    if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
-                            }
-                            __threadfence_system();                           // the tile is visible to every GPU before the arrival
-                        }
-                        named_bar_sync(1, 256);                               // every warp is done with the staging tile
-                        if (go && tid < p.n_peers) atomicAdd_system(p.ctr_peers[tid], 1ull);
-                    }
+                }
+                // publish this head's norms, per half of its columns: plain stores now, one fence and the arrival by one thread
+                // after the barrier below (the barrier orders every thread's stores before that thread's release)
+                const size_t tile_off = ((size_t)it.qt * p.nag_heads) * NORM_STRIDE;   // [nag_heads][2 halves][2 norms][128] of this query tile
+                const size_t mine_off = tile_off + (size_t)(p.nag_h0 + it.h) * NORM_STRIDE + wg * 256 + t;
+                if (p.n_peers == 0) {
+                    p.nag_part[mine_off] = lp;
+                    p.nag_part[mine_off + 128] = lg;
                 } else {
+                    for (int pe = 0; pe < p.n_peers; pe++) { p.nag_part_peers[pe][mine_off] = lp; p.nag_part_peers[pe][mine_off + 128] = lg; }   // plain stores over NVLink
+                }
+                named_bar_sync(1, 256);                                   // norms stored by everyone
+                // The arrival on the tile's counter needs a fence that waits for those stores (a few thousand cycles): in the
+                // deferred form warp 11 does both, so that nobody here waits for it. (The barrier above orders every thread's
+                // stores before thread 0's mbarrier arrive, which warp 11 acquires before its own fence and release.)
+                auto publish = [&](int qt) {
+                    if (p.n_peers == 0) {
+                        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + qt), "r"(1u) : "memory");
+                    } else {
+                        asm volatile("fence.acq_rel.sys;" ::: "memory");
+                        for (int pe = 0; pe < p.n_peers; pe++)
+                            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.nag_flag_peers[pe] + qt), "r"(1u) : "memory");
+                    }
+                };
+                if constexpr (DEFER) {
+                    // warp 11 publishes, then fetches this item's norms over all heads (it waits for the other heads itself); the
+                    // totals of the item before were taken over by every thread before the barrier above
+                    if (tid == 0) { sm_item[0] = (uint32_t)it.qt; mbar_arrive(bar(BAR_PARKED)); }
+                    pend_valid = ok;
+                    pend_h = it.h; pend_q0 = it.q0;
+                } else {
+                    // fp32 output: wait here for the other heads, blend from TMEM, store rows
+                    if (tid == 0) publish(it.qt);
+                    nag_wait_norms(it.qt);
+                    const bool all_here = wg_here[0] != 0u;
+                    float tp = 0.f, tg = 0.f;
+                    if (all_here)
+                        for (int hh = 0; hh < 2 * p.nag_heads; hh++) {        // head and half order: same sum everywhere
+                            tp += __ldcg(p.nag_part + tile_off + (size_t)hh * 256 + t);
+                            tg += __ldcg(p.nag_part + tile_off + (size_t)hh * 256 + 128 + t);
+                        }
+                    const float ratio = tg / fmaxf(tp, 1e-12f);
+                    const float kclamp = ratio > p.nag_tau ? p.nag_tau / ratio : 1.f;
+                    const float ag = p.nag_alpha * kclamp, ap = 1.f - p.nag_alpha;
                     const int row = it.q0 + t;
                     OutT* dst = reinterpret_cast<OutT*>(p.out) + (size_t)row * (size_t)p.ldo + (size_t)it.h * HD + wg * 64;
-                    if (go) {
+                    if (ok && all_here) {
 #pragma unroll
                         for (int q = 0; q < 2; q++) {
                             uint32_t a[32], n[32];
@@ -824,11 +906,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (wg_stop[1] != 0u) break;
             }
         }
+        if (MODE == MODE_NAG && sizeof(OutT) == 2) {                      // the last parked item; the loader stores it
+            const bool last = pend_valid;
+            nag_finish(false);
+            nag_finish(true);
+            if (tid == 0 && last) mbar_arrive(bar(BAR_QEMPTY + 0));
+        }
         if (lane == 0) tma_store_wait_all();                              // bulk stores issued by this thread have landed
         tc_fence_before();
         cta_sync();
     } else {
-        setmaxnreg_dec<88>();   // 384 x 168 registers at launch = 256 x 208 + 128 x 88: a larger value here would leave the increase above waiting forever
+        setmaxnreg_dec<OTHER_REGS>();
         if (warp == 8 || warp == 10) {
             // ------------------------------------------------------------------ MMA issue: one warp (one lane) per stream
             // Two issuing threads, because one thread's waits, fences and commits between two batches of eight MMAs take
@@ -964,11 +1052,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tma_load_3d(dst, tm, mbar, it.h * HD, row0, bb);
                     tma_load_3d(dst + HALF_BYTES, tm, mbar, it.h * HD + 64, row0, bb);
                 };
+                // MODE_NAG, 16-bit output: the softmax threads leave the blended tile of the item before in the Q tile; store it
+                auto store_staged = [&]() {
+                    if (MODE == MODE_NAG && sizeof(OutT) == 2 && sm_store[0]) {
+                        tma_store_3d(&tmO, sQ, (int)sm_store[1] * HD, (int)sm_store[2], 0);
+                        tma_store_3d(&tmO, sQ + HALF_BYTES, (int)sm_store[1] * HD + 64, (int)sm_store[2], 0);
+                        tma_store_commit();
+                        tma_store_wait_read();                                // the tile has been read: Q may land on it
+                    }
+                };
                 auto load_q = [&](int i) {
                     // the previous segment's S MMAs (and its output staging in the same space) are done with this tile
                     good = mbar_wait(bar(BAR_QEMPTY + i), (qe_cnt[i] & 1u) ^ 1u, abort_flag);
                     ++qe_cnt[i];
                     if (!good) return;
+                    store_staged();
                     mbar_expect_tx(bar(BAR_QFULL + i), TILE_BYTES);
                     load_tile(sQ + i * TILE_BYTES, &tmQ, bar(BAR_QFULL + i), it.q0 + i * BM, it.b);
                 };
@@ -981,7 +1079,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     ++n;
                 };
                 SegIter<MODE> iter(p);
+                bool any = false;
                 while (good && iter.next(it)) {
+                    any = true;
+                    if (MODE == MODE_NAG) {
+                        // the first K tiles do not depend on the Q tile, which the previous item's output may still occupy
+                        if (it.je[0] > 0) load_kv(&tmK0, 0);
+                        if (good && it.je[1] > 0) load_kv(&tmK1, 0);
+                        if (!good) break;
+                    }
                     load_q(0);
                     if (!good) break;
                     if (MODE == MODE_PAIR) {
@@ -993,8 +1099,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             if (good && j + 1 < je) load_kv(&tmK0, (j + 1) * BN);
                         }
                     } else {
-                        if (it.je[0] > 0) load_kv(&tmK0, 0);
-                        if (good && it.je[1] > 0) load_kv(&tmK1, 0);
                         const int nmax = max(it.je[0], it.je[1]);
                         for (int j = 0; j < nmax && good; ++j) {
                             for (int i = 0; i < 2 && good; i++) {
@@ -1005,6 +1109,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         }
                     }
                 }
+                if (MODE == MODE_NAG && sizeof(OutT) == 2 && good && any) {
+                    // two hand-overs are still to come: the last epilogue's (it staged the item before the last) and the final
+                    // one after the loop (the last item)
+                    for (int k = 0; k < 2 && good; k++) {
+                        good = mbar_wait(bar(BAR_QEMPTY + 0), (qe_cnt[0] & 1u) ^ 1u, abort_flag);
+                        ++qe_cnt[0];
+                        if (good) store_staged();
+                    }
+                    tma_store_wait_all();
+                }
                 // on failure, let the copies already in flight land before the CTA's shared memory goes away
                 if (!good || *abort_flag) {
                     const uint64_t t0 = globaltimer_ns();
@@ -1012,6 +1126,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             }
             __syncwarp();
+        }
+        if (warp == 11 && MODE == MODE_NAG && sizeof(OutT) == 2) {
+            // ------------------------------------------------------------------ norm fetcher (MODE_NAG, 16-bit output)
+            // For every item the softmax threads park: wait (bounded) until all heads of its query tile have published their
+            // norms, sum them per row in a fixed order (same bits in every thread block) and leave the totals in shared memory,
+            // all under the main loop of the next item.
+            float* const f_tot = fbuf + 256;
+            SegIter<MODE> iter(p);
+            Seg it;
+            uint32_t n = 0;
+            bool good = true;
+            while (good && iter.next(it)) {
+                good = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PARKED), n & 1u, abort_flag));
+                ++n;
+                if (!good) break;
+                const int qt = (int)sm_item[0];
+                uint32_t here = 0;
+                if (lane == 0) {
+                    // this thread block's norms of the item are stored (ordered before the arrival just acquired): make them
+                    // visible and count this head in, then wait for the other heads
+                    if (p.n_peers == 0) {
+                        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.nag_flag + qt), "r"(1u) : "memory");
+                    } else {
+                        asm volatile("fence.acq_rel.sys;" ::: "memory");
+                        for (int pe = 0; pe < p.n_peers; pe++)
+                            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.nag_flag_peers[pe] + qt), "r"(1u) : "memory");
+                    }
+                    const uint32_t target = p.nag_epoch * (uint32_t)p.nag_heads;
+                    const uint64_t t0 = globaltimer_ns();
+                    uint32_t seen = 0;
+                    for (;;) {
+                        if (p.n_peers == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + qt) : "memory");
+                        else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.nag_flag + qt) : "memory");
+                        if (seen >= target || *abort_flag) break;
+                        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1u; break; }
+                        __nanosleep(64);
+                    }
+                    here = seen >= target ? 1u : 0u;
+                }
+                here = __shfl_sync(0xffffffffu, here, 0);
+                // rows 4 lane .. 4 lane + 3: 16-byte loads, four (head, half) entries in flight at a time
+                const float4* src = reinterpret_cast<const float4*>(p.nag_part + ((size_t)qt * p.nag_heads) * 512) + lane;
+                float4 tp = make_float4(0.f, 0.f, 0.f, 0.f), tg = tp;
+                if (here) {
+                    const int n_e = 2 * p.nag_heads;                          // head and half order: same sum everywhere
+                    for (int h0 = 0; h0 < n_e; h0 += 4) {
+                        float4 a[4], b[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (h0 + u < n_e) { a[u] = __ldcg(src + (size_t)(h0 + u) * 64); b[u] = __ldcg(src + (size_t)(h0 + u) * 64 + 32); }
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (h0 + u < n_e) {
+                                tp.x += a[u].x; tp.y += a[u].y; tp.z += a[u].z; tp.w += a[u].w;
+                                tg.x += b[u].x; tg.y += b[u].y; tg.z += b[u].z; tg.w += b[u].w;
+                            }
+                    }
+                }
+                reinterpret_cast<float4*>(f_tot)[lane] = tp;
+                reinterpret_cast<float4*>(f_tot + 128)[lane] = tg;
+                if (lane == 0) wg_here[1] = here;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_NORMS));
+            }
         }
         cta_sync();
         if (warp == 8) {

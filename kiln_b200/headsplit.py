@@ -8,7 +8,7 @@ output, which is what the following output projection reads.
 Data paths:
   fused  : the attention kernel's epilogue stores each finished tile into every rank's output buffer over
            NVLink (peer-mapped pointers) and bumps arrival counters; a one-thread wait kernel gates what follows.
-           NAG: the per-token norms of the combine span all heads, so the kernels exchange 8 bytes per token and
+           NAG: the per-token norms of the combine span all heads, so the kernels exchange 16 bytes per token and
            head through every rank's exchange area, blend locally in fp32 and push only the final tiles.
   nccl   : local attention into a [T, (H/G)*128] buffer, then all_gather_into_tensor (layout [G][T][cols]) —
            the baseline the fused path is measured against.
@@ -63,7 +63,7 @@ class HeadSplit:
         self.n_qt = (T + 127) // 128
         self.xchg_bytes = L.kb_nag_exchange_bytes(T, H)
         self.xchg_off = self.N_BUFFERS * self.buf_bytes
-        self.flag_off = self.xchg_off + ((self.n_qt * H * 256 * 4 + 255) // 256) * 256
+        self.flag_off = self.xchg_off + L.kb_nag_exchange_counter_offset(T, H)
         self.ctr_off = self.xchg_off + self.xchg_bytes
         total = self.ctr_off + (2 * self.N_BUFFERS + 1) * self._CTR_LINE
         base = ctypes.c_void_p()

@@ -93,7 +93,7 @@ def measure(T=4096, H=16, L=512, reps=20, check=True, seed=7):
     us = timed(lambda: ops.attn_cross(local_out, mine["q"], mine["k"], mine["v"], T, T, 0, hs.hl, workspace=ws))
     result["self_local_only_us"] = us
     result["nag_fused_us"] = timed(nag_call)
-    # bytes each rank pushes to remote GPUs per call (final tiles only; NAG adds 8 bytes per token and local head)
+    # bytes each rank pushes to remote GPUs per call (final tiles only; NAG adds 16 bytes per token and local head)
     result["remote_bytes_per_rank"] = (G - 1) * T * hs.hl * 128 * 2
     result["push_gbs_per_rank"] = result["remote_bytes_per_rank"] / max(result["self_fused_us"] - result["self_local_only_us"], 1e-3) / 1e3
     result["nvlink_peak_gbs_per_direction"] = 900

@@ -24,10 +24,21 @@ void need_d128(int Dh, const char* what) {
 void set_context(const OpContext& ctx) { g_ctx = ctx; }
 const OpContext& context() { return g_ctx; }
 
+namespace { ExactAttentionFn g_exact = nullptr; }
+void set_exact_attention(ExactAttentionFn fn) { g_exact = fn; }
+bool attention_eligible(int Dh, bool causal, int ldq, int ldk, int ldv, int ldo) {
+    return !causal && Dh == 128 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && ldo % 4 == 0;   // engine/src/kernels.cu:830, tcflash.cuh:170-172
+}
+
 void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, int Tq, int Tk,
                int H, int Dh, bool causal, int npad) {
-    need_d128(Dh, "attention");
-    if (causal) throw std::runtime_error("attention: causal attention is not on the fused path");
+    if (!attention_eligible(Dh, causal, ldq, ldk, ldv, ldo)) {
+        // the reference's dispatcher keeps these on its exact fp32 path (engine/src/kernels.cu:842-865)
+        if (g_exact) return g_exact(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, causal, npad);
+        need_d128(Dh, "attention");
+        throw std::runtime_error(causal ? "attention: causal attention is not on the fused path and no exact path is registered"
+                                        : "attention: unsupported head size or row stride");
+    }
     check(kb_attn_cross(out, q, nullptr, k, v, Tq, Tk, npad, H, ldq, ldk, ldv, ldo, KB_F32, KB_F32, 1e-6f, g_ctx.workspace,
                         g_ctx.workspace_bytes, g_ctx.stream),
           "attention");
@@ -43,8 +54,10 @@ void attention16(__half* out, int ldo, const float* q, int ldq, const float* k, 
 
 void rmsnorm(float* y, const float* x, const uint16_t* w_bf16, int rows, int dim, float eps) {
     if (dim != 128) throw std::runtime_error("rmsnorm: only the per-head rows of 128 are on this path");
-    // rows of 128 are (token, head) pairs: one "head" per row
-    check(kb_qk_prep(y, 128, KB_F32, x, 128, KB_F32, rows, 1, 1, w_bf16, eps, nullptr, nullptr, g_ctx.stream), "rmsnorm");
+    // rows of 128 are (token, head) pairs: one "head" per row; no weight = weight 1 (engine/src/kernels.cu:650-673)
+    const void* w = w_bf16 ? static_cast<const void*>(w_bf16) : kb_unit_norm_weight();
+    if (!w) throw std::runtime_error("rmsnorm: no device");
+    check(kb_qk_prep(y, 128, KB_F32, x, 128, KB_F32, rows, 1, 1, w, eps, nullptr, nullptr, g_ctx.stream), "rmsnorm");
 }
 
 void rope_half(float* x, int T, int H, int Dh, const float* cos_t, const float* sin_t) {
@@ -136,6 +149,47 @@ int kbh_linear16(void* y, int ldy, const void* x16, int T, const void* w16, int 
         if (a.epi == 4) kiln_b200::linear16_heads((__half*)a.y, a.ldy, (const __half*)a.x, a.T, W, a.nw, a.c, a.s, a.rope_T, a.eps);
         else kiln_b200::linear16(a.y, a.ldy, (const __half*)a.x, a.T, W, (kiln_b200::Epi16)a.epi, a.gate);
     }, &a);
+}
+struct SA { void* out; int ldo; const float *q, *k, *v; int ld; int B, T, H; const uint16_t *qw, *kw; const float *c, *s; float eps; };
+int kbh_self_attention16(void* out, int ldo, const float* q, const float* k, const float* v, int ld, int B, int T, int H, const uint16_t* qn_w,
+                         const uint16_t* kn_w, const float* c, const float* s, float eps, char* err, int n) {
+    SA a{out, ldo, q, k, v, ld, B, T, H, qn_w, kn_w, c, s, eps};
+    return guard(err, n, [](void* p) {
+        SA& a = *(SA*)p;
+        kiln_b200::self_attention16((__half*)a.out, a.ldo, a.q, a.ld, a.k, a.ld, a.v, a.ld, a.B, a.T, a.H, a.qw, a.kw, a.c, a.s, a.eps);
+    }, &a);
+}
+struct NA { void* out; int ldo; const float* q; int ldq; const uint16_t* qw; const float *kp, *vp; int Tp, npp; const float *kn, *vn; int Tn, npn, ldkv; float s, tau, alpha; int Tq, H; float eps; };
+int kbh_nag_attention16(void* out, int ldo, const float* q, int ldq, const uint16_t* qn_w, const float* kp, const float* vp, int Tp, int npp,
+                        const float* kn, const float* vn, int Tn, int npn, int ldkv, float s, float tau, float alpha, int Tq, int H, float eps,
+                        char* err, int n) {
+    NA a{out, ldo, q, ldq, qn_w, kp, vp, Tp, npp, kn, vn, Tn, npn, ldkv, s, tau, alpha, Tq, H, eps};
+    return guard(err, n, [](void* p) {
+        NA& a = *(NA*)p;
+        kiln_b200::nag_attention16((__half*)a.out, a.ldo, a.q, a.ldq, a.qw, a.kp, a.vp, a.Tp, a.npp, a.kn, a.vn, a.Tn, a.npn, a.ldkv, a.s, a.tau,
+                                   a.alpha, a.Tq, a.H, a.eps);
+    }, &a);
+}
+struct LQ { void *q, *k, *v; int ldy; const void* x; int T; const void *wq, *wk, *wv; int rows, cols; const uint16_t *qw, *kw; const float *c, *s; int rope_T; float eps; };
+int kbh_linear16_qkv(void* q, void* k, void* v, int ldy, const void* x16, int T, const void* wq, const void* wk, const void* wv, int rows, int cols,
+                     const uint16_t* qn_w, const uint16_t* kn_w, const float* c, const float* s, int rope_T, float eps, char* err, int n) {
+    LQ a{q, k, v, ldy, x16, T, wq, wk, wv, rows, cols, qn_w, kn_w, c, s, rope_T, eps};
+    return guard(err, n, [](void* p) {
+        LQ& a = *(LQ*)p;
+        kiln_b200::Weight16 W[3];
+        const void* ws[3] = {a.wq, a.wk, a.wv};
+        for (int i = 0; i < 3; i++) { W[i].p = (const __half*)ws[i]; W[i].rows = a.rows; W[i].cols = a.cols; }
+        kiln_b200::linear16_qkv((__half*)a.q, (__half*)a.k, (__half*)a.v, a.ldy, (const __half*)a.x, a.T, W[0], W[1], W[2], a.qw, a.kw, a.c, a.s,
+                                a.rope_T, a.eps);
+    }, &a);
+}
+// the exact-path hook: a stand-in "engine path" that only records that it was reached
+static int g_exact_calls = 0;
+static void exact_probe(float*, int, const float*, int, const float*, int, const float*, int, int, int, int, int, bool, int) { ++g_exact_calls; }
+int kbh_register_exact_probe(int on) { kiln_b200::set_exact_attention(on ? exact_probe : nullptr); return g_exact_calls; }
+int kbh_rmsnorm_only(float* x, const uint16_t* w, int rows, float eps, char* err, int n) {
+    NR a{x, w, rows, 0, 0, eps, nullptr, nullptr};
+    return guard(err, n, [](void* p) { NR& a = *(NR*)p; kiln_b200::rmsnorm(a.x, a.x, a.w, a.rows, 128, a.eps); }, &a);
 }
 // Host cost of enqueueing one fp16 cross-attention call through the C ABI (argument checks, four tensor-map encodes, one
 // launch), in microseconds: wall clock around n back-to-back calls that are not waited for, then one synchronise.

@@ -31,17 +31,26 @@ void set_context(const OpContext& ctx);
 const OpContext& context();
 
 // q [Tq, ldq], k/v [Tk, ld*], out [Tq, ldo] fp32; head h at column h*Dh; npad zero keys join the softmax.
-// Dh must be 128 and causal false: the reference sends everything else to its cuBLAS path, which is not part of this library.
+// The fused kernels take what the reference's own fast path takes (engine/src/kernels.cu:830: not causal, Dh == 128, row strides
+// that are multiples of 4). The reference's dispatcher sends everything else - the causal text encoder (engine/src/te.cu:90),
+// the Dh = 64 adapter (engine/src/dit.cu:106-169) - to its exact fp32 path (engine/src/kernels.cu:842-865), which is not
+// part of this library: the engine registers that path here once and attention() falls through to it exactly as the
+// reference's dispatcher does; without a registered path such a call throws.
+using ExactAttentionFn = void (*)(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                  int Tq, int Tk, int H, int Dh, bool causal, int npad);
+void set_exact_attention(ExactAttentionFn fn);
+bool attention_eligible(int Dh, bool causal, int ldq, int ldk, int ldv, int ldo);
 void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                int Tq, int Tk, int H, int Dh, bool causal, int npad = 0);
 void attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                  int Tq, int Tk, int H, int Dh, int npad = 0);
 
 // In-place fp32 RMSNorm over rows of 128 with a bf16 weight (the reference passes a Weight*; its ->p is this pointer).
+// A null weight normalises with weight 1, as the reference does (engine/src/kernels.cu:650-673).
 void rmsnorm(float* y, const float* x, const uint16_t* w_bf16, int rows, int dim, float eps);
 void rope_half(float* x, int T, int H, int Dh, const float* cos_t, const float* sin_t);
 
-// Fused forms the DiT block driver can call instead of the unfused sequences (see INTEGRATION.md):
+// Fused forms the DiT block driver can call instead of the unfused sequences:
 // rmsnorm(Q) + rmsnorm(K) + rope_half(Q) + rope_half(K) + attention16 per batch element -> one call for the whole batch
 void self_attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                       int B, int T, int H, const uint16_t* qn_w, const uint16_t* kn_w, const float* rope_cos,

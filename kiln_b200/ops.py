@@ -73,6 +73,8 @@ def lib():
                                        i, i, i, i, i, i, i, f, vp, sz, vp]
         L.kb_nag_exchange_bytes.restype = sz
         L.kb_nag_exchange_bytes.argtypes = [i, i]
+        L.kb_nag_exchange_counter_offset.restype = sz
+        L.kb_nag_exchange_counter_offset.argtypes = [i, i]
         L.kb_bump_counters.restype = i
         L.kb_bump_counters.argtypes = [ctypes.POINTER(vp), i, vp]
         L.kb_push_arrivals_per_call.restype = ull

@@ -15,7 +15,15 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libkiln_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libkiln_ref.so")
-GCC_B = "/usr/lib/gcc/x86_64-linux-gnu/13/"   # where libgomp.spec lives on images whose gcc wrapper hides it
+
+
+def _gomp_dir():
+    """Directory of libgomp.spec as gcc itself reports it, for images whose gcc wrapper does not find it for -fopenmp."""
+    try:
+        path = subprocess.run(["gcc", "-print-file-name=libgomp.spec"], capture_output=True, text=True).stdout.strip()
+    except OSError:
+        return None
+    return os.path.dirname(path) + os.sep if os.path.isabs(path) and os.path.exists(path) else None
 
 
 def _newer(target, *deps):
@@ -31,8 +39,9 @@ def build_oracle(force=False):
         return ORACLE_SO
     base = ["gcc", "-O3", "-fopenmp", "-fPIC", "-mavx2", "-mfma", "-fno-math-errno", "-shared", "-o", ORACLE_SO, src, "-lm"]
     r = subprocess.run(base, capture_output=True, text=True)
-    if r.returncode != 0 and os.path.isdir(GCC_B):
-        r = subprocess.run(base[:1] + ["-B" + GCC_B] + base[1:], capture_output=True, text=True)
+    gomp = _gomp_dir()
+    if r.returncode != 0 and gomp:
+        r = subprocess.run(base[:1] + ["-B" + gomp] + base[1:], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + r.stderr)
     return ORACLE_SO

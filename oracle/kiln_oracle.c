@@ -43,6 +43,15 @@ int ko_max_threads(void) {
 #endif
 }
 
+/* size of the OpenMP team of the following calls (a launcher may export OMP_NUM_THREADS=1 to its ranks) */
+void ko_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ---- 16-bit float helpers (round to nearest even), so Python and C agree on the rounded inputs ---- */
 static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }

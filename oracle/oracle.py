@@ -50,6 +50,12 @@ def max_threads():
     return lib().ko_max_threads()
 
 
+def set_threads(n):
+    """Size of the OpenMP team used by the following calls."""
+    lib().ko_set_num_threads.argtypes = [ctypes.c_int]
+    lib().ko_set_num_threads(int(n))
+
+
 def randn(seed, n):
     """torch.manual_seed(seed); torch.randn(n) on CPU, restated (reference: engine/src/pipeline.cu:16-64)."""
     out = np.empty(n, np.float32)

@@ -41,9 +41,9 @@ def test_error_strings_and_sizes(built_lib):
     assert kiln_b200.workspace_bytes(100, 7, 2, F16, True, False) == 100 * 256 * 2 + split
     assert kiln_b200.workspace_bytes(100, 7, 2, F16) == split
     assert kiln_b200.workspace_bytes(1, 1, 1, F16, True, True) == 512 + split
-    # NAG adds the cross-head norm exchange: [12 query tiles][16 heads][2][128] floats + 12 counters (256-byte aligned)
-    assert kiln_b200.workspace_bytes(1536, 512, 16, F32, n_ctx=2) == (1536 + 4 * 512) * 2048 * 2 + 12 * 16 * 1024 + 256
-    assert kiln_b200.workspace_bytes(1536, 512, 16, F16, n_ctx=2) == 12 * 16 * 1024 + 256
+    # NAG adds the cross-head norm exchange: [12 query tiles][16 heads][2 column halves][2][128] floats + 12 counters (256-byte aligned)
+    assert kiln_b200.workspace_bytes(1536, 512, 16, F32, n_ctx=2) == (1536 + 4 * 512) * 2048 * 2 + 12 * 16 * 2048 + 256
+    assert kiln_b200.workspace_bytes(1536, 512, 16, F16, n_ctx=2) == 12 * 16 * 2048 + 256
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")

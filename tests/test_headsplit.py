@@ -160,7 +160,7 @@ def test_nag_push_epilogue_and_exchange_counters_on_one_gpu(built_lib):
     kb.attn_nag(ref, dq, dkp, dvp, Tp, Lc - Tp, dkn, dvn, Tn, Lc - Tn, 5.0, 2.5, 0.25, Tq, H, qn_w=dw, workspace=ws)
     xb = L.kb_nag_exchange_bytes(Tq, H)
     n_qt = (Tq + 127) // 128
-    flag_off = ((n_qt * H * 256 * 4 + 255) // 256) * 256
+    flag_off = L.kb_nag_exchange_counter_offset(Tq, H)
     xch = [torch.zeros(xb, dtype=torch.uint8, device="cuda") for _ in range(2)]
     bufs = [torch.full((Tq, 2 * D), 9.0, device="cuda", dtype=torch.bfloat16) for _ in range(2)]      # the heads land at columns D..2D
     ctrs = torch.zeros(2, 32, dtype=torch.int64, device="cuda")

@@ -110,3 +110,87 @@ def test_enqueue_cost_from_cpp(shim):
     us = shim.kbh_enqueue_cost_us(P(out), P(q), P(k), P(v), Tq, Tk, 0, H, 200)
     print(f"\nhost cost per kb_attn_cross call from C++: {us:.2f} us (200 calls, device time ~8 us each)")
     assert 0 < us < 100
+
+
+def _bits(w):
+    return (w.view(np.uint32) >> 16).astype(np.uint16)
+
+
+def test_fused_self_attention16_engine_buffers(shim):
+    """self_attention16: the engine's fp32 Q/K/V quarters of one [R, 4D] buffer (engine/src/dit.cu:387-388) with the per-head
+    norm weights and the RoPE tables, B = 2, fp16 out - one call for rmsnorm x2 + rope_half x2 per image + attention16."""
+    Hp, Wp, B, H = 9, 14, 2, 4
+    T, D = Hp * Wp, 4 * 128
+    big = oracle.randn(700, B * T * 4 * D).reshape(B * T, 4 * D)
+    wq = oracle.round16(1 + 0.02 * oracle.randn(701, 128), 1)
+    wk = oracle.round16(1 + 0.02 * oracle.randn(702, 128), 1)
+    c, s = oracle.cosmos_rope(Hp, Wp)
+    dbig = dev(big)
+    out = torch.full((B * T, D), float("nan"), device="cuda", dtype=torch.float16)
+    err = ctypes.create_string_buffer(256)
+    q_ptr = ctypes.c_void_p(dbig.data_ptr())
+    k_ptr = ctypes.c_void_p(dbig.data_ptr() + D * 4)
+    v_ptr = ctypes.c_void_p(dbig.data_ptr() + 2 * D * 4)
+    dwq, dwk = dev(_bits(wq).view(np.int16)), dev(_bits(wk).view(np.int16))
+    assert shim.kbh_self_attention16(P(out), D, q_ptr, k_ptr, v_ptr, 4 * D, B, T, H, P(dwq), P(dwk), P(dev(c)), P(dev(s)), ctypes.c_float(1e-6),
+                                     err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    q, k, v = (np.ascontiguousarray(big[:, i * D:(i + 1) * D]) for i in range(3))
+    nr = lambda x, w: np.concatenate([oracle.rope_half(oracle.rmsnorm(x[b * T:(b + 1) * T], _bits(w), H), T, H, c, s) for b in range(B)])
+    qn, kn = nr(q, wq), nr(k, wk)
+    ref = np.concatenate([oracle.attention(qn[b * T:(b + 1) * T], kn[b * T:(b + 1) * T], v[b * T:(b + 1) * T], H) for b in range(B)])
+    assert_close(out.float().cpu().numpy(), ref, "shim self_attention16")
+
+
+def test_fused_nag_attention16_and_qkv_projection(shim):
+    """nag_attention16 (rmsnorm(Q) + attention16 x2 + k_nag in one call, engine/src/dit.cu:476-487) and linear16_qkv (the three
+    projections + norm + RoPE of engine/src/dit.cu:461-468 in one launch) against the oracle chains."""
+    Tq, H, L, Tp, Tn = 200, 4, 512, 77, 26
+    D = H * 128
+    q = oracle.randn(710, Tq * D).reshape(Tq, D)
+    ctx = [oracle.randn(711 + i, L * D).reshape(L, D) for i in range(4)]
+    wq = oracle.round16(1 + 0.02 * oracle.randn(715, 128), 1)
+    out = torch.full((Tq, D), float("nan"), device="cuda", dtype=torch.float16)
+    err = ctypes.create_string_buffer(256)
+    f = ctypes.c_float
+    dctx = [dev(x) for x in ctx]
+    assert shim.kbh_nag_attention16(P(out), D, P(dev(q)), D, P(dev(_bits(wq).view(np.int16))), P(dctx[0]), P(dctx[1]), Tp, L - Tp, P(dctx[2]), P(dctx[3]),
+                                    Tn, L - Tn, D, f(5.0), f(2.5), f(0.25), Tq, H, f(1e-6), err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    qn = oracle.rmsnorm(q, _bits(wq), H)
+    zp = oracle.attention(qn, ctx[0][:Tp], ctx[1][:Tp], H, L - Tp)
+    zn = oracle.attention(qn, ctx[2][:Tn], ctx[3][:Tn], H, L - Tn)
+    assert_close(out.float().cpu().numpy(), oracle.nag(zp, zn, 5.0, 2.5, 0.25), "shim nag_attention16")
+
+    M, K = 150, 256
+    x = oracle.round16(oracle.randn(720, M * K), 0).reshape(M, K)
+    ws = [oracle.round16(oracle.randn(721 + i, D * K) * np.float32(0.05), 0).reshape(D, K) for i in range(3)]
+    wk = oracle.round16(1 + 0.02 * oracle.randn(725, 128), 1)
+    cos, sin = oracle.cosmos_rope(10, 15)
+    ys = [torch.full((M, D), float("nan"), device="cuda", dtype=torch.float16) for _ in range(3)]
+    dws = [dev(w).half() for w in ws]
+    assert shim.kbh_linear16_qkv(P(ys[0]), P(ys[1]), P(ys[2]), D, P(dev(x).half()), M, P(dws[0]), P(dws[1]), P(dws[2]), D, K,
+                                 P(dev(_bits(wq).view(np.int16))), P(dev(_bits(wk).view(np.int16))), P(dev(cos)), P(dev(sin)), 150, f(1e-6), err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    assert_close(ys[0].float().cpu().numpy(), oracle.linear_heads16(x, ws[0], H, _bits(wq), cos, sin), "shim linear16_qkv q")
+    assert_close(ys[1].float().cpu().numpy(), oracle.linear_heads16(x, ws[1], H, _bits(wk), cos, sin), "shim linear16_qkv k")
+    ref_v = oracle.linear16(x, ws[2], 1)
+    assert np.abs(ys[2].float().cpu().numpy() - ref_v).max() <= 2e-4 + 2.0 ** -10 * np.abs(ref_v).max()
+
+
+def test_ineligible_attention_falls_through_to_the_engines_exact_path(shim):
+    """attention() forwards to the fused kernels only what the reference's own fast path takes; a causal call (the text
+    encoder) or Dh = 64 (the adapter) goes to the exact path the engine registered, as in the reference's dispatcher
+    (engine/src/kernels.cu:830-866); rmsnorm with no weight normalises with weight 1 (engine/src/kernels.cu:650-673)."""
+    t = torch.zeros(64, 256, device="cuda")
+    err = ctypes.create_string_buffer(256)
+    before = shim.kbh_register_exact_probe(1)
+    assert shim.kbh_attention(P(t), 256, P(t), 256, P(t), 256, P(t), 256, 64, 64, 2, 128, 1, 0, 1, err, 256) == 0      # causal
+    assert shim.kbh_attention(P(t), 256, P(t), 256, P(t), 256, P(t), 256, 64, 64, 4, 64, 0, 0, 1, err, 256) == 0       # Dh = 64
+    assert shim.kbh_register_exact_probe(0) == before + 2
+    assert shim.kbh_attention(P(t), 256, P(t), 256, P(t), 256, P(t), 256, 64, 64, 2, 128, 1, 0, 1, err, 256) == -1     # nothing registered: throws
+    x = oracle.randn(730, 40 * 128).reshape(40, 128)
+    dx = dev(x)
+    assert shim.kbh_rmsnorm_only(P(dx), None, 40, ctypes.c_float(1e-6), err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(dx.cpu().numpy(), oracle.rmsnorm(x, None, 1), rtol=1e-5, atol=2e-6)
