@@ -163,7 +163,8 @@ struct PrepBatch {
         sg.in = in; sg.out = out; sg.w = static_cast<const __nv_bfloat16*>(w); sg.cos_t = c; sg.sin_t = s;
         sg.rows = rows; sg.ld_in = ld_in; sg.ld_out = ld_out; sg.T = T > 0 ? T : 1;
         sg.block0 = pp.blocks;
-        pp.blocks += (unsigned)(((long long)rows * pp.H + PREP_ITEMS_PER_BLOCK - 1) / PREP_ITEMS_PER_BLOCK);
+        const int per_block = c ? PREP_ITEMS_PER_BLOCK_ROPE : PREP_ITEMS_PER_BLOCK;
+        pp.blocks += (unsigned)(((long long)rows * pp.H + per_block - 1) / per_block);
     }
 };
 

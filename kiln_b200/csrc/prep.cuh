@@ -116,9 +116,13 @@ struct PrepParams {
 
 // Measured on B200: a plain one-16-byte-load-per-thread conversion runs at the speed of a device copy
 // (101 MB in 18.6 us), and unrolling for more loads in flight buys nothing; what costs bandwidth is
-// occupancy. So: one (row, head) per half-warp, lane `sub` holds elements [8 sub, 8 sub + 8), one pass,
-// no loop; a thread block belongs to exactly one tensor so the tensor lookup is block-uniform.
-constexpr int PREP_ITEMS_PER_BLOCK = 16;   // 256 threads / 16 lanes
+// occupancy and narrow accesses. So: no loop, one pass, 16-byte accesses for 16-bit data everywhere, and a thread
+// block belongs to exactly one tensor so the tensor lookup is block-uniform.
+//   without RoPE: one (row, head) per half-warp, lane `sub` holds elements [8 sub, 8 sub + 8);
+//   with RoPE   : one (row, head) per quarter-warp, lane `sub` holds elements [8 sub, 8 sub + 8) AND their rotation
+//                 partners [64 + 8 sub, ...), so the rotation needs no shuffle and each table entry is loaded once.
+constexpr int PREP_ITEMS_PER_BLOCK = 16;        // 256 threads / 16 lanes
+constexpr int PREP_ITEMS_PER_BLOCK_ROPE = 32;   // 256 threads / 8 lanes
 
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
@@ -130,42 +134,46 @@ qk_prep_kernel(const __grid_constant__ PrepParams pp) {
     for (int i = 1; i < 5; i++)
         if (i < pp.nseg && blockIdx.x >= pp.seg[i].block0) si = i;
     const PrepSeg& sg = pp.seg[si];
-    const int sub = threadIdx.x & 15;
-    const long long item = (long long)(blockIdx.x - sg.block0) * PREP_ITEMS_PER_BLOCK + (threadIdx.x >> 4);
-    const bool live = item < (long long)sg.rows * pp.H;      // uniform across a half-warp
-    const int r = live ? (int)(item / pp.H) : 0, h = live ? (int)(item % pp.H) : 0;
     if (sg.cos_t) {
-        // RoPE tensors: lane `sub` holds elements [4 sub, 4 sub + 4) and their partners [64 + 4 sub, ...), so the
-        // rotation needs no shuffle and each table entry is loaded once (8-byte accesses for 16-bit data).
-        F4 a = {}, b = {};
-        const InT* src = static_cast<const InT*>(sg.in) + (size_t)r * sg.ld_in + h * 128 + 4 * sub;
-        if (live) { a = Io<InT>::ld4(src); b = Io<InT>::ld4(src + 64); }
+        const int sub = threadIdx.x & 7;
+        const long long item = (long long)(blockIdx.x - sg.block0) * PREP_ITEMS_PER_BLOCK_ROPE + (threadIdx.x >> 3);
+        const bool live = item < (long long)sg.rows * pp.H;  // uniform across a quarter-warp
+        const int r = live ? (int)(item / pp.H) : 0, h = live ? (int)(item % pp.H) : 0;
+        F8 a, b;
+#pragma unroll
+        for (int e = 0; e < 8; e++) a.v[e] = b.v[e] = 0.f;
+        const InT* src = static_cast<const InT*>(sg.in) + (size_t)r * sg.ld_in + h * 128 + 8 * sub;
+        if (live) { a = Io<InT>::ld8(src); b = Io<InT>::ld8(src + 64); }
         if (sg.w) {
             float ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < 4; e++) ss += a.v[e] * a.v[e] + b.v[e] * b.v[e];
+            for (int e = 0; e < 8; e++) ss += a.v[e] * a.v[e] + b.v[e] * b.v[e];
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float rs = rsqrtf(ss * (1.f / 128.f) + pp.eps);
-            const F4 wa = Io<__nv_bfloat16>::ld4(sg.w + 4 * sub), wb = Io<__nv_bfloat16>::ld4(sg.w + 64 + 4 * sub);
+            const F8 wa = Io<__nv_bfloat16>::ld8(sg.w + 8 * sub), wb = Io<__nv_bfloat16>::ld8(sg.w + 64 + 8 * sub);
 #pragma unroll
-            for (int e = 0; e < 4; e++) { a.v[e] = a.v[e] * rs * wa.v[e]; b.v[e] = b.v[e] * rs * wb.v[e]; }
+            for (int e = 0; e < 8; e++) { a.v[e] = a.v[e] * rs * wa.v[e]; b.v[e] = b.v[e] * rs * wb.v[e]; }
         }
-        const size_t tr = (size_t)(r % sg.T) * 64 + 4 * sub;
-        const F4 c = Io<float>::ld4(sg.cos_t + tr), s = Io<float>::ld4(sg.sin_t + tr);
-        F4 x, y;
+        const size_t tr = (size_t)(r % sg.T) * 64 + 8 * sub;
+        const F8 c = Io<float>::ld8(sg.cos_t + tr), s = Io<float>::ld8(sg.sin_t + tr);
+        F8 x, y;
 #pragma unroll
-        for (int e = 0; e < 4; e++) {                         // engine/src/kernels.cu:769-771
+        for (int e = 0; e < 8; e++) {                         // engine/src/kernels.cu:769-771
             x.v[e] = a.v[e] * c.v[e] - b.v[e] * s.v[e];
             y.v[e] = b.v[e] * c.v[e] + a.v[e] * s.v[e];
         }
         if (live) {
-            OutT* dst = static_cast<OutT*>(sg.out) + (size_t)r * sg.ld_out + h * 128 + 4 * sub;
-            Io<OutT>::st4(dst, x);
-            Io<OutT>::st4(dst + 64, y);
+            OutT* dst = static_cast<OutT*>(sg.out) + (size_t)r * sg.ld_out + h * 128 + 8 * sub;
+            Io<OutT>::st8(dst, x);
+            Io<OutT>::st8(dst + 64, y);
         }
         return;
     }
+    const int sub = threadIdx.x & 15;
+    const long long item = (long long)(blockIdx.x - sg.block0) * PREP_ITEMS_PER_BLOCK + (threadIdx.x >> 4);
+    const bool live = item < (long long)sg.rows * pp.H;      // uniform across a half-warp
+    const int r = live ? (int)(item / pp.H) : 0, h = live ? (int)(item % pp.H) : 0;
     // no RoPE: lane `sub` holds elements [8 sub, 8 sub + 8) (16-byte accesses for 16-bit data)
     F8 x;
     if (live) x = Io<InT>::ld8(static_cast<const InT*>(sg.in) + (size_t)r * sg.ld_in + h * 128 + 8 * sub);
