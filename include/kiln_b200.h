@@ -197,8 +197,8 @@ const void* kb_unit_norm_weight(void);
 /* The projections either side of attention: C = epilogue(A[M,K] * W[N,K]^T), A and W fp16 row-major
  * (row strides lda, ldw in elements), fp32 accumulation. Replaces the engine's fp16-activation GEMM
  * linear16 -> tc16::launch (engine/src/kernels.cu:559-609, engine/src/tcgemm16.cuh:57-190; call sites
- * engine/src/dit.cu:461-463 (q/k/v), 471 (o-proj into the residual), 475, 488) without its LoRA second
- * product. Epilogues as there (engine/src/tcgemm16.cuh:145-174):
+ * engine/src/dit.cu:461-463 (q/k/v), 471 (o-proj into the residual), 475, 488); its LoRA second product is
+ * kb_linear16_lora below. Epilogues as there (engine/src/tcgemm16.cuh:145-174):
  *   KB_EPI_F32     C fp32 = acc
  *   KB_EPI_F16     C fp16 = acc
  *   KB_EPI_GELU16  C fp16 = gelu_erf(acc)
@@ -210,7 +210,8 @@ const void* kb_unit_norm_weight(void);
  *                  pre-pass into the q / k projection, so the attention entry points get fp16 operands
  *                  that need no further pass.
  * N must be a multiple of 128 and K of 64 (the engine asks N % 128 == 0, K % 32 == 0; every DiT weight
- * has K = 2048 or 8192); M is free. Pointers 16-byte aligned, strides multiples of 8 (fp16) / 4 (fp32). */
+ * has K = 2048 or 8192); M is free. The three plain store epilogues (F32, F16, GELU16) also take any N that is a
+ * multiple of 8: a LoRA down-projection t = x . A_cat^T has the stacked rank for its width. Pointers 16-byte aligned, strides multiples of 8 (fp16) / 4 (fp32). */
 enum { KB_EPI_F32 = 0, KB_EPI_F16 = 1, KB_EPI_GELU16 = 2, KB_EPI_RESID = 3, KB_EPI_HEADS16 = 4 };
 int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw, int M, int N, int K, int epi,
                 const float* gate, const void* head_w_bf16, const float* rope_cos, const float* rope_sin, int rope_T,
@@ -226,6 +227,29 @@ int kb_linear16(void* C, int ldc, const void* A, int lda, const void* W, int ldw
 int kb_linear16_qkv(void* const* C3, int ldc, const void* A, int lda, const void* const* W3, int ldw, int M, int N, int K,
                     const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
                     float eps, void* stream);
+
+/* kb_linear16 with a second product, the engine's unmerged LoRA side path (Args::A2, W2, K2 of
+ * engine/src/tcgemm16.cuh:26-28, consumed at tcgemm16.cuh:70-76; composed by linear16, engine/src/kernels.cu:578-596):
+ *   C = epilogue(A . W^T + A2 . W2^T),   A2 fp16 [M, K2] (row stride lda2), W2 fp16 [N, K2] (row stride ldw2).
+ * In the engine A2 is t = x . A_cat^T (the stacked down-projections) and W2 is B_cat = [s1 B1 | s2 B2 | ...] with the
+ * LoRA scales folded in, so every epilogue sees the LoRA-adjusted value. K2 is a multiple of 8 (the engine pads the
+ * stacked rank to 32; here a last partial 64-wide k step reads zeros), K2 = 0 is kb_linear16. The second product's k
+ * steps follow the first's in the same accumulator: no extra launch, no extra pass over C. Same argument rules as
+ * kb_linear16 otherwise. */
+int kb_linear16_lora(void* C, int ldc, const void* A, int lda, const void* W, int ldw, const void* A2, int lda2, const void* W2,
+                     int ldw2, int K2, int M, int N, int K, int epi, const float* gate, const void* head_w_bf16,
+                     const float* rope_cos, const float* rope_sin, int rope_T, float eps, void* stream);
+
+/* kb_linear16_qkv with a second product per projection: A2_3[i] fp16 [M, K2_3[i]] with row stride lda2_3[i],
+ * W2_3[i] fp16 [N, K2_3[i]] with row stride ldw2_3[i] (K2_3[i] = 0: projection i has no LoRA and its pointers may be NULL). Bit-identical to three kb_linear16_lora calls. */
+int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const void* const* W3, int ldw, const void* const* A2_3,
+                         const int* lda2_3, const void* const* W2_3, const int* ldw2_3, const int* K2_3, int M, int N, int K,
+                         const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
+                         float eps, void* stream);
+
+/* dst[r * ld + col0 + c] = fp16(scale * src[r, c]) for a bf16 matrix [rows, cols]: builds the stacked operands A_cat
+ * (scale 1) and B_cat (the LoRA's scale) of the second product (k_lora_pack, engine/src/kernels.cu:548-554). */
+int kb_lora_pack(void* dst_f16, int ld, int col0, const void* src_bf16, int rows, int cols, float scale, void* stream);
 
 /* Read and clear the device status word of the current device (synchronises the device).
  * *status_bits = 0 when every kernel since the last call finished normally; returns KB_ERR_TIMEOUT

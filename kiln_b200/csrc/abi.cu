@@ -571,7 +571,7 @@ template <int EPI, bool PAIR>
 int launch_gemm_shape(DeviceState* st, const CUtensorMap& ta, const GemmMaps& maps, GemmParams p, int n_seg, cudaStream_t stream) {
     const int tile = PAIR ? 256 : 128, per_group = PAIR ? 2 : 1;
     p.tiles_m = (p.M + tile - 1) / tile;
-    p.tiles_n_seg = p.N / tile;
+    p.tiles_n_seg = (p.N + tile - 1) / tile;
     p.tiles_n = p.tiles_n_seg * n_seg;
     const int n_tiles = p.tiles_m * p.tiles_n, max_groups = st->sm_count / per_group;
     const int groups = n_tiles < max_groups ? n_tiles : max_groups;
@@ -602,10 +602,19 @@ int launch_gemm(DeviceState* st, const CUtensorMap& ta, const GemmMaps& maps, co
     return launch_gemm_shape<EPI, false>(st, ta, maps, p, n_seg, stream);
 }
 
+// The second product of a segment (null = none): A2 [M, K2] with row stride lda2, W2 [N, K2] with row stride ldw2.
+struct SecondProduct {
+    const void* const* A2 = nullptr;
+    const void* const* W2 = nullptr;
+    const int* K2 = nullptr;
+    const int* lda2 = nullptr;
+    const int* ldw2 = nullptr;
+};
+
 // shared body of kb_linear16 (one weight matrix) and kb_linear16_qkv (three, one launch)
 int linear16_segments(void* const* C, int ldc, const void* A, int lda, const void* const* W, int ldw, int n_seg, int M, int N, int K, int epi,
                       const float* gate, const void* const* head_w, const int* rope_on, const float* rope_cos, const float* rope_sin,
-                      int rope_T, float eps, cudaStream_t stream) {
+                      int rope_T, float eps, cudaStream_t stream, const SecondProduct& sp = SecondProduct()) {
     if (!A || M < 0 || N <= 0 || K <= 0 || n_seg < 1 || n_seg > 3) return KB_ERR_ARG;
     if (epi < KB_EPI_F32 || epi > KB_EPI_HEADS16) return KB_ERR_ARG;
     if ((rope_cos == nullptr) != (rope_sin == nullptr)) return KB_ERR_ARG;
@@ -623,7 +632,17 @@ int linear16_segments(void* const* C, int ldc, const void* A, int lda, const voi
         any_rope = any_rope || rope_on[i];
     }
     if (any_rope && !rope_cos) return KB_ERR_ARG;
-    if ((N % 128) || (K % GB_K) || lda < K || ldw < K || ldc < N) return KB_ERR_SHAPE;
+    // A plain store epilogue of one matrix also takes a width that is no multiple of the 128-column tile (the rank of a
+    // LoRA down-projection): the weight rows past N read as zeros and the stores past N are left out.
+    const bool narrow_ok = n_seg == 1 && (epi == KB_EPI_F32 || epi == KB_EPI_F16 || epi == KB_EPI_GELU16);
+    if ((narrow_ok ? (N % 8) : (N % 128)) || (K % GB_K) || lda < K || ldw < K || ldc < N) return KB_ERR_SHAPE;
+    for (int i = 0; i < n_seg && sp.K2; i++) {
+        if (sp.K2[i] < 0) return KB_ERR_ARG;
+        if (sp.K2[i] == 0) continue;
+        if (!sp.A2 || !sp.W2 || !sp.lda2 || !sp.ldw2 || !sp.A2[i] || !sp.W2[i]) return KB_ERR_ARG;
+        if (!aligned16(sp.A2[i]) || !aligned16(sp.W2[i]) || (sp.lda2[i] & 7) || (sp.ldw2[i] & 7)) return KB_ERR_ALIGN;
+        if ((sp.K2[i] % 8) || sp.lda2[i] < sp.K2[i] || sp.ldw2[i] < sp.K2[i]) return KB_ERR_SHAPE;
+    }
     if (M == 0) return KB_OK;
     DeviceState* st;
     int rc;
@@ -637,6 +656,10 @@ int linear16_segments(void* const* C, int ldc, const void* A, int lda, const voi
         if ((rc = make_tmap_mat(&maps.w[i], W[i], N, K, ldw)) || (rc = make_tmap_out(&maps.c[i], C[i], M, N, ldc, c32, epi == KB_EPI_HEADS16))) return rc;
         p.head_w[i] = static_cast<const __nv_bfloat16*>(head_w[i]);
         p.rope_on[i] = rope_on[i] ? 1 : 0;
+        if (sp.K2 && sp.K2[i] > 0) {
+            p.K2[i] = sp.K2[i];
+            if ((rc = make_tmap_mat(&maps.a2[i], sp.A2[i], M, sp.K2[i], sp.lda2[i])) || (rc = make_tmap_mat(&maps.w2[i], sp.W2[i], N, sp.K2[i], sp.ldw2[i]))) return rc;
+        }
     }
     p.C = C[0]; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
     p.gate = gate;
@@ -673,6 +696,42 @@ int kb_linear16_qkv(void* const* C3, int ldc, const void* A, int lda, const void
     if (!C3 || !W3 || !head_w3 || !rope_on3) return KB_ERR_ARG;
     return linear16_segments(C3, ldc, A, lda, W3, ldw, 3, M, N, K, KB_EPI_HEADS16, nullptr, head_w3, rope_on3, rope_cos, rope_sin, rope_T, eps,
                              static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear16_lora(void* C, int ldc, const void* A, int lda, const void* W, int ldw, const void* A2, int lda2, const void* W2,
+                     int ldw2, int K2, int M, int N, int K, int epi, const float* gate, const void* head_w_bf16,
+                     const float* rope_cos, const float* rope_sin, int rope_T, float eps, void* stream) {
+    if (epi != KB_EPI_HEADS16 && (head_w_bf16 || rope_cos)) return KB_ERR_ARG;
+    void* const cs[1] = {C};
+    const void* const ws[1] = {W};
+    const void* const hw[1] = {head_w_bf16};
+    const int rope_on[1] = {rope_cos != nullptr};
+    const void* const a2[1] = {A2};
+    const void* const w2[1] = {W2};
+    SecondProduct sp;
+    sp.A2 = a2; sp.W2 = w2; sp.K2 = &K2; sp.lda2 = &lda2; sp.ldw2 = &ldw2;
+    return linear16_segments(cs, ldc, A, lda, ws, ldw, 1, M, N, K, epi, gate, hw, rope_on, rope_cos, rope_sin, rope_T, eps,
+                             static_cast<cudaStream_t>(stream), sp);
+}
+
+int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const void* const* W3, int ldw, const void* const* A2_3,
+                         const int* lda2_3, const void* const* W2_3, const int* ldw2_3, const int* K2_3, int M, int N, int K,
+                         const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
+                         float eps, void* stream) {
+    if (!C3 || !W3 || !head_w3 || !rope_on3 || !K2_3) return KB_ERR_ARG;
+    SecondProduct sp;
+    sp.A2 = A2_3; sp.W2 = W2_3; sp.K2 = K2_3; sp.lda2 = lda2_3; sp.ldw2 = ldw2_3;
+    return linear16_segments(C3, ldc, A, lda, W3, ldw, 3, M, N, K, KB_EPI_HEADS16, nullptr, head_w3, rope_on3, rope_cos, rope_sin, rope_T, eps,
+                             static_cast<cudaStream_t>(stream), sp);
+}
+
+int kb_lora_pack(void* dst_f16, int ld, int col0, const void* src_bf16, int rows, int cols, float scale, void* stream) {
+    if (!dst_f16 || !src_bf16 || rows < 0 || cols < 0 || col0 < 0 || ld < col0 + cols) return KB_ERR_ARG;
+    const size_t n = (size_t)rows * cols;
+    if (!n) return KB_OK;
+    lora_pack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half*>(dst_f16), ld, col0, static_cast<const __nv_bfloat16*>(src_bf16), rows, cols, scale);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 int kb_status(unsigned* status_bits) {

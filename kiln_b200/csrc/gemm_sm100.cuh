@@ -47,6 +47,10 @@ struct GemmParams {
     void* C;
     int ldc;
     int M, N, K;
+    // Second product (LoRA side path, engine/src/tcgemm16.cuh:26-28): the accumulator of segment s also takes
+    // A2_s[M, K2_s] * W2_s[N, K2_s]^T, as further k steps after the first product's, so every epilogue sees the sum.
+    // K2 = 0: none. A last partial k step reads zeros past column K2 (the tensor maps fill out-of-range elements).
+    int K2[3];
     int tiles_m, tiles_n;          // in tiles of the launched shape (256x256 for PAIR, 128x128 otherwise)
     // Up to three weight matrices [N, K] share one launch (the q, k, v projections of one activation): column tile tn
     // belongs to segment tn / tiles_n_seg, which has its own W and C tensor maps and its own head epilogue settings.
@@ -64,6 +68,8 @@ struct GemmParams {
 struct alignas(64) GemmMaps {
     CUtensorMap w[3];              // per segment: the weight matrix, box 64 columns x 128 rows
     CUtensorMap c[3];              // per segment: the output, box as the epilogue stores it
+    CUtensorMap a2[3];             // per segment: left operand [M, K2] of the second product (unused when K2 = 0)
+    CUtensorMap w2[3];             // per segment: right operand [N, K2] of the second product
 };
 
 enum { GBAR_FULL = 0, GBAR_EMPTY = G_STAGES, GBAR_ACC_FULL = 2 * G_STAGES, GBAR_ACC_EMPTY = 2 * G_STAGES + 2, GBAR_COUNT = 2 * G_STAGES + 4 };
@@ -77,6 +83,15 @@ __device__ __forceinline__ void gemm_tile(int w, const GemmParams& p, int& tm, i
     const int first = (w / per_group) * G_GROUP_M, gsz = min(p.tiles_m - first, G_GROUP_M), in_g = w % per_group;
     tm = first + in_g % gsz;
     tn = in_g / gsz;
+}
+
+// dst[r * ld + col0 + c] = fp16(scale * src[r, c]) for a bf16 LoRA matrix [rows, cols]: how the stacked operands of the
+// second product are laid out, with the LoRA's scale folded into its up-projection (engine/src/kernels.cu:548-554)
+__global__ void lora_pack_kernel(__half* dst, int ld, int col0, const __nv_bfloat16* src, int rows, int cols, float scale) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols) return;
+    const int r = (int)(i / cols), c = (int)(i % cols);
+    dst[(size_t)r * ld + col0 + c] = __float2half_rn(scale * __bfloat162float(src[i]));
 }
 
 template <int EPI, bool PAIR>
@@ -105,7 +120,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                  // 0 issues the MMAs
     const int group = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int n_groups = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-    const int n_tiles = p.tiles_m * p.tiles_n, ksteps = p.K / GB_K;
+    const int n_tiles = p.tiles_m * p.tiles_n, ksteps1 = p.K / GB_K;
 
     if (tid == 0) {
         for (int i = 0; i < GBAR_COUNT; i++) mbar_init(bar(i), (i >= GBAR_ACC_EMPTY) ? (PAIR ? 2u : 1u) * G_EPI_WARPS : 1u);   // acc_empty: one arrival per epilogue warp of the group
@@ -331,14 +346,14 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && nrow > 0) {
-                        const int x = n0 + ch * CW, y = m0 + quarter * 32;
+                    const int x = n0 + ch * CW, y = m0 + quarter * 32;
+                    if (lane == 0 && nrow > 0 && x < p.N) {                   // a narrow last column tile stores only the boxes that begin inside it
                         if constexpr (EPI == EPI_RESID) {
                             tma_reduce_add_3d(&maps.c[seg], smem_u32(my_stage), x, y, 0);
                             tma_reduce_add_3d(&maps.c[seg], smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
                         } else {
                             tma_store_3d(&maps.c[seg], smem_u32(my_stage), x, y, 0);
-                            tma_store_3d(&maps.c[seg], smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
+                            if (x + CW / 2 < p.N) tma_store_3d(&maps.c[seg], smem_u32(my_stage) + 4096, x + CW / 2, y, 0);
                         }
                         tma_store_commit();
                     }
@@ -361,6 +376,9 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
                 ++use[buf];
                 if (!good) break;
                 tc_fence_after();
+                int tm, tn;
+                gemm_tile(w, p, tm, tn);
+                const int ksteps = ksteps1 + (p.K2[tn / p.tiles_n_seg] + GB_K - 1) / GB_K;
                 for (int ks = 0; ks < ksteps && good; ++ks, ++ring) {
                     const uint32_t st = ring % G_STAGES;
                     good = mbar_wait(bar(GBAR_FULL + st), (ring / G_STAGES) & 1u, abort_flag);
@@ -392,9 +410,13 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
                 int tm, tn;
                 gemm_tile(w, p, tm, tn);
                 const int seg = tn / p.tiles_n_seg;
-                const CUtensorMap* const tmW = &maps.w[seg];
                 const int m0 = tm * TILE_M + (int)rank * GB_M, wrow0 = (tn - seg * p.tiles_n_seg) * BN + (int)rank * 128;
+                const int ksteps = ksteps1 + (p.K2[seg] + GB_K - 1) / GB_K;
                 for (int ks = 0; ks < ksteps && good; ++ks, ++ring) {
+                    const bool second = ks >= ksteps1;                    // the k steps of the second product follow the first's
+                    const CUtensorMap* const tmL = second ? &maps.a2[seg] : &tmA;
+                    const CUtensorMap* const tmW = second ? &maps.w2[seg] : &maps.w[seg];
+                    const int k0 = (second ? ks - ksteps1 : ks) * GB_K;
                     const uint32_t st = ring % G_STAGES;
                     good = mbar_wait(bar(GBAR_EMPTY + st), ((ring / G_STAGES) & 1u) ^ 1u, abort_flag);
                     if (!good) break;
@@ -403,12 +425,12 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
                         // both CTAs' bytes complete on the issuing CTA's barrier
                         if (rank == 0) mbar_expect_tx(bar(GBAR_FULL + st), 2 * G_STAGE_BYTES);
                         const uint32_t fb = mapa_u32(bar(GBAR_FULL + st), 0);
-                        tma_load_3d_pair(a_s, &tmA, fb, ks * GB_K, m0, 0);
-                        tma_load_3d_pair(a_s + GB_M * GB_K * 2, tmW, fb, ks * GB_K, wrow0, 0);
+                        tma_load_3d_pair(a_s, tmL, fb, k0, m0, 0);
+                        tma_load_3d_pair(a_s + GB_M * GB_K * 2, tmW, fb, k0, wrow0, 0);
                     } else {
                         mbar_expect_tx(bar(GBAR_FULL + st), G_STAGE_BYTES);
-                        tma_load_3d(a_s, &tmA, bar(GBAR_FULL + st), ks * GB_K, m0, 0);
-                        tma_load_3d(a_s + GB_M * GB_K * 2, tmW, bar(GBAR_FULL + st), ks * GB_K, wrow0, 0);
+                        tma_load_3d(a_s, tmL, bar(GBAR_FULL + st), k0, m0, 0);
+                        tma_load_3d(a_s + GB_M * GB_K * 2, tmW, bar(GBAR_FULL + st), k0, wrow0, 0);
                     }
                 }
             }

@@ -80,8 +80,43 @@ void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16
           "nag_attention16");
 }
 
+void pack_lora(__half* a_cat, __half* b_cat, int out, int in, const LoraAdd16* adds, int n) {
+    const int rank = lora_rank_padded(adds, n);
+    if (cudaMemsetAsync(a_cat, 0, (size_t)rank * in * 2, g_ctx.stream) != cudaSuccess ||
+        cudaMemsetAsync(b_cat, 0, (size_t)out * rank * 2, g_ctx.stream) != cudaSuccess)
+        throw std::runtime_error("pack_lora: clearing the stacked operands failed");
+    int o = 0;
+    for (int i = 0; i < n; i++) {                                                   // engine/src/kernels.cu:584-590
+        check(kb_lora_pack(a_cat + (size_t)o * in, in, 0, adds[i].A, adds[i].r, in, 1.f, g_ctx.stream), "pack_lora(A)");
+        check(kb_lora_pack(b_cat, rank, o, adds[i].B, out, adds[i].r, adds[i].scale, g_ctx.stream), "pack_lora(B)");
+        o += adds[i].r;
+    }
+}
+
+namespace {
+bool has_lora(const Weight16& W) { return W.lora && W.lora->rank > 0; }
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+// t = x16 . a_cat^T (fp16 [T, rank]) at byte offset `at` of the workspace: engine/src/kernels.cu:591-595
+__half* lora_down(const __half* x16, int T, const Weight16& W, size_t at) {
+    const size_t need = at + (size_t)T * W.lora->rank * 2;
+    if (!g_ctx.workspace || g_ctx.workspace_bytes < need) throw std::runtime_error("linear16: the workspace is too small for the LoRA product");
+    __half* t = reinterpret_cast<__half*>(static_cast<char*>(g_ctx.workspace) + at);
+    check(kb_linear16(t, W.lora->rank, x16, W.cols, W.lora->a_cat, W.cols, T, W.lora->rank, W.cols, KB_EPI_F16, nullptr, nullptr, nullptr,
+                      nullptr, 0, 0.f, g_ctx.stream),
+          "linear16(lora down-projection)");
+    return t;
+}
+}  // namespace
+
 void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi16 epi, const float* gate) {
     if (W.rows % 128 || W.cols % 64) throw std::runtime_error("linear16: the weight is not tensor-core eligible");   // engine/src/kernels.cu:560
+    if (has_lora(W)) {
+        const __half* t = lora_down(x16, T, W, 0);
+        check(kb_linear16_lora(y, ldy, x16, W.cols, W.p, W.cols, t, W.lora->rank, W.lora->b_cat, W.lora->rank, W.lora->rank, T, W.rows,
+                               W.cols, (int)epi, gate, nullptr, nullptr, nullptr, 0, 0.f, g_ctx.stream),
+              "linear16");
+        return;
+    }
     check(kb_linear16(y, ldy, x16, W.cols, W.p, W.cols, T, W.rows, W.cols, (int)epi, gate, nullptr, nullptr, nullptr, 0, 0.f, g_ctx.stream),
           "linear16");
 }
@@ -89,6 +124,13 @@ void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi
 void linear16_heads(__half* y, int ldy, const __half* x16, int T, const Weight16& W, const uint16_t* norm_w_bf16, const float* rope_cos,
                     const float* rope_sin, int rope_T, float eps) {
     if (W.rows % 128 || W.cols % 64) throw std::runtime_error("linear16: the weight is not tensor-core eligible");
+    if (has_lora(W)) {
+        const __half* t = lora_down(x16, T, W, 0);
+        check(kb_linear16_lora(y, ldy, x16, W.cols, W.p, W.cols, t, W.lora->rank, W.lora->b_cat, W.lora->rank, W.lora->rank, T, W.rows,
+                               W.cols, KB_EPI_HEADS16, nullptr, norm_w_bf16, rope_cos, rope_sin, rope_T, eps, g_ctx.stream),
+              "linear16_heads");
+        return;
+    }
     check(kb_linear16(y, ldy, x16, W.cols, W.p, W.cols, T, W.rows, W.cols, KB_EPI_HEADS16, nullptr, norm_w_bf16, rope_cos, rope_sin, rope_T,
                       eps, g_ctx.stream),
           "linear16_heads");
@@ -103,6 +145,24 @@ void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, i
     const void* const W3[3] = {Wq.p, Wk.p, Wv.p};
     const void* const hw3[3] = {qn_w_bf16, kn_w_bf16, nullptr};
     const int rope3[3] = {rope_cos != nullptr, rope_cos != nullptr, 0};
+    const Weight16* const Ws[3] = {&Wq, &Wk, &Wv};
+    if (has_lora(Wq) || has_lora(Wk) || has_lora(Wv)) {
+        const void* A2[3] = {nullptr, nullptr, nullptr};
+        const void* W2[3] = {nullptr, nullptr, nullptr};
+        int K2[3] = {0, 0, 0}, ld2[3] = {0, 0, 0};
+        size_t at = 0;
+        for (int i = 0; i < 3; i++) {
+            if (!has_lora(*Ws[i])) continue;
+            A2[i] = lora_down(x16, T, *Ws[i], at);
+            W2[i] = Ws[i]->lora->b_cat;
+            K2[i] = ld2[i] = Ws[i]->lora->rank;
+            at = align256(at + (size_t)T * K2[i] * 2);
+        }
+        check(kb_linear16_qkv_lora(C3, ldy, x16, Wq.cols, W3, Wq.cols, A2, ld2, W2, ld2, K2, T, Wq.rows, Wq.cols, hw3, rope3, rope_cos,
+                                   rope_sin, rope_T, eps, g_ctx.stream),
+              "linear16_qkv");
+        return;
+    }
     check(kb_linear16_qkv(C3, ldy, x16, Wq.cols, W3, Wq.cols, T, Wq.rows, Wq.cols, hw3, rope3, rope_cos, rope_sin, rope_T, eps, g_ctx.stream),
           "linear16_qkv");
 }
@@ -179,6 +239,45 @@ int kbh_linear16_qkv(void* q, void* k, void* v, int ldy, const void* x16, int T,
         kiln_b200::Weight16 W[3];
         const void* ws[3] = {a.wq, a.wk, a.wv};
         for (int i = 0; i < 3; i++) { W[i].p = (const __half*)ws[i]; W[i].rows = a.rows; W[i].cols = a.cols; }
+        kiln_b200::linear16_qkv((__half*)a.q, (__half*)a.k, (__half*)a.v, a.ldy, (const __half*)a.x, a.T, W[0], W[1], W[2], a.qw, a.kw, a.c, a.s,
+                                a.rope_T, a.eps);
+    }, &a);
+}
+// linear16 on a weight with two unmerged LoRAs (r2 = 0: one): packs them into the caller's a_cat / b_cat, then runs the layer
+struct LL { void* y; int ldy; const void* x; int T; const void* w; int rows, cols, epi; const float* gate; kiln_b200::LoraAdd16 adds[2]; int n_adds; void *a_cat, *b_cat; };
+int kbh_linear16_lora(void* y, int ldy, const void* x16, int T, const void* w16, int rows, int cols, int epi, const float* gate,
+                      const uint16_t* A1, int r1, const uint16_t* B1, float s1, const uint16_t* A2, int r2, const uint16_t* B2, float s2,
+                      void* a_cat, void* b_cat, char* err, int n) {
+    LL a{y, ldy, x16, T, w16, rows, cols, epi, gate, {{A1, r1, B1, s1}, {A2, r2, B2, s2}}, r2 > 0 ? 2 : 1, a_cat, b_cat};
+    return guard(err, n, [](void* p) {
+        LL& a = *(LL*)p;
+        kiln_b200::Lora16 L; L.a_cat = (const __half*)a.a_cat; L.b_cat = (const __half*)a.b_cat; L.rank = kiln_b200::lora_rank_padded(a.adds, a.n_adds);
+        kiln_b200::pack_lora((__half*)a.a_cat, (__half*)a.b_cat, a.rows, a.cols, a.adds, a.n_adds);
+        kiln_b200::Weight16 W; W.p = (const __half*)a.w; W.rows = a.rows; W.cols = a.cols; W.lora = &L;
+        kiln_b200::linear16(a.y, a.ldy, (const __half*)a.x, a.T, W, (kiln_b200::Epi16)a.epi, a.gate);
+    }, &a);
+}
+// linear16_qkv with one LoRA on the q and one on the v projection (already packed by kbh_pack_lora)
+struct LQL { LQ b; const void *aq, *bq; int rq; const void *av, *bv; int rv; };
+int kbh_pack_lora(void* a_cat, void* b_cat, int out, int in, const uint16_t* A, int r, const uint16_t* B, float scale, char* err, int n) {
+    struct PL { void *a, *b; int out, in; kiln_b200::LoraAdd16 add; } a{a_cat, b_cat, out, in, {A, r, B, scale}};
+    return guard(err, n, [](void* p) { PL& a = *(PL*)p; kiln_b200::pack_lora((__half*)a.a, (__half*)a.b, a.out, a.in, &a.add, 1); }, &a);
+}
+int kbh_linear16_qkv_lora(void* q, void* k, void* v, int ldy, const void* x16, int T, const void* wq, const void* wk, const void* wv, int rows,
+                          int cols, const uint16_t* qn_w, const uint16_t* kn_w, const float* c, const float* s, int rope_T, float eps,
+                          const void* a_cat_q, const void* b_cat_q, int rank_q, const void* a_cat_v, const void* b_cat_v, int rank_v,
+                          char* err, int n) {
+    LQL a{{q, k, v, ldy, x16, T, wq, wk, wv, rows, cols, qn_w, kn_w, c, s, rope_T, eps}, a_cat_q, b_cat_q, rank_q, a_cat_v, b_cat_v, rank_v};
+    return guard(err, n, [](void* p) {
+        LQL& l = *(LQL*)p;
+        LQ& a = l.b;
+        kiln_b200::Lora16 Lq, Lv;
+        Lq.a_cat = (const __half*)l.aq; Lq.b_cat = (const __half*)l.bq; Lq.rank = l.rq;
+        Lv.a_cat = (const __half*)l.av; Lv.b_cat = (const __half*)l.bv; Lv.rank = l.rv;
+        kiln_b200::Weight16 W[3];
+        const void* ws[3] = {a.wq, a.wk, a.wv};
+        for (int i = 0; i < 3; i++) { W[i].p = (const __half*)ws[i]; W[i].rows = a.rows; W[i].cols = a.cols; }
+        W[0].lora = &Lq; W[2].lora = &Lv;
         kiln_b200::linear16_qkv((__half*)a.q, (__half*)a.k, (__half*)a.v, a.ldy, (const __half*)a.x, a.T, W[0], W[1], W[2], a.qw, a.kw, a.c, a.s,
                                 a.rope_T, a.eps);
     }, &a);

@@ -5,7 +5,7 @@
 //   attention16()  engine/src/gpu.h:155-156, engine/src/kernels.cu:868-873
 //   rmsnorm()      engine/src/gpu.h:133,     engine/src/kernels.cu:668-673   (rows of 128: the per-head Q/K norm)
 //   rope_half()    engine/src/gpu.h:145,     engine/src/kernels.cu:773-777
-//   linear16()     engine/src/gpu.h (Epi16, linear16), engine/src/kernels.cu:559-609   (without the LoRA side product)
+//   linear16()     engine/src/gpu.h (Epi16, linear16), engine/src/kernels.cu:559-609   (LoRAs unmerged, as a second product)
 //   nag_combine is the k_nag launch of engine/src/dit.cu:486 (fp16 rows) / :524 (fp32 rows)
 //
 // Like the reference ops they run on one stream, take device pointers the caller owns, and throw
@@ -64,9 +64,26 @@ void nag_attention16(__half* out, int ldo, const float* q, int ldq, const uint16
 // f16 set; a bf16 weight is converted by the caller once, as the reference does into G.wbuf). Epilogues as the reference's
 // Epi16 (engine/src/kernels.cu:597-603); y is fp32 for F32 / Resid and fp16 for F16 / Gelu16.
 enum class Epi16 { F32 = 0, F16 = 1, Gelu16 = 2, Resid = 3 };
+// The LoRAs of one weight, stacked and converted ONCE (pack_lora below). The reference's linear16 rebuilds these two
+// matrices from the bf16 LoRA tensors on every call (engine/src/kernels.cu:578-590); they depend only on the weights.
+struct Lora16 {
+    const __half* a_cat = nullptr;   // [rank, in]  the down-projections, one under the other
+    const __half* b_cat = nullptr;   // [out, rank] the up-projections side by side, each times its LoRA's scale
+    int rank = 0;                    // stacked rank padded to a multiple of 8 with zero rows / columns
+};
+struct LoraAdd16 {                   // one LoRA as the reference holds it (LoraAdd, engine/src/gpu.h:37), bf16 on the device
+    const uint16_t* A; int r;        // [r, in]
+    const uint16_t* B;               // [out, r]
+    float scale;
+};
+inline int lora_rank_padded(const LoraAdd16* adds, int n) { int r = 0; for (int i = 0; i < n; i++) r += adds[i].r; return (r + 7) / 8 * 8; }
+// Fills a_cat [rank, in] and b_cat [out, rank] (device buffers of the caller, rank = lora_rank_padded) on the context's stream.
+void pack_lora(__half* a_cat, __half* b_cat, int out, int in, const LoraAdd16* adds, int n);
 struct Weight16 {
     const __half* p = nullptr;
     int rows = 0, cols = 0;          // out, in
+    const Lora16* lora = nullptr;    // null: none. With LoRAs a call first forms t = x16 . a_cat^T ([T, rank] fp16, at the start
+                                     // of the context's workspace) and the GEMM adds t . b_cat^T before its epilogue
 };
 void linear16(void* y, int ldy, const __half* x16, int T, const Weight16& W, Epi16 epi, const float* gate = nullptr);
 // linear16 + rmsnorm + rope_half of engine/src/dit.cu:461-468 in one launch, fp16 out: what attention consumes directly

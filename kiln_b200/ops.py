@@ -49,6 +49,14 @@ def lib():
         L.kb_qk_prep.argtypes = [vp, i, i, vp, i, i, i, i, i, vp, f, vp, vp, vp]
         L.kb_linear16.restype = i
         L.kb_linear16.argtypes = [vp, i, vp, i, vp, i, i, i, i, i, vp, vp, vp, vp, i, f, vp]
+        L.kb_linear16_lora.restype = i
+        L.kb_linear16_lora.argtypes = [vp, i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, vp, vp, vp, vp, i, f, vp]
+        pi = ctypes.POINTER(i)
+        pvp = ctypes.POINTER(vp)
+        L.kb_linear16_qkv_lora.restype = i
+        L.kb_linear16_qkv_lora.argtypes = [pvp, i, vp, i, pvp, i, pvp, pi, pvp, pi, pi, i, i, i, pvp, pi, vp, vp, i, f, vp]
+        L.kb_lora_pack.restype = i
+        L.kb_lora_pack.argtypes = [vp, i, i, vp, i, i, f, vp]
         L.kb_linear16_qkv.restype = i
         L.kb_linear16_qkv.argtypes = [ctypes.POINTER(vp), i, vp, i, ctypes.POINTER(vp), i, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), vp, vp, i, f, vp]
         L.kb_status.restype = i
@@ -210,22 +218,39 @@ def qk_prep(out, x, rows, H, T, w=None, rope_cos=None, rope_sin=None, eps=1e-6):
 EPI_F32, EPI_F16, EPI_GELU16, EPI_RESID, EPI_HEADS16 = 0, 1, 2, 3, 4
 
 
-def linear16(C, A, W, epi, gate=None, head_w=None, rope_cos=None, rope_sin=None, eps=1e-6):
+def linear16(C, A, W, epi, gate=None, head_w=None, rope_cos=None, rope_sin=None, eps=1e-6, lora=None):
     """C = epilogue(A @ W.T): A [M, K] and W [N, K] fp16, fp32 accumulation (engine: linear16, engine/src/kernels.cu:559-609).
 
     EPI_F32 / EPI_RESID take an fp32 C, the others an fp16 C; EPI_HEADS16 applies the per-head RMSNorm (head_w bf16[128])
     and rotate-half RoPE (tables [T, 64]) to every 128-column head before the fp16 store.
+    lora = (A2 [M, K2], W2 [N, K2]) fp16 adds the second product A2 @ W2.T to the accumulator before the epilogue
+    (engine/src/kernels.cu:578-596).
     """
     M, K = A.shape
     N = W.shape[0]
     rope_T = rope_cos.shape[0] if rope_cos is not None else 0
+    if lora is not None:
+        A2, W2 = lora
+        _check(lib().kb_linear16_lora(_ptr(C), _ld(C), _ptr(A), _ld(A), _ptr(W), _ld(W), _ptr(A2), _ld(A2), _ptr(W2), _ld(W2), A2.shape[1],
+                                      M, N, K, epi, _ptr(gate), _ptr(head_w), _ptr(rope_cos), _ptr(rope_sin), rope_T, eps, _stream()),
+               "kb_linear16_lora")
+        return C
     _check(lib().kb_linear16(_ptr(C), _ld(C), _ptr(A), _ld(A), _ptr(W), _ld(W), M, N, K, epi, _ptr(gate), _ptr(head_w),
                              _ptr(rope_cos), _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16")
     return C
 
 
-def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, False), rope_cos=None, rope_sin=None, eps=1e-6):
-    """Three projections of one activation in one launch: Cs[i] = heads16(A @ Ws[i].T), fp16; see kb_linear16_qkv."""
+def lora_pack(dst, col0, src, scale=1.0):
+    """dst[:, col0:col0 + cols] = fp16(scale * src) for a bf16 LoRA matrix src [rows, cols] (k_lora_pack, engine/src/kernels.cu:548-554)."""
+    rows, cols = src.shape
+    _check(lib().kb_lora_pack(_ptr(dst), _ld(dst), col0, _ptr(src), rows, cols, float(scale), _stream()), "kb_lora_pack")
+    return dst
+
+
+def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, False), rope_cos=None, rope_sin=None, eps=1e-6, loras=None):
+    """Three projections of one activation in one launch: Cs[i] = heads16(A @ Ws[i].T), fp16; see kb_linear16_qkv.
+
+    loras = three entries, each None or (A2 [M, K2], W2 [N, K2]) fp16: the second product of that projection."""
     M, K = A.shape
     N = Ws[0].shape[0]
     vp3 = ctypes.c_void_p * 3
@@ -233,6 +258,16 @@ def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, Fal
     on = (ctypes.c_int * 3)(*[int(bool(r) and rope_cos is not None) for r in rope_on])
     rope_T = rope_cos.shape[0] if rope_cos is not None else 0
     assert all(_ld(c) == _ld(Cs[0]) for c in Cs) and all(_ld(w) == _ld(Ws[0]) for w in Ws)
+    if loras is not None:
+        i3 = ctypes.c_int * 3
+        a2 = [None if l is None else l[0] for l in loras]
+        w2 = [None if l is None else l[1] for l in loras]
+        _check(lib().kb_linear16_qkv_lora(arr(Cs), _ld(Cs[0]), _ptr(A), _ld(A), arr(Ws), _ld(Ws[0]), arr(a2),
+                                          i3(*[0 if t is None else _ld(t) for t in a2]), arr(w2),
+                                          i3(*[0 if t is None else _ld(t) for t in w2]), i3(*[0 if t is None else t.shape[1] for t in a2]),
+                                          M, N, K, arr(head_ws), on, _ptr(rope_cos), _ptr(rope_sin), rope_T, eps, _stream()),
+               "kb_linear16_qkv_lora")
+        return Cs
     _check(lib().kb_linear16_qkv(arr(Cs), _ld(Cs[0]), _ptr(A), _ld(A), arr(Ws), _ld(Ws[0]), M, N, K, arr(head_ws), on, _ptr(rope_cos),
                                  _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16_qkv")
     return Cs

@@ -115,12 +115,29 @@ def nag(zp, zn, s, tau, alpha, acc64=True):
     return a
 
 
-def linear16(x, w, epi=0, gate=None, c=None):
+def lora_operands(x, loras):
+    """The operands of the LoRA second product as linear16 composes them (reference: engine/src/kernels.cu:578-596).
+
+    x [M, in] fp16-exact; loras = [(A [r, in], B [out, r], scale), ...] with bf16-exact A and B. Returns
+    (t, b_cat): b_cat = [s1 B1 | s2 B2 | ...] rounded to fp16 ([out, R], k_lora_pack at kernels.cu:548-554) and
+    t = fp16(x . A_cat^T) ([M, R]; the reference's cublasGemmEx with an fp16 result and fp32 accumulation, summed in
+    double here). The reference pads R to its k tile with zero columns, which add nothing to the product."""
+    a_cat = np.concatenate([round16(_f32(a), 0) for a, _, _ in loras], axis=0)
+    b_cat = np.concatenate([round16(np.float32(s) * _f32(b), 0) for _, b, s in loras], axis=1)
+    return linear16(x, a_cat, 1), b_cat
+
+
+def linear16(x, w, epi=0, gate=None, c=None, lora=None):
     """epi(x [M, K] . w [N, K]^T) with fp16-exact inputs (reference: engine/src/tcgemm16.cuh:57-175).
 
     epi 0 fp32, 1 fp16-rounded, 2 fp16-rounded GELU, 3 c + gate * acc (c is the fp32 residual stream, copied).
+    lora = (t [M, K2], b_cat [N, K2]): the second product joins the accumulator before the epilogue
+    (tcgemm16.cuh:70-76), which is one product over the concatenated k range.
     """
     x, w = _f32(x), _f32(w)
+    if lora is not None:
+        x = np.concatenate([x, _f32(lora[0])], axis=1)
+        w = np.concatenate([w, _f32(lora[1])], axis=1)
     M, K = x.shape
     N = w.shape[0]
     out = np.zeros((M, N), np.float32) if c is None else _f32(c).copy()

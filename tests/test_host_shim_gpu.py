@@ -194,3 +194,70 @@ def test_ineligible_attention_falls_through_to_the_engines_exact_path(shim):
     assert shim.kbh_rmsnorm_only(P(dx), None, 40, ctypes.c_float(1e-6), err, 256) == 0, err.value
     torch.cuda.synchronize()
     np.testing.assert_allclose(dx.cpu().numpy(), oracle.rmsnorm(x, None, 1), rtol=1e-5, atol=2e-6)
+
+
+def _bf16(seed, rows, cols, amp):
+    a = oracle.round16(oracle.randn(seed, max(rows * cols, 16))[:rows * cols] * np.float32(amp), 1).reshape(rows, cols)
+    return a, dev(_bits(a).view(np.int16))
+
+
+def test_linear16_with_unmerged_loras(shim):
+    """linear16 on a weight that carries two LoRAs (engine/src/kernels.cu:578-596): the shim stacks and converts them, forms
+    t = x A_cat^T in the context's workspace and adds t B_cat^T inside the GEMM — every Epi16 against the oracle's restatement
+    of that sequence; then the q/k/v form with LoRAs on q and v."""
+    M, N, K, H = 150, 256, 128, 2
+    x = oracle.round16(oracle.randn(800, M * K), 0).reshape(M, K)
+    w = oracle.round16(oracle.randn(801, N * K) * np.float32(0.05), 0).reshape(N, K)
+    gate = oracle.randn(802, N)
+    resid = oracle.randn(803, M * N).reshape(M, N)
+    (a1, da1), (b1, db1) = _bf16(804, 12, K, 0.05), _bf16(805, N, 12, 0.05)      # rank 12 + 16 = 28 -> padded to 32
+    (a2, da2), (b2, db2) = _bf16(806, 16, K, 0.05), _bf16(807, N, 16, 0.05)
+    loras = [(a1, b1, 2.0), (a2, b2, -1.25)]
+    t_ref, b_ref = oracle.lora_operands(x, loras)
+    dx, dw = dev(x).half(), dev(w).half()
+    a_cat = torch.full((32, K), float("nan"), device="cuda", dtype=torch.float16)
+    b_cat = torch.full((N, 32), float("nan"), device="cuda", dtype=torch.float16)
+    err = ctypes.create_string_buffer(256)
+    f = ctypes.c_float
+    shim.kbh_linear16_lora.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, f, ctypes.c_void_p,
+                                       ctypes.c_int, ctypes.c_void_p, f, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+    for epi in range(4):
+        c32 = epi in (0, 3)
+        c = dev(resid).clone() if epi == 3 else torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32 if c32 else torch.float16)
+        assert shim.kbh_linear16_lora(P(c), N, P(dx), M, P(dw), N, K, epi, P(dev(gate)) if epi == 3 else None, P(da1), 12, P(db1), 2.0,
+                                      P(da2), 16, P(db2), -1.25, P(a_cat), P(b_cat), err, 256) == 0, err.value
+        torch.cuda.synchronize()
+        ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None, lora=(t_ref, b_ref))
+        # t is rounded to fp16 on both sides from sums in different orders: one fp16 step of t times |B| summed over the rank
+        assert np.abs(c.float().cpu().numpy() - ref).max() <= 2e-3 + 2.0 ** -10 * np.abs(ref).max(), epi
+    assert np.array_equal(b_cat[:, :28].float().cpu().numpy(), b_ref) and not b_cat[:, 28:].float().abs().sum().item()
+    assert not a_cat[28:].float().abs().sum().item()
+
+    # q/k/v in one launch, LoRA on q (rank 16) and v (rank 8), none on k
+    D = H * 128
+    ws = [oracle.round16(oracle.randn(810 + i, D * K) * np.float32(0.05), 0).reshape(D, K) for i in range(3)]
+    dws = [dev(a).half() for a in ws]
+    wq, wk = (oracle.round16(1.0 + 0.05 * oracle.randn(820 + i, 128), 1) for i in range(2))
+    cos, sin = oracle.cosmos_rope(10, 15)
+    (aq, daq), (bq, dbq) = _bf16(830, 16, K, 0.05), _bf16(831, D, 16, 0.05)
+    (av, dav), (bv, dbv) = _bf16(832, 8, K, 0.05), _bf16(833, D, 8, 0.05)
+    packs = []
+    for da, db, r, s in ((daq, dbq, 16, 1.5), (dav, dbv, 8, 3.0)):
+        ac = torch.empty((r, K), device="cuda", dtype=torch.float16)
+        bc = torch.empty((D, r), device="cuda", dtype=torch.float16)
+        assert shim.kbh_pack_lora(P(ac), P(bc), D, K, P(da), r, P(db), f(s), err, 256) == 0, err.value
+        packs.append((ac, bc, r))
+    ys = [torch.full((M, D), float("nan"), device="cuda", dtype=torch.float16) for _ in range(3)]
+    assert shim.kbh_linear16_qkv_lora(P(ys[0]), P(ys[1]), P(ys[2]), D, P(dx), M, P(dws[0]), P(dws[1]), P(dws[2]), D, K,
+                                      P(dev(_bits(wq).view(np.int16))), P(dev(_bits(wk).view(np.int16))), P(dev(cos)), P(dev(sin)), 150, f(1e-6),
+                                      P(packs[0][0]), P(packs[0][1]), 16, P(packs[1][0]), P(packs[1][1]), 8, err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    tq, bqc = oracle.lora_operands(x, [(aq, bq, 1.5)])
+    yq = oracle.rmsnorm(oracle.linear16(x, ws[0], 0, lora=(tq, bqc)), _bits(wq), H, 1e-6)
+    yq = oracle.round16(oracle.rope_half(yq, M, H, cos, sin), 0)
+    assert_close(ys[0].float().cpu().numpy(), yq, "shim linear16_qkv q with LoRA")
+    assert_close(ys[1].float().cpu().numpy(), oracle.linear_heads16(x, ws[1], H, _bits(wk), cos, sin), "shim linear16_qkv k")
+    tv, bvc = oracle.lora_operands(x, [(av, bv, 3.0)])
+    ref_v = oracle.linear16(x, ws[2], 1, lora=(tv, bvc))
+    assert np.abs(ys[2].float().cpu().numpy() - ref_v).max() <= 2e-3 + 2.0 ** -10 * np.abs(ref_v).max()

@@ -189,7 +189,7 @@ def test_argument_errors(kb):
 
     assert call() == 0
     assert call(M=0) == 0
-    assert call(N=64) == -3 and call(K=32) == -3 and call(lda=64) == -3          # KB_ERR_SHAPE
+    assert call(N=60) == -3 and call(N=64, epi=3) == -3 and call(N=64, epi=4) == -3 and call(K=32) == -3 and call(lda=64) == -3   # KB_ERR_SHAPE
     assert call(epi=5) == -1 and call(epi=0, gate=p(c)) == -1                     # KB_ERR_ARG
     assert call(epi=4, cos=p(c), sin=None) == -1 and call(epi=4, cos=p(c), sin=p(c), T=0) == -1
     assert call(lda=132) == -2 and call(ldc=130) == -2                            # KB_ERR_ALIGN
@@ -259,4 +259,147 @@ def test_qkv_argument_errors(kb):
     assert L.kb_linear16_qkv(*args(r=on)) == -1                                   # RoPE asked for without tables
     assert L.kb_linear16_qkv(*args(W=vp3(a.data_ptr(), None, a.data_ptr()))) == -1
     assert L.kb_linear16_qkv(*args(C=vp3(a.data_ptr(), a.data_ptr() + 2, a.data_ptr()))) == -2
+    assert kb.check_status() == 0
+
+
+def _lora_device_operands(kb, x16, loras, pad_to):
+    """A_cat / B_cat packed on the device by kb_lora_pack, the stacked rank padded with zero rows / columns to a multiple of
+    `pad_to`, and t = x . A_cat^T by the narrow fp16 epilogue."""
+    from kiln_b200 import ops
+    K, N = loras[0][0].shape[1], loras[0][1].shape[0]
+    R = sum(a.shape[0] for a, _, _ in loras)
+    Rp = (R + pad_to - 1) // pad_to * pad_to
+    ac = torch.zeros((Rp, K), device="cuda", dtype=torch.float16)
+    bc = torch.zeros((N, Rp), device="cuda", dtype=torch.float16)
+    o = 0
+    for a, b, s in loras:
+        ops.lora_pack(ac[o:], 0, dev(a).to(torch.bfloat16), 1.0)
+        ops.lora_pack(bc, o, dev(b).to(torch.bfloat16), s)
+        o += a.shape[0]
+    t = torch.full((x16.shape[0], Rp), float("nan"), device="cuda", dtype=torch.float16)
+    ops.linear16(t, x16, ac, ops.EPI_F16)
+    return t, bc, R
+
+
+@pytest.mark.parametrize("case", [c for c in ggen.GEMM_CASES if c[0] in ggen.LORA_CASES], ids=[c[0] for c in ggen.GEMM_CASES if c[0] in ggen.LORA_CASES])
+@pytest.mark.parametrize("pad_to", [8, 64], ids=["rank_as_is", "rank_padded_to_k_step"])
+def test_lora_second_product_vs_oracle_and_reference_golden(kb, gemm_golden, case, pad_to):
+    """The engine's unmerged LoRA path (linear16, engine/src/kernels.cu:578-596): operands packed, t = x A_cat^T, then
+    acc = x W^T + t B_cat^T under every epilogue — against the oracle and against the reference kernel's own outputs."""
+    from kiln_b200 import ops
+    name, M, N, K = case
+    x, w, gate, resid = ggen.gemm_inputs(case)
+    loras = ggen.lora_inputs(case)
+    t_ref, b_ref = oracle.lora_operands(x, loras)
+    dx = dev(x, "f16")
+    t, bc, R = _lora_device_operands(kb, dx, loras, pad_to)
+    assert kb.check_status() == 0
+    # packed operand: a rounding of a product of two exact values — bit-exact against the oracle and the reference's kernel
+    assert np.array_equal(bc[:, :R].float().cpu().numpy(), b_ref), "B_cat differs from the oracle"
+    assert np.array_equal(bc[:, :R].cpu().numpy().view(np.uint16), gemm_golden[f"{name}/lora_b"][:, :R].view(np.uint16)), "B_cat differs from k_lora_pack"
+    assert not t[:, R:].float().abs().sum().item(), "padding columns of t are not zero"
+    tn = t[:, :R].float().cpu().numpy()
+    _close(tn, t_ref, K, f"{name} t vs oracle", True)
+    _close(tn, gemm_golden[f"{name}/lora_t"][:, :R].astype(np.float32), K, f"{name} t vs the reference's product", True)
+    for ename, epi in ggen.EPIS.items():
+        c32 = epi in (ops.EPI_F32, ops.EPI_RESID)
+        full = torch.full((M, N + 8), float("nan"), device="cuda", dtype=torch.float32 if c32 else torch.float16)
+        c = full[:, :N]
+        if epi == ops.EPI_RESID:
+            c.copy_(dev(resid))
+        ops.linear16(c, dx, dev(w, "f16"), epi, gate=dev(gate) if epi == ops.EPI_RESID else None, lora=(t, bc))
+        assert kb.check_status() == 0
+        assert torch.isnan(full[:, N:].float()).all(), "wrote outside the output columns"
+        out = c.float().cpu().numpy()
+        # the oracle gets the t this library produced, so that only the second product itself is compared here
+        ref = oracle.linear16(x, w, epi, gate if epi == 3 else None, resid if epi == 3 else None, lora=(tn, b_ref))
+        _close(out, ref, K + R, f"{name}/lora_{ename} vs oracle", epi in (1, 2))
+        g = gemm_golden[f"{name}/lora_{ename}"].astype(np.float32)
+        tile_err = 2.0 ** -11 * np.sqrt((K + R) / 32) * 4.0
+        assert np.abs(out - g).max() <= tile_err + 2.0 ** -9 * np.abs(g).max(), f"{name}/lora_{ename} vs reference kernel: {np.abs(out - g).max():.3e}"
+
+
+@pytest.mark.parametrize("M,N,K,K2", [(300, 512, 128, 8), (300, 512, 128, 72), (70, 384, 64, 128), (4096, 2048, 2048, 32)],
+                         ids=["pair_tiles_rank8", "pair_tiles_partial_k_step", "single_tiles_two_k_steps", "dit_size_rank32"])
+def test_second_product_shapes(kb, M, N, K, K2):
+    """Second product of any width that is a multiple of 8, on both tile shapes, in a padded buffer (the columns past K2
+    hold NaN and must not be read): sampled rows against the oracle."""
+    from kiln_b200 import ops
+    x, w = seeded(400, M, K, "f16"), seeded(401, N, K, "f16", 1.0 / np.sqrt(K))
+    t, b = seeded(402, M, K2, "f16"), seeded(403, N, K2, "f16", 1.0 / np.sqrt(K2))
+    tf = torch.full((M, K2 + 8), float("nan"), device="cuda", dtype=torch.float16)
+    bf = torch.full((N, K2 + 16), float("nan"), device="cuda", dtype=torch.float16)
+    tf[:, :K2].copy_(dev(t, "f16")); bf[:, :K2].copy_(dev(b, "f16"))
+    c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32)
+    ops.linear16(c, dev(x, "f16"), dev(w, "f16"), ops.EPI_F32, lora=(tf[:, :K2], bf[:, :K2]))
+    assert kb.check_status() == 0
+    rows = sample_rows(M, 24)
+    ref = oracle.linear16(x[rows], w, 0, lora=(t[rows], b))
+    _close(c[torch.as_tensor(rows, device="cuda")].cpu().numpy(), ref, K + K2, f"{M}x{N}x{K}+{K2}", False)
+
+
+@pytest.mark.parametrize("M,H,K", [(300, 2, 128), (333, 3, 192)], ids=["pair_tiles", "single_tiles"])
+def test_qkv_lora_one_launch_equals_three_calls(kb, M, H, K):
+    """kb_linear16_qkv_lora with a different rank per projection (none on v) — bit-identical to three kb_linear16_lora /
+    kb_linear16 calls, and the head epilogue sees the LoRA-adjusted value (checked against the oracle on q)."""
+    from kiln_b200 import ops
+    N = H * 128
+    x = seeded(500, M, K, "f16")
+    dx = dev(x, "f16")
+    wn = [seeded(501 + i, N, K, "f16", 1.0 / np.sqrt(K)) for i in range(3)]
+    ws = [dev(a, "f16") for a in wn]
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(510, 128), 1)
+    nws = [dev(nw).to(torch.bfloat16), None]
+    cos_n, sin_n = oracle.cosmos_rope(20, 15)
+    cos, sin = dev(cos_n), dev(sin_n)
+    ranks = [16, 40, 0]
+    tn = [seeded(520 + i, M, r, "f16") if r else None for i, r in enumerate(ranks)]
+    bn = [seeded(530 + i, N, r, "f16", 0.2) if r else None for i, r in enumerate(ranks)]
+    loras = [None if r == 0 else (dev(tn[i], "f16"), dev(bn[i], "f16")) for i, r in enumerate(ranks)]
+    one = [torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16) for _ in range(3)]
+    ops.linear16_qkv(one, dx, ws, head_ws=(nws[0], nws[1], None), rope_on=(True, True, False), rope_cos=cos, rope_sin=sin, loras=loras)
+    three = [torch.empty((M, N), device="cuda", dtype=torch.float16) for _ in range(3)]
+    ops.linear16(three[0], dx, ws[0], ops.EPI_HEADS16, head_w=nws[0], rope_cos=cos, rope_sin=sin, lora=loras[0])
+    ops.linear16(three[1], dx, ws[1], ops.EPI_HEADS16, head_w=nws[1], rope_cos=cos, rope_sin=sin, lora=loras[1])
+    ops.linear16(three[2], dx, ws[2], ops.EPI_F16)
+    assert kb.check_status() == 0
+    for i in range(3):
+        assert torch.equal(one[i], three[i]), f"projection {i} differs from its own launch"
+    # q: rmsnorm and rope of (x W^T + t B^T), the order of engine/src/dit.cu:461-468 with a LoRA on the projection
+    y = oracle.linear16(x, wn[0], 0, lora=(tn[0], bn[0]))
+    bits = (nw.view(np.uint32) >> 16).astype(np.uint16)
+    y = oracle.rmsnorm(y, bits, H, 1e-6)
+    reps = (M + cos_n.shape[0] - 1) // cos_n.shape[0]                    # table shorter than M: rows wrap
+    y = oracle.round16(oracle.rope_half(y, M, H, np.tile(cos_n, (reps, 1))[:M], np.tile(sin_n, (reps, 1))[:M]), 0)
+    out = one[0].float().cpu().numpy()
+    assert np.all(np.abs(out - y) <= 2.0 ** -10 * np.abs(y) + 1e-4), f"q with LoRA: {np.abs(out - y).max():.3e}"
+
+
+@pytest.mark.parametrize("N", [8, 24, 72, 200], ids=lambda n: f"n{n}")
+def test_narrow_outputs_of_the_store_epilogues(kb, N):
+    """Output widths that are no multiple of the 128-column tile (the stacked rank of a LoRA down-projection): the three
+    store epilogues against the oracle, nothing written past column N."""
+    from kiln_b200 import ops
+    M, K = 333, 192
+    x, w = seeded(600, M, K, "f16"), seeded(601 + N, N, K, "f16", 1.0 / np.sqrt(K))
+    for epi in (ops.EPI_F32, ops.EPI_F16, ops.EPI_GELU16):
+        out = _run(kb, x, w, epi, ldc_pad=136)
+        _close(out, oracle.linear16(x, w, epi), K, f"N={N} epi {epi}", epi in (1, 2))
+
+
+def test_lora_argument_errors(kb):
+    import ctypes
+    L = kb.lib()
+    a = torch.zeros((128, 128), device="cuda", dtype=torch.float16)
+    c = torch.zeros((128, 128), device="cuda", dtype=torch.float32)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def call(A2=p(a), lda2=128, W2=p(a), ldw2=128, K2=32):
+        return L.kb_linear16_lora(p(c), 128, p(a), 128, p(a), 128, A2, lda2, W2, ldw2, K2, 128, 128, 128, 0, None, None, None, None, 0, 1e-6, None)
+
+    assert call() == 0 and call(K2=0, A2=None, W2=None) == 0
+    assert call(A2=None) == -1 and call(W2=None) == -1 and call(K2=-8) == -1      # KB_ERR_ARG
+    assert call(K2=12) == -3 and call(lda2=16) == -3                              # KB_ERR_SHAPE
+    assert call(lda2=132) == -2 and call(A2=ctypes.c_void_p(a.data_ptr() + 2)) == -2   # KB_ERR_ALIGN
+    assert L.kb_lora_pack(p(a), 128, 120, p(a), 4, 16, 1.0, None) == -1           # columns past the row stride
     assert kb.check_status() == 0
