@@ -247,6 +247,17 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
                          const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
                          float eps, void* stream);
 
+/* The cross-attention K/V of one context for one block, as the engine's per-generation cache makes them
+ * (Dit::cache_context, engine/src/dit.cu:217-234, and per block at dit.cu:407-413):
+ *   K = rmsnorm_per_head(ctx . Wk^T, kn_w),  V = ctx . Wv^T
+ * but emitted as fp16 [L, ld_out] and already normalised: what kb_attn_cross / kb_attn_nag read with dtype KB_F16
+ * and no staging pass, in half the engine's cache (which holds fp32 K and V and converts them in every attention call).
+ * ctx [L, K] (K = 1024 in the engine) fp32, fp16 or bf16 with row stride ld_ctx; Wk, Wv fp16 [N, ldw]; kn_w bf16[128]
+ * or NULL. One conversion launch when ctx is not fp16 (L * K * 2 bytes of workspace) and ONE GEMM launch for both
+ * projections. N and K multiples of 128. */
+int kb_cross_kv(void* k16, void* v16, int ld_out, const void* ctx, int ld_ctx, int ctx_dtype, int L, int N, int K, const void* Wk,
+                const void* Wv, int ldw, const void* kn_w_bf16, float eps, void* workspace, size_t workspace_bytes, void* stream);
+
 /* dst[r * ld + col0 + c] = fp16(scale * src[r, c]) for a bf16 matrix [rows, cols]: builds the stacked operands A_cat
  * (scale 1) and B_cat (the LoRA's scale) of the second product (k_lora_pack, engine/src/kernels.cu:548-554). */
 int kb_lora_pack(void* dst_f16, int ld, int col0, const void* src_bf16, int rows, int cols, float scale, void* stream);

@@ -725,6 +725,36 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
                              static_cast<cudaStream_t>(stream), sp);
 }
 
+int kb_cross_kv(void* k16, void* v16, int ld_out, const void* ctx, int ld_ctx, int ctx_dtype, int L, int N, int K, const void* Wk,
+                const void* Wv, int ldw, const void* kn_w_bf16, float eps, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!k16 || !v16 || !ctx || !Wk || !Wv || L < 0 || N <= 0 || K <= 0 || !valid_in_dtype(ctx_dtype)) return KB_ERR_ARG;
+    if ((N % 128) || (K % 128) || ld_ctx < K) return KB_ERR_SHAPE;
+    if (!aligned16(ctx) || (ld_ctx & (ctx_dtype == KB_F32 ? 3 : 7))) return KB_ERR_ALIGN;
+    if (L == 0) return KB_OK;
+    const void* x16 = ctx;
+    int ldx = ld_ctx;
+    if (ctx_dtype != KB_F16) {                                   // the context as fp16 rows in the workspace, as the GEMM reads it
+        const size_t need = (size_t)L * K * 2;
+        if (!workspace || workspace_bytes < need) return KB_ERR_WORKSPACE;
+        if (!aligned16(workspace)) return KB_ERR_ALIGN;
+        DeviceState* st;
+        int rc;
+        if ((rc = get_state(&st))) return rc;
+        PrepBatch pb;
+        pb.pp.H = K / 128; pb.pp.eps = eps;
+        pb.add(workspace, K, ctx, ld_ctx, L, L, nullptr, nullptr, nullptr);
+        if ((rc = launch_prep(st, pb, ctx_dtype, KB_F16, stream))) return rc;
+        x16 = workspace;
+        ldx = K;
+    }
+    void* const cs[2] = {k16, v16};
+    const void* const ws[2] = {Wk, Wv};
+    const void* const hw[2] = {kn_w_bf16, nullptr};
+    const int rope_on[2] = {0, 0};
+    return linear16_segments(cs, ld_out, x16, ldx, ws, ldw, 2, L, N, K, KB_EPI_HEADS16, nullptr, hw, rope_on, nullptr, nullptr, 0, eps, stream);
+}
+
 int kb_lora_pack(void* dst_f16, int ld, int col0, const void* src_bf16, int rows, int cols, float scale, void* stream) {
     if (!dst_f16 || !src_bf16 || rows < 0 || cols < 0 || col0 < 0 || ld < col0 + cols) return KB_ERR_ARG;
     const size_t n = (size_t)rows * cols;

@@ -167,6 +167,14 @@ void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, i
           "linear16_qkv");
 }
 
+void cross_kv16(__half* k16, __half* v16, int ldy, const float* ctx, int L, const Weight16& Wk, const Weight16& Wv, const uint16_t* kn_w_bf16,
+                float eps) {
+    if (Wk.rows != Wv.rows || Wk.cols != Wv.cols) throw std::runtime_error("cross_kv16: the two weights must share one shape");
+    check(kb_cross_kv(k16, v16, ldy, ctx, Wk.cols, KB_F32, L, Wk.rows, Wk.cols, Wk.p, Wv.p, Wk.cols, kn_w_bf16, eps, g_ctx.workspace,
+                      g_ctx.workspace_bytes, g_ctx.stream),
+          "cross_kv16");
+}
+
 }  // namespace kiln_b200
 
 // C trampolines so the shim can be exercised from the test-suite without a C++ test runner:
@@ -280,6 +288,17 @@ int kbh_linear16_qkv_lora(void* q, void* k, void* v, int ldy, const void* x16, i
         W[0].lora = &Lq; W[2].lora = &Lv;
         kiln_b200::linear16_qkv((__half*)a.q, (__half*)a.k, (__half*)a.v, a.ldy, (const __half*)a.x, a.T, W[0], W[1], W[2], a.qw, a.kw, a.c, a.s,
                                 a.rope_T, a.eps);
+    }, &a);
+}
+struct CK { void *k, *v; int ldy; const float* ctx; int L; const void *wk, *wv; int rows, cols; const uint16_t* kw; float eps; };
+int kbh_cross_kv16(void* k16, void* v16, int ldy, const float* ctx, int L, const void* wk, const void* wv, int rows, int cols, const uint16_t* kn_w,
+                   float eps, char* err, int n) {
+    CK a{k16, v16, ldy, ctx, L, wk, wv, rows, cols, kn_w, eps};
+    return guard(err, n, [](void* p) {
+        CK& a = *(CK*)p;
+        kiln_b200::Weight16 Wk, Wv;
+        Wk.p = (const __half*)a.wk; Wv.p = (const __half*)a.wv; Wk.rows = Wv.rows = a.rows; Wk.cols = Wv.cols = a.cols;
+        kiln_b200::cross_kv16((__half*)a.k, (__half*)a.v, a.ldy, a.ctx, a.L, Wk, Wv, a.kw, a.eps);
     }, &a);
 }
 // the exact-path hook: a stand-in "engine path" that only records that it was reached

@@ -96,4 +96,10 @@ void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, i
                   const Weight16& Wv, const uint16_t* qn_w_bf16, const uint16_t* kn_w_bf16, const float* rope_cos, const float* rope_sin,
                   int rope_T, float eps);
 
+// Cross-attention K and V of one context for one block (the body of Dit::cache_context's loop, engine/src/dit.cu:228-230:
+// linear + rmsnorm + linear), emitted fp16 and already normalised: attention16 / nag_attention16 then read them without the
+// per-call conversion, and the cache is half the size. ctx fp32 [L, Wk.cols]; k16, v16 [L, ldy]; kn_w bf16[128].
+void cross_kv16(__half* k16, __half* v16, int ldy, const float* ctx, int L, const Weight16& Wk, const Weight16& Wv, const uint16_t* kn_w_bf16,
+                float eps);
+
 }  // namespace kiln_b200

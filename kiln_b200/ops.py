@@ -57,6 +57,8 @@ def lib():
         L.kb_linear16_qkv_lora.argtypes = [pvp, i, vp, i, pvp, i, pvp, pi, pvp, pi, pi, i, i, i, pvp, pi, vp, vp, i, f, vp]
         L.kb_lora_pack.restype = i
         L.kb_lora_pack.argtypes = [vp, i, i, vp, i, i, f, vp]
+        L.kb_cross_kv.restype = i
+        L.kb_cross_kv.argtypes = [vp, vp, i, vp, i, i, i, i, i, vp, vp, i, vp, f, vp, ctypes.c_size_t, vp]
         L.kb_linear16_qkv.restype = i
         L.kb_linear16_qkv.argtypes = [ctypes.POINTER(vp), i, vp, i, ctypes.POINTER(vp), i, i, i, i, ctypes.POINTER(vp), ctypes.POINTER(i), vp, vp, i, f, vp]
         L.kb_status.restype = i
@@ -271,6 +273,19 @@ def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, Fal
     _check(lib().kb_linear16_qkv(arr(Cs), _ld(Cs[0]), _ptr(A), _ld(A), arr(Ws), _ld(Ws[0]), M, N, K, arr(head_ws), on, _ptr(rope_cos),
                                  _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16_qkv")
     return Cs
+
+
+def cross_kv(k16, v16, ctx, Wk, Wv, kn_w=None, eps=1e-6, workspace=None):
+    """fp16, already normalised cross-attention K and V of one context for one block: K = rmsnorm_per_head(ctx @ Wk.T),
+    V = ctx @ Wv.T (engine: Dit::cache_context, engine/src/dit.cu:217-234). ctx [L, K] fp32 / fp16 / bf16; Wk, Wv fp16 [N, K]."""
+    import torch
+    L, K = ctx.shape
+    N = Wk.shape[0]
+    if workspace is None and ctx.dtype != torch.float16:
+        workspace = torch.empty(max(L * K * 2, 16), dtype=torch.uint8, device=ctx.device)
+    _check(lib().kb_cross_kv(_ptr(k16), _ptr(v16), _ld(k16), _ptr(ctx), _ld(ctx), _dt(ctx), L, N, K, _ptr(Wk), _ptr(Wv), _ld(Wk), _ptr(kn_w), eps,
+                             _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream()), "kb_cross_kv")
+    return k16, v16
 
 
 def check_status():

@@ -261,3 +261,24 @@ def test_linear16_with_unmerged_loras(shim):
     tv, bvc = oracle.lora_operands(x, [(av, bv, 3.0)])
     ref_v = oracle.linear16(x, ws[2], 1, lora=(tv, bvc))
     assert np.abs(ys[2].float().cpu().numpy() - ref_v).max() <= 2e-3 + 2.0 ** -10 * np.abs(ref_v).max()
+
+
+def test_cross_kv16_then_nag_attention_on_the_cache(shim):
+    """cross_kv16 (the body of the engine's cache_context loop, engine/src/dit.cu:228-230) for a prompt and a NAG negative
+    context, against the oracle's linear + rmsnorm + linear."""
+    H, KD, L = 2, 1024, 77
+    D = H * 128
+    ctx = oracle.randn(900, L * KD).reshape(L, KD)
+    wk, wv = (oracle.round16(oracle.randn(901 + j, D * KD) * np.float32(1.0 / 32), 0).reshape(D, KD) for j in range(2))
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(903, 128), 1)
+    k16 = torch.full((L, D), float("nan"), device="cuda", dtype=torch.float16)
+    v16 = torch.full((L, D), float("nan"), device="cuda", dtype=torch.float16)
+    err = ctypes.create_string_buffer(256)
+    assert shim.kbh_cross_kv16(P(k16), P(v16), D, P(dev(ctx)), L, P(dev(wk).half()), P(dev(wv).half()), D, KD, P(dev(_bits(nw).view(np.int16))),
+                               ctypes.c_float(1e-6), err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    x16 = oracle.round16(ctx, 0)
+    k_ref = oracle.round16(oracle.rmsnorm(oracle.linear16(x16, wk, 0), _bits(nw), H, 1e-6), 0)
+    v_ref = oracle.linear16(x16, wv, 1)
+    assert np.all(np.abs(k16.float().cpu().numpy() - k_ref) <= 2.0 ** -10 * np.abs(k_ref) + 1e-4)
+    assert np.all(np.abs(v16.float().cpu().numpy() - v_ref) <= 2.0 ** -10 * np.abs(v_ref) + 1e-4)

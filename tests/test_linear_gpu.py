@@ -403,3 +403,37 @@ def test_lora_argument_errors(kb):
     assert call(lda2=132) == -2 and call(A2=ctypes.c_void_p(a.data_ptr() + 2)) == -2   # KB_ERR_ALIGN
     assert L.kb_lora_pack(p(a), 128, 120, p(a), 4, 16, 1.0, None) == -1           # columns past the row stride
     assert kb.check_status() == 0
+
+
+@pytest.mark.parametrize("L,src", [(26, "f32"), (77, "f32"), (512, "f32"), (300, "f16"), (40, "bf16")], ids=lambda v: str(v))
+def test_cross_kv_producer_feeds_cross_attention(kb, L, src):
+    """kb_cross_kv: K = rmsnorm(ctx Wk^T) and V = ctx Wv^T of a [L, 1024] context as fp16 in one GEMM launch — against the oracle's
+    restatement of Dit::cache_context (engine/src/dit.cu:228-230), then through kb_attn_cross against the oracle's attention on the
+    oracle's K and V (the engine's order: cache_context, then attention16 with npad zero keys, dit.cu:476-481)."""
+    from kiln_b200 import ops
+    H, KD = 3, 1024
+    N = H * 128
+    kind = {"f32": None, "f16": "f16", "bf16": "bf16"}[src]
+    ctx = oracle.randn(700 + L, L * KD).reshape(L, KD)
+    if kind:
+        ctx = oracle.round16(ctx, 0 if kind == "f16" else 1)
+    wk, wv = (seeded(710 + j, N, KD, "f16", 1.0 / np.sqrt(KD)) for j in range(2))
+    nw = oracle.round16(1.0 + 0.05 * oracle.randn(712, 128), 1)
+    bits = (nw.view(np.uint32) >> 16).astype(np.uint16)
+    k16 = torch.full((L, N + 8), float("nan"), device="cuda", dtype=torch.float16)
+    v16 = torch.full((L, N + 8), float("nan"), device="cuda", dtype=torch.float16)
+    ops.cross_kv(k16[:, :N], v16[:, :N], dev(ctx, kind), dev(wk, "f16"), dev(wv, "f16"), kn_w=dev(nw).to(torch.bfloat16))
+    assert kb.check_status() == 0
+    assert torch.isnan(k16[:, N:].float()).all() and torch.isnan(v16[:, N:].float()).all(), "wrote outside the output columns"
+    x16 = oracle.round16(ctx, 0)                                     # the GEMM reads the context as fp16
+    k_ref = oracle.round16(oracle.rmsnorm(oracle.linear16(x16, wk, 0), bits, H, 1e-6), 0)
+    v_ref = oracle.linear16(x16, wv, 1)
+    ko, vo = k16[:, :N].float().cpu().numpy(), v16[:, :N].float().cpu().numpy()
+    assert np.all(np.abs(ko - k_ref) <= 2.0 ** -10 * np.abs(k_ref) + 1e-4), f"K: {np.abs(ko - k_ref).max():.3e}"
+    assert np.all(np.abs(vo - v_ref) <= 2.0 ** -10 * np.abs(v_ref) + 1e-4), f"V: {np.abs(vo - v_ref).max():.3e}"
+    Tq, npad = 200, 512 - L if L < 512 else 0
+    q = seeded(720, Tq, N, "f16")
+    out = torch.empty((Tq, N), device="cuda", dtype=torch.float32)
+    kb.attn_cross(out, dev(q, "f16"), k16[:, :N], v16[:, :N], Tq, L, npad, H)
+    assert kb.check_status() == 0
+    assert_close(out.cpu().numpy(), oracle.attention(q, k_ref, v_ref, H, npad), f"cross-attention on produced K/V, L={L}")
