@@ -11,7 +11,7 @@ Every block has its own buffers (28 x 109 MB), so consecutive launches never fin
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --all-configs                     # one JSON line per benchmark configuration (1 GPU)
-    python bench.py --case self|cross|nag|prep|linear|block [--tokens T] [--batch B] [--ctx L] [--valid V] [--dtype f16|bf16]
+    python bench.py --case self|cross|nag|prep|linear|block|bwd [--tokens T] [--batch B] [--ctx L] [--valid V] [--dtype f16|bf16]
                     [--norm] [--reps R] [--warm W]    # one kernel family a few times: what the profiler captures run
 
 N > 1 (under torchrun): one image per GPU, no communication on the data path ("weak" scaling); the line then also carries
@@ -615,6 +615,8 @@ def run_case(a):
     assert kb.lib().kb_init() == 0
     if a.case in ("linear", "block"):
         return linear_cases(a)
+    if a.case == "bwd":
+        return bwd_case(a)
     dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
     T, B, H, L = a.tokens, a.batch, a.heads, a.ctx
     D = H * 128
@@ -677,6 +679,34 @@ def _timed_us(fn, warm, reps):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / reps * 1e3
+
+
+def bwd_case(a):
+    """Attention backward (kb_attn_bwd: pre-pass if needed, forward for the statistics, D reduction, dK/dV kernel, dQ kernel) at
+    --tokens queries against --tokens keys (self-attention, train.cu:344) or --ctx keys of which --valid are real (--valid > 0:
+    the trainer's cross-attention call, train.cu:334). Algorithmic flops: the reference's five products, 10 * Tq * Tk * 128 * H."""
+    import torch
+    import kiln_b200 as kb
+    T, H = a.tokens, a.heads
+    D = H * 128
+    cross = a.valid > 0
+    Tk, npad = (a.valid, a.ctx - a.valid) if cross else (T, 0)
+    dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[a.dtype]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    rn = lambda r: torch.randn(r, D, device="cuda", generator=g).to(dt)
+    q, k, v, do = rn(T), rn(Tk), rn(Tk), rn(T)
+    dq, dk, dv = torch.empty(T, D, device="cuda"), torch.empty(Tk, D, device="cuda"), torch.empty(Tk, D, device="cuda")
+    ws = torch.empty(kb.lib().kb_attn_bwd_workspace_bytes(1, T, Tk, H, kb.ops._dt(q)), dtype=torch.uint8, device="cuda")
+    fn = lambda: kb.attn_bwd(dq, dk, dv, q, k, v, do, 1, T, Tk, npad, H, workspace=ws)
+    us = _timed_us(fn, a.warm, a.reps)
+    assert kb.check_status() == 0
+    flop = 10.0 * T * Tk * 128 * H
+    print(f"case=bwd tokens={T} keys={Tk} npad={npad} heads={H} dtype={a.dtype}: {us:.1f} us/call (all launches), {flop / us / 1e6:.1f} TFLOP/s")
+    fwd = torch.empty(T, D, device="cuda", dtype=torch.float32)
+    ws2 = torch.empty(max(16, kb.workspace_bytes(T, Tk, H, q.dtype, False, False)), dtype=torch.uint8, device="cuda")
+    us_f = _timed_us(lambda: kb.attn_cross(fwd, q, k, v, T, Tk, npad, H, workspace=ws2), a.warm, a.reps)
+    print(f"  forward alone on the same operands: {us_f:.1f} us/call")
 
 
 def linear_cases(a):
@@ -757,7 +787,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--all-configs", action="store_true", help="one JSON line per benchmark configuration (1 GPU) instead of the benchmark line")
-    ap.add_argument("--case", default=None, choices=["self", "cross", "nag", "prep", "linear", "block"], help="run one kernel family a few times (for profilers)")
+    ap.add_argument("--case", default=None, choices=["self", "cross", "nag", "prep", "linear", "block", "bwd"], help="run one kernel family a few times (for profilers)")
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--epi", default="f16", choices=["f32", "f16", "gelu16", "resid", "heads16"])
@@ -766,7 +796,7 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--valid", type=int, default=0, help="cross: real keys of the padded context (0 = all)")
-    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "f32"])
     ap.add_argument("--norm", action="store_true", help="Q/K RMSNorm (+ RoPE for self) through the staging pre-pass")
     ap.add_argument("--cublas", action="store_true", help="linear: also time torch.matmul on the same operands")
     ap.add_argument("--reps", type=int, default=5)

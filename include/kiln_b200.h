@@ -247,6 +247,20 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
                          const void* const* head_w3, const int* rope_on3, const float* rope_cos, const float* rope_sin, int rope_T,
                          float eps, void* stream);
 
+/* Attention backward: dq [B*Tq, ld_dq], dk, dv [B*Tk, ld_*] (fp32, written) of out = softmax(q k^T / sqrt(128)) v per head,
+ * from q, k, v and dout (the gradient of out), all in `dtype`; npad zero keys of score 0 join the softmax as in the forward
+ * calls. Replaces the engine's exact backward attention_bwd (engine/src/train.cu:216-242 with k_softmax_pad, train.cu:103-121,
+ * and k_dsoftmax, train.cu:124-131; call sites train.cu:334 (cross-attention, npad) and train.cu:344 (self-attention)), which
+ * materialises the [heads, Tq, Tk] probabilities and their gradients in the arena: here they are recomputed tile by tile on
+ * the tensor cores (fp16 operands, fp32 accumulation; the engine's is fp32 throughout), nothing of size Tq x Tk is stored,
+ * and every output element is written once in a fixed order (bit-identical from run to run). Launches: staging pre-pass
+ * (unless dtype is KB_F16), the forward kernel (for the per-row softmax statistics and O), a reduction for
+ * sum_d dout * O, the dK/dV kernel and the dQ kernel. The workspace (kb_attn_bwd_workspace_bytes) is always required. */
+size_t kb_attn_bwd_workspace_bytes(int B, int Tq, int Tk, int H, int dtype);
+int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, const void* v, const void* dout, int B, int Tq, int Tk,
+                int npad, int H, int ld_q, int ld_k, int ld_v, int ld_do, int ld_dq, int ld_dk, int ld_dv, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream);
+
 /* The cross-attention K/V of one context for one block, as the engine's per-generation cache makes them
  * (Dit::cache_context, engine/src/dit.cu:217-234, and per block at dit.cu:407-413):
  *   K = rmsnorm_per_head(ctx . Wk^T, kn_w),  V = ctx . Wv^T

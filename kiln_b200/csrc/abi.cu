@@ -14,6 +14,7 @@
 #include "combine.cuh"
 #include "selfcheck.cuh"
 #include "gemm_sm100.cuh"
+#include "attn_bwd_sm100.cuh"
 
 namespace {
 
@@ -92,6 +93,8 @@ int init_device(DeviceState& st, int dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     int rc;
+    if ((rc = set_smem(attn_bwd_kernel<BWD_DKV>, BWD_SMEM))) return rc;
+    if ((rc = set_smem(attn_bwd_kernel<BWD_DQ>, BWD_SMEM))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>, ATTN_SMEM_PAIR))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>, ATTN_SMEM_PAIR))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>, ATTN_SMEM_PAIR))) return rc;
@@ -194,7 +197,7 @@ int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtyp
 
 template <int MODE, typename OutT>
 int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
-                  const CUtensorMap& tv1, const CUtensorMap& to, const AttnParams& p, int sm_count, cudaStream_t stream) {
+                  const CUtensorMap& tv1, const CUtensorMap& to, const PeerMaps& tp, const AttnParams& p, int sm_count, cudaStream_t stream) {
     // persistent kernel: one CTA per SM (its shared memory and TMEM fill an SM) walks the work items
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
@@ -211,7 +214,7 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, OutT>, tq, tk0, tv0, tk1, tv1, to, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, OutT>, tq, tk0, tv0, tk1, tv1, to, tp, p);
     return e == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
@@ -219,21 +222,28 @@ template <int MODE>
 int launch_attn(int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
                 const CUtensorMap& tv1, const AttnParams& p, int sm_count, cudaStream_t stream) {
     // 16-bit outputs of single-GPU calls leave through TMA stores: [B][Tq][H*128] view of `out`, box = 64 columns x 128 rows
+    // head-split runs: the same view of every GPU's gathered buffer, beginning at this GPU's first column there
     CUtensorMap to;
+    PeerMaps tp;
     memset(&to, 0, sizeof(to));
-    if (out_dtype != KB_F32 && p.n_peers == 0) {
+    memset(&tp, 0, sizeof(tp));
+    if (out_dtype != KB_F32) {
         const cuuint64_t dims[3] = {(cuuint64_t)p.H * 128, (cuuint64_t)p.Tq, (cuuint64_t)p.B};
         const cuuint64_t strides[2] = {(cuuint64_t)p.ldo * 2, (cuuint64_t)p.Tq * (cuuint64_t)p.ldo * 2};
         const cuuint32_t box[3] = {64, 128, 1};
         const cuuint32_t estr[3] = {1, 1, 1};
-        if (g_encode(&to, out_dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, p.out, dims, strides,
-                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return KB_ERR_CUDA;
+        const int n_maps = p.n_peers == 0 ? 1 : p.n_peers;
+        for (int i = 0; i < n_maps; i++) {
+            void* const base = p.n_peers == 0 ? p.out : static_cast<void*>(static_cast<char*>(p.out_peers[i]) + (size_t)p.col0 * 2);
+            if (g_encode(p.n_peers == 0 ? &to : &tp.m[i], out_dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                         base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return KB_ERR_CUDA;
+        }
     }
-    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
-    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
-    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
+    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
+    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
+    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
 }
 
 constexpr float SCALE_LOG2 = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
@@ -288,7 +298,7 @@ bool split_pays(int n_items, int nb, int sm_count) {
 int attn_pair(void* out, const void* q, const void* k, const void* v, const void* qn_w, const void* kn_w,
               const float* rope_cos, const float* rope_sin, int B, int Tq, int Tk, int npad, int H, int ld_q, int ld_k,
               int ld_v, int ld_o, int dtype, int out_dtype, float eps, void* workspace, size_t workspace_bytes,
-              cudaStream_t stream, const PeerSpec* peers = nullptr) {
+              cudaStream_t stream, const PeerSpec* peers = nullptr, float* stats = nullptr) {
     if (!valid_in_dtype(dtype)) return KB_ERR_ARG;
     if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || npad < 0) return KB_ERR_ARG;
     if (peers) {
@@ -329,6 +339,7 @@ int attn_pair(void* out, const void* q, const void* k, const void* v, const void
     p.n_items = ((Tq + 2 * BM - 1) / (2 * BM)) * H * B;
     p.scale_log2 = SCALE_LOG2;
     p.status = st->status;
+    p.stats = stats;
     // Balanced schedule: worth it when equal (item, key block) ranges per SM beat whole items per SM by more than the
     // cost of writing and merging the cut items' partial results (about two key blocks), and the workspace has room for
     // those partial results; otherwise every CTA takes whole items.
@@ -723,6 +734,81 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
     sp.A2 = A2_3; sp.W2 = W2_3; sp.K2 = K2_3; sp.lda2 = lda2_3; sp.ldw2 = ldw2_3;
     return linear16_segments(C3, ldc, A, lda, W3, ldw, 3, M, N, K, KB_EPI_HEADS16, nullptr, head_w3, rope_on3, rope_cos, rope_sin, rope_T, eps,
                              static_cast<cudaStream_t>(stream), sp);
+}
+
+// ------------------------------------------------------------------------------------------- attention backward
+namespace {
+size_t bwd_stats_bytes(int B, int Tq, int H) { return align256((size_t)B * H * ((Tq + 127) / 128) * 256 * sizeof(float)); }
+size_t bwd_fixed_bytes(int B, int Tq, int Tk, int H, int dtype) {
+    size_t n = bwd_stats_bytes(B, Tq, H) + align256((size_t)B * Tq * H * 128 * sizeof(float));             // statistics, O (fp32)
+    if (dtype != KB_F16) n += 2 * align256((size_t)B * Tq * H * 128 * 2) + 2 * align256((size_t)B * Tk * H * 128 * 2);   // fp16 Q, dO, K, V
+    return n;
+}
+}  // namespace
+
+size_t kb_attn_bwd_workspace_bytes(int B, int Tq, int Tk, int H, int dtype) {
+    if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || H > MAX_HEADS || !valid_in_dtype(dtype)) return 0;
+    // + what the forward pass inside wants for its balanced schedule (it runs on fp16 operands: no staging of its own)
+    return bwd_fixed_bytes(B, Tq, Tk, H, dtype) + kb_attn_workspace_bytes(B * Tq, B * Tk, 1, H, KB_F16, 0, 0);
+}
+
+int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, const void* v, const void* dout, int B, int Tq, int Tk,
+                int npad, int H, int ld_q, int ld_k, int ld_v, int ld_do, int ld_dq, int ld_dk, int ld_dv, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!dq || !dk || !dv || !q || !k || !v || !dout || !valid_in_dtype(dtype)) return KB_ERR_ARG;
+    if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || npad < 0) return KB_ERR_ARG;
+    if (H > MAX_HEADS) return KB_ERR_SHAPE;
+    int rc;
+    if ((rc = check_mat(q, ld_q, H, dtype)) || (rc = check_mat(k, ld_k, H, dtype)) || (rc = check_mat(v, ld_v, H, dtype)) ||
+        (rc = check_mat(dout, ld_do, H, dtype)) || (rc = check_out(dq, ld_dq, H, KB_F32)) || (rc = check_out(dk, ld_dk, H, KB_F32)) ||
+        (rc = check_out(dv, ld_dv, H, KB_F32)))
+        return rc;
+    if (!workspace || !aligned16(workspace)) return KB_ERR_WORKSPACE;
+    DeviceState* st;
+    if ((rc = get_state(&st))) return rc;
+    Stage sg{static_cast<char*>(workspace), workspace_bytes};
+    float* stats = static_cast<float*>(sg.take_bytes(bwd_stats_bytes(B, Tq, H)));
+    float* o32 = static_cast<float*>(sg.take_bytes((size_t)B * Tq * H * 128 * sizeof(float)));
+    const void *qq = q, *kk = k, *vv = v, *gg = dout;
+    int ldq = ld_q, ldk = ld_k, ldv = ld_v, ldg = ld_do;
+    PrepBatch pb;
+    pb.pp.H = H; pb.pp.eps = 0.f;
+    if (dtype != KB_F16) {
+        void* d;
+        d = sg.take((size_t)B * Tq, H); if (d) pb.add(d, H * 128, q, ld_q, B * Tq, Tq, nullptr, nullptr, nullptr); qq = d; ldq = H * 128;
+        d = sg.take((size_t)B * Tq, H); if (d) pb.add(d, H * 128, dout, ld_do, B * Tq, Tq, nullptr, nullptr, nullptr); gg = d; ldg = H * 128;
+        d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, k, ld_k, B * Tk, Tk, nullptr, nullptr, nullptr); kk = d; ldk = H * 128;
+        d = sg.take((size_t)B * Tk, H); if (d) pb.add(d, H * 128, v, ld_v, B * Tk, Tk, nullptr, nullptr, nullptr); vv = d; ldv = H * 128;
+    }
+    if (sg.overflow) return KB_ERR_WORKSPACE;
+    if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
+    // forward on the fp16 operands: O (fp32) for D, and L into the statistics
+    if ((rc = attn_pair(o32, qq, kk, vv, nullptr, nullptr, nullptr, nullptr, B, Tq, Tk, npad, H, ldq, ldk, ldv, H * 128, KB_F16, KB_F32, 0.f,
+                        sg.ws, sg.left, stream, nullptr, stats)))
+        return rc;
+    {
+        const long long warps = (long long)B * H * ((Tq + 127) / 128) * 128;
+        const unsigned grid = (unsigned)((warps + 7) / 8);
+        // dO as the tensor cores see it (fp16), so that the rows of dS sum to zero as exactly as the products allow
+        bwd_delta_kernel<<<grid, 256, 0, stream>>>(stats, static_cast<const __half*>(gg), ldg, o32, H * 128, B, Tq, H);
+        if (cudaGetLastError() != cudaSuccess) return KB_ERR_CUDA;
+    }
+    CUtensorMap tq, tk, tv, tg;
+    if ((rc = make_tmap(&tq, qq, Tq, H, B, ldq)) || (rc = make_tmap(&tk, kk, Tk, H, B, ldk)) || (rc = make_tmap(&tv, vv, Tk, H, B, ldv)) ||
+        (rc = make_tmap(&tg, gg, Tq, H, B, ldg)))
+        return rc;
+    BwdParams p = {};
+    p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
+    p.stats = stats; p.scale_log2 = SCALE_LOG2; p.scale = 0.08838834764831845f;
+    p.status = st->status;
+    ProfScope ps(st, KB_PROF_ATTENTION, stream);
+    p.out0 = static_cast<float*>(dv); p.ld0 = ld_dv; p.out1 = static_cast<float*>(dk); p.ld1 = ld_dk;
+    attn_bwd_kernel<BWD_DKV><<<dim3((unsigned)((Tk + 127) / 128), (unsigned)H, (unsigned)B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
+    if (cudaGetLastError() != cudaSuccess) return KB_ERR_CUDA;
+    p.out0 = static_cast<float*>(dq); p.ld0 = ld_dq; p.out1 = nullptr; p.ld1 = 0;
+    attn_bwd_kernel<BWD_DQ><<<dim3((unsigned)((Tq + 127) / 128), (unsigned)H, (unsigned)B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
 int kb_cross_kv(void* k16, void* v16, int ld_out, const void* ctx, int ld_ctx, int ctx_dtype, int L, int N, int K, const void* Wk,

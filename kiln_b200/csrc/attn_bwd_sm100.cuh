@@ -1,0 +1,299 @@
+// Attention backward on sm_100a: dQ, dK, dV of softmax(Q K^T / sqrt(128)) V per head, from Q, K, V and dO.
+//
+// It takes the place of the reference's exact backward attention_bwd (engine/src/train.cu:216-242: five batched cuBLAS SGEMMs
+// per head group around k_softmax_pad, train.cu:103-121, and k_dsoftmax, train.cu:124-131, with the [heads, Tq, Tk]
+// probabilities P and their gradient dP materialised in the arena) for the LoRA trainer's two call sites (train.cu:334, 344).
+// Here nothing of size Tq x Tk exists in memory: like the forward kernel the products are formed tile by tile on the tensor
+// cores (fp16 operands, fp32 accumulation in TMEM) and P is recomputed from a per-row statistic.
+//
+// Four launches (kb_attn_bwd): the staging pre-pass (Q, K, V, dO -> fp16), the forward kernel, which also leaves
+// L_i = log2 of the softmax denominator of row i (npad zero keys included) in the "stats" array, a small kernel for
+// D_i = sum_d dO[i, d] O[i, d] (= sum_j P_ij dP_ij, what k_dsoftmax sums), and this file's kernel twice:
+//
+//   BWD_DKV  one thread block per (key block j, head, image), query blocks i streamed through a two-stage ring:
+//              S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                      (two SS products into TMEM)
+//              P^T  = 2^(c S^T - L_i)      dS^T = P^T (dP^T - D_i)                (softmax warps; fp16, written over S^T / dP^T)
+//              dV_j += P^T dO_i            dK_j += dS^T Q_i                       (A operand from TMEM, B the same shared-memory
+//                                                                                  tiles read MN-major)
+//   BWD_DQ   one thread block per (query block i, head, image), key blocks j streamed:
+//              S = Q_i K_j^T,  dP = dO_i V_j^T,  dS = 2^(c S - L_i) (dP - D_i),  dQ_i += dS K_j
+//
+// Two kernels instead of one with atomics: every output element is written once by one thread block, in a fixed order, so
+// results are bit-identical from run to run (the reference's are too). The price is that S and dP are formed twice.
+// The npad zero keys only enter through L_i: their dP is 0 and their K is 0, so they add nothing to any gradient
+// (train.cu:124 says the same of the reference). Rows past Tq or Tk are zero-filled by TMA; a zero Q/dO row has dS = 0 and
+// adds nothing to dK / dV, a zero K row adds nothing to dQ, so ragged sizes need no masking - only finite statistics, which
+// the stats array (padded to whole query blocks) always holds.
+//
+// TMEM (512 columns): T0 [0,128) S or S^T, T1 [128,256) dP or dP^T, acc0 [256,384), acc1 [384,512). The fp16 P^T / dS^T
+// go over the first 64 columns of T0 / T1: each of the two warps that share a lane quarter first loads its 64 columns of
+// both, the pair meets at a named barrier, and only then either of them stores. One product pair in flight per thread
+// block (the S products of block i+1 wait for the dV / dK products of block i): simple and correct first, ~40 % of the
+// tensor pipe; the forward kernel's two-stream overlap is the known next step.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "attn_sm100.cuh"
+#include "ptx.cuh"
+
+namespace kb {
+
+constexpr int BWD_DKV = 0, BWD_DQ = 1;
+constexpr int BWD_THREADS = 384;                              // warps 0-7 softmax / epilogue, 8 MMA issue, 9 TMA loads, 10-11 idle
+constexpr int BWD_SOFTMAX_REGS = 224, BWD_OTHER_REGS = 56;    // 384 x 168 = 256 x 224 + 128 x 56
+constexpr int BWD_STAGE_BYTES = 2 * TILE_BYTES + 1024;        // two streamed tiles + the statistics of a query block
+constexpr int BWD_SMEM = 2 * TILE_BYTES + 2 * BWD_STAGE_BYTES + 1024;   // resident pair, two stages, control block
+
+struct BwdParams {
+    float* out0;            // BWD_DKV: dV [B*Tk, ld0]; BWD_DQ: dQ [B*Tq, ld0]
+    float* out1;            // BWD_DKV: dK [B*Tk, ld1]
+    int ld0, ld1;
+    int B, H, Tq, Tk;
+    const float* stats;     // [B][H][ceil(Tq/128)][2][128]: L (log2 of the softmax denominator, in units of c * score), then D
+    float scale_log2;       // c = log2(e) / sqrt(128)
+    float scale;            // 1 / sqrt(128)
+    uint32_t* status;
+};
+
+enum { BB_RES = 0, BB_XFULL = 1, BB_XEMPTY = 3, BB_TFULL = 5, BB_PFULL = 6, BB_ACC = 7, BB_COUNT = 8 };
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// D_i = sum_d dO[i, d] * O[i, d] per (row, head) into the stats array; one warp per (row, head), rows of whole query blocks
+// (rows past Tq get 0). dO fp16 as staged for the tensor cores, O fp32 from the forward pass.
+__global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, const float* o, int ld_o, int B, int Tq, int H) {
+    const int nqb = (Tq + BM - 1) / BM;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const long long total = (long long)B * H * nqb * BM;
+    if (w >= total) return;
+    const int r = (int)(w % (nqb * BM)), h = (int)((w / (nqb * BM)) % H), b = (int)(w / ((long long)nqb * BM * H));
+    float s = 0.f;
+    if (r < Tq) {
+        const uint2 gv = *reinterpret_cast<const uint2*>(dout + ((size_t)b * Tq + r) * (size_t)ld_do + (size_t)h * HD + lane * 4);
+        const float4 ov = *reinterpret_cast<const float4*>(o + ((size_t)b * Tq + r) * (size_t)ld_o + (size_t)h * HD + lane * 4);
+        const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&gv.x)), gb = __half22float2(*reinterpret_cast<const __half2*>(&gv.y));
+        s = ga.x * ov.x + ga.y * ov.y + gb.x * ov.z + gb.y * ov.w;
+    }
+    for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
+    if (lane == 0) stats[(((size_t)b * H + h) * nqb + r / BM) * 256 + 128 + (r % BM)] = s;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {                                           // never seen; without it every tile would be garbage
+        if (threadIdx.x == 0) atomicOr(p.status, ST_TIMEOUT);
+        return;
+    }
+    const uint32_t sR0 = base, sR1 = base + TILE_BYTES;            // resident: K_j, V_j (BWD_DKV) or Q_i, dO_i (BWD_DQ)
+    const uint32_t sX = base + 2 * TILE_BYTES;                     // stages: X0 (Q_i or K_j), X1 (dO_i or V_j), statistics
+    uint8_t* const ctrl = smem_raw + 2 * TILE_BYTES + 2 * BWD_STAGE_BYTES;
+    const uint32_t bars = sX + 2 * BWD_STAGE_BYTES;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 128);
+    volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 132);
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int nqb = (p.Tq + BM - 1) / BM;
+    const int n_it = MODE == BWD_DKV ? nqb : (p.Tk + BN - 1) / BN;
+
+    if (tid == 0) {
+        for (int i = 0; i < BB_COUNT; i++) mbar_init(bar(i), i == BB_PFULL ? 8u : 1u);
+        *abort_flag = 0u;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 9 && lane == 0) { tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO); }
+    if (warp == 8) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        setmaxnreg_inc<BWD_SOFTMAX_REGS>();
+        // ------------------------------------------------------------------ softmax warps: TMEM lane quarter x column half
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;                          // row of the resident block (= TMEM lane)
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tT0 = tmem_base + lane_base, tT1 = tmem_base + lane_base + 128u;
+        const float c = p.scale_log2;
+        float Lr = 0.f, Dr = 0.f;                                   // BWD_DQ: this row's statistics
+        if (MODE == BWD_DQ) {
+            const float* st = p.stats + (((size_t)b * p.H + h) * nqb + blk) * 256;
+            Lr = __ldg(st + r);
+            Dr = __ldg(st + 128 + r);
+        }
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int st = it & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_TFULL), (uint32_t)it & 1u, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+            const float* sStats = reinterpret_cast<const float*>(smem_raw + 2 * TILE_BYTES + st * BWD_STAGE_BYTES + 2 * TILE_BYTES);
+            if (MODE == BWD_DKV) {                                  // the statistics came with the stage's tiles (already complete: the
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_XFULL + st), ((uint32_t)it >> 1) & 1u, abort_flag));   // products read them)
+                if (!ok) break;
+            }
+            uint32_t s0[32], s1[32], d0[32], d1[32];
+            tmem_ld32(tT0 + (uint32_t)(half * 64), s0);
+            tmem_ld32(tT0 + (uint32_t)(half * 64 + 32), s1);
+            tmem_ld32(tT1 + (uint32_t)(half * 64), d0);
+            tmem_ld32(tT1 + (uint32_t)(half * 64 + 32), d1);
+            tmem_wait_ld();
+            reg_fence32(s0); reg_fence32(s1); reg_fence32(d0); reg_fence32(d1);
+            // both warps of the lane quarter hold their columns: the fp16 results may now go over the first 64 columns
+            named_bar_sync(1 + quarter, 64);
+            uint32_t pk[32], dk[32];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+#pragma unroll
+                for (int u = 0; u < 2; u++) {                       // u = 0: columns [0,32) of this warp's half, 1: [32,64)
+                    const uint32_t* sv = u ? s1 : s0;
+                    const uint32_t* dv = u ? d1 : d0;
+                    float L0 = Lr, L1 = Lr, D0 = Dr, D1 = Dr;
+                    if (MODE == BWD_DKV) {                          // per column: the query row's statistics (a broadcast read)
+                        const int col = half * 64 + u * 32 + e;
+                        const float2 l2 = *reinterpret_cast<const float2*>(sStats + col);
+                        const float2 dd = *reinterpret_cast<const float2*>(sStats + 128 + col);
+                        L0 = l2.x; L1 = l2.y; D0 = dd.x; D1 = dd.y;
+                    }
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[e]), c, -L0));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), c, -L1));
+                    const float g0 = p0 * (__uint_as_float(dv[e]) - D0);
+                    const float g1 = p1 * (__uint_as_float(dv[e + 1]) - D1);
+                    pk[u * 16 + (e >> 1)] = pack16<DT_F16>(p0, p1);
+                    dk[u * 16 + (e >> 1)] = pack16<DT_F16>(g0, g1);
+                }
+            }
+            // element pair (2c, 2c+1) of the contraction index in column c: this warp's 64 elements are columns [32 half, +32)
+            if (MODE == BWD_DKV) tmem_st32(tT0 + (uint32_t)(half * 32), pk);
+            tmem_st32(tT1 + (uint32_t)(half * 32), dk);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BB_PFULL));
+        }
+        // ------------------------------------------------------------------ epilogue: accumulators -> global, one row per thread
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_ACC), 0u, abort_flag));
+        if (ok) {
+            tc_fence_after();
+            const int T = MODE == BWD_DKV ? p.Tk : p.Tq;
+            const int row = blk * BM + r;
+#pragma unroll
+            for (int a = 0; a < (MODE == BWD_DKV ? 2 : 1); a++) {
+                float* const out = a ? p.out1 : p.out0;
+                const int ld = a ? p.ld1 : p.ld0;
+                const float k = (MODE == BWD_DKV && a == 0) ? 1.f : p.scale;   // dV unscaled; dK and dQ carry 1/sqrt(128)
+                float* dst = out + ((size_t)b * T + (size_t)row) * (size_t)ld + (size_t)h * HD + half * 64;
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    uint32_t o[32];
+                    float v[32];
+                    tmem_ld32(tmem_base + lane_base + 256u + (uint32_t)(a * 128 + half * 64 + 32 * q), o);
+                    tmem_wait_ld();
+                    reg_fence32(o);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * k;
+                    if (row < T) store32<float>(dst + 32 * q, v);
+                }
+            }
+        }
+    } else {
+        setmaxnreg_dec<BWD_OTHER_REGS>();
+        if (warp == 8 && lane == 0) {
+            // ------------------------------------------------------------------ MMA issue
+            constexpr uint32_t IDESC_T = idesc_f16(0, 0, 0, 0, BM, BN);   // T = R X^T, both operands K-major (rows of 128 head channels)
+            constexpr uint32_t IDESC_A = idesc_f16(0, 0, 0, 1, BM, HD);   // acc += (fp16 in TMEM) X, X MN-major (rows = contraction index)
+            constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
+            auto issue_T = [&](uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr) {
+                const uint32_t alo = smem_desc_lo(a_saddr, 16), blo = smem_desc_lo(b_saddr, 16);
+                mma_ss_w<0>(d_tmem, alo, blo, DESC_HI, IDESC_T);
+#pragma unroll
+                for (int kk = 1; kk < 8; kk++) {
+                    const uint32_t off = ((uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32u) >> 4;
+                    mma_ss_w<1>(d_tmem, alo + off, blo + off, DESC_HI, IDESC_T);
+                }
+            };
+            auto issue_A = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_saddr, bool first) {
+                const uint32_t blo = smem_desc_lo(b_saddr, HALF_BYTES);
+                if (first) mma_ts_w<0>(d_tmem, a_tmem, blo, DESC_HI, IDESC_A);
+                else mma_ts_w<1>(d_tmem, a_tmem, blo, DESC_HI, IDESC_A);
+#pragma unroll
+                for (int kk = 1; kk < 8; kk++) mma_ts_w<1>(d_tmem, a_tmem + (uint32_t)(kk * 8), blo + (uint32_t)(kk * 128), DESC_HI, IDESC_A);
+            };
+            bool good = mbar_wait(bar(BB_RES), 0u, abort_flag);
+            for (int it = 0; it < n_it && good; ++it) {
+                const int st = it & 1;
+                const uint32_t x0 = sX + st * BWD_STAGE_BYTES, x1 = x0 + TILE_BYTES;
+                good = mbar_wait(bar(BB_XFULL + st), ((uint32_t)it >> 1) & 1u, abort_flag);
+                if (!good) break;
+                tc_fence_after();
+                // T0 and T1 are free: the products that read the fp16 data in them were issued before these (same thread, in
+                // order), and the softmax warps were done with them before they signalled those products
+                issue_T(tmem_base, sR0, x0);
+                issue_T(tmem_base + 128u, sR1, x1);
+                tc_commit(bar(BB_TFULL));
+                good = mbar_wait(bar(BB_PFULL), (uint32_t)it & 1u, abort_flag);
+                if (!good) break;
+                tc_fence_after();
+                if (MODE == BWD_DKV) {
+                    issue_A(tmem_base + 256u, tmem_base, x1, it == 0);             // dV += P^T dO_i
+                    issue_A(tmem_base + 384u, tmem_base + 128u, x0, it == 0);      // dK += dS^T Q_i
+                } else {
+                    issue_A(tmem_base + 256u, tmem_base + 128u, x0, it == 0);      // dQ += dS K_j
+                }
+                tc_commit(bar(BB_XEMPTY + st));                                    // the stage may be reloaded
+            }
+            if (good) tc_commit(bar(BB_ACC));
+        } else if (warp == 9 && lane == 0) {
+            // ------------------------------------------------------------------ TMA loads
+            auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t mbar, int row0) {
+                tma_load_3d(dst, tm, mbar, h * HD, row0, b);
+                tma_load_3d(dst + HALF_BYTES, tm, mbar, h * HD + 64, row0, b);
+            };
+            mbar_expect_tx(bar(BB_RES), 2 * TILE_BYTES);
+            load_tile(sR0, MODE == BWD_DKV ? &tmK : &tmQ, bar(BB_RES), blk * BM);
+            load_tile(sR1, MODE == BWD_DKV ? &tmV : &tmdO, bar(BB_RES), blk * BM);
+            bool good = true;
+            int issued = 0;
+            for (int it = 0; it < n_it && good; ++it) {
+                const int st = it & 1;
+                good = mbar_wait(bar(BB_XEMPTY + st), (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag);
+                if (!good) break;
+                issued = it + 1;
+                const uint32_t x0 = sX + st * BWD_STAGE_BYTES, x1 = x0 + TILE_BYTES;
+                mbar_expect_tx(bar(BB_XFULL + st), 2 * TILE_BYTES + (MODE == BWD_DKV ? 1024 : 0));
+                load_tile(x0, MODE == BWD_DKV ? &tmQ : &tmK, bar(BB_XFULL + st), it * BM);
+                load_tile(x1, MODE == BWD_DKV ? &tmdO : &tmV, bar(BB_XFULL + st), it * BM);
+                if (MODE == BWD_DKV) bulk_load_1d(x1 + TILE_BYTES, p.stats + (((size_t)b * p.H + h) * nqb + it) * 256, 1024, bar(BB_XFULL + st));
+            }
+            if (!good || *abort_flag) {                               // let the copies already requested land before the memory goes away
+                drain_wait(bar(BB_RES), 0u);
+                for (int k = issued > 2 ? issued - 2 : 0; k < issued; ++k) drain_wait(bar(BB_XFULL + (k & 1)), ((uint32_t)k >> 1) & 1u);
+            }
+        }
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        if (lane == 0 && *abort_flag) atomicOr(p.status, ST_TIMEOUT);
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace kb

@@ -434,9 +434,16 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ G
                     }
                 }
             }
-            if (!good || *abort_flag) {                                   // let copies in flight land before the memory goes away
-                const uint64_t t0 = globaltimer_ns();
-                while (globaltimer_ns() - t0 < 20000ull) {}
+            if (!good || *abort_flag) {
+                // let the copies already requested land before the memory goes away: a bounded wait on the FULL barrier of every
+                // stage with a request outstanding. In a pair those barriers live in the first CTA; the second one cannot poll
+                // them and waits a fixed 20 us instead (both then meet at the cluster barrier below).
+                if (!PAIR || rank == 0) {
+                    for (uint32_t k = ring > (uint32_t)G_STAGES ? ring - G_STAGES : 0u; k < ring; ++k) drain_wait(bar(GBAR_FULL + k % G_STAGES), (k / G_STAGES) & 1u);
+                } else {
+                    const uint64_t t0 = globaltimer_ns();
+                    while (globaltimer_ns() - t0 < 20000ull) {}
+                }
             }
         }
         __syncwarp();

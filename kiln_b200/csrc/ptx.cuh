@@ -63,6 +63,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
+// On the way out after a failure: give a load this thread has issued a bounded chance to land. Its FULL barrier's phase
+// completes when the bytes are in shared memory, so a thread block that waits here does not exit under a copy in flight.
+// Bounded (the copy may never have been accepted): 200 us, far beyond any copy's latency.
+__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(bar, parity) && globaltimer_ns() - t0 < 200000ull) {}
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -57,6 +57,10 @@ def lib():
         L.kb_linear16_qkv_lora.argtypes = [pvp, i, vp, i, pvp, i, pvp, pi, pvp, pi, pi, i, i, i, pvp, pi, vp, vp, i, f, vp]
         L.kb_lora_pack.restype = i
         L.kb_lora_pack.argtypes = [vp, i, i, vp, i, i, f, vp]
+        L.kb_attn_bwd_workspace_bytes.restype = ctypes.c_size_t
+        L.kb_attn_bwd_workspace_bytes.argtypes = [i, i, i, i, i]
+        L.kb_attn_bwd.restype = i
+        L.kb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, i, i, vp, ctypes.c_size_t, vp]
         L.kb_cross_kv.restype = i
         L.kb_cross_kv.argtypes = [vp, vp, i, vp, i, i, i, i, i, vp, vp, i, vp, f, vp, ctypes.c_size_t, vp]
         L.kb_linear16_qkv.restype = i
@@ -273,6 +277,17 @@ def linear16_qkv(Cs, A, Ws, head_ws=(None, None, None), rope_on=(True, True, Fal
     _check(lib().kb_linear16_qkv(arr(Cs), _ld(Cs[0]), _ptr(A), _ld(A), arr(Ws), _ld(Ws[0]), M, N, K, arr(head_ws), on, _ptr(rope_cos),
                                  _ptr(rope_sin), rope_T, eps, _stream()), "kb_linear16_qkv")
     return Cs
+
+
+def attn_bwd(dq, dk, dv, q, k, v, dout, B, Tq, Tk, npad, H, workspace=None):
+    """dq, dk, dv (fp32) of softmax(q k^T / sqrt(128)) v per head from q, k, v, dout (engine: attention_bwd,
+    engine/src/train.cu:216-242). q, dout [B*Tq, >= H*128], k, v [B*Tk, >= H*128], one dtype."""
+    import torch
+    if workspace is None:
+        workspace = torch.empty(lib().kb_attn_bwd_workspace_bytes(B, Tq, Tk, H, _dt(q)), dtype=torch.uint8, device=q.device)
+    _check(lib().kb_attn_bwd(_ptr(dq), _ptr(dk), _ptr(dv), _ptr(q), _ptr(k), _ptr(v), _ptr(dout), B, Tq, Tk, npad, H, _ld(q), _ld(k), _ld(v),
+                             _ld(dout), _ld(dq), _ld(dk), _ld(dv), _dt(q), _ptr(workspace), workspace.numel(), _stream()), "kb_attn_bwd")
+    return dq, dk, dv
 
 
 def cross_kv(k16, v16, ctx, Wk, Wv, kn_w=None, eps=1e-6, workspace=None):

@@ -214,6 +214,73 @@ void ko_attention_f64(float* out, int ldo, const float* q, int ldq, const float*
     }
 }
 
+/* ---- attention backward (train.cu:216-242 with k_softmax_pad, train.cu:103-121, and k_dsoftmax, train.cu:124-131) ----
+ * q [Tq, ldq], k/v [Tk, ld], dout [Tq, ldo] -> dq [Tq, ldq'], dk, dv [Tk, ld']; head h at columns [h*128, +128). Per head:
+ *   S = QK^T/sqrt(128); P = softmax over the Tk keys and npad zero keys of score 0; dP = dO V^T; dV = P^T dO;
+ *   dS = P (dP - sum_j P dP) (padding keys have dP = 0 and drop out of the sum); dQ = dS K/sqrt(128); dK = dS^T Q/sqrt(128).
+ * Everything in double (the reference runs fp32 cuBLAS SGEMMs). Key rows [j0, j1) of dk / dv only: dq rows are independent of
+ * each other, so sampled query rows are exact with the full K/V; dk / dv need every query row, which the caller passes. */
+void ko_attention_bwd(float* dq, int lddq, float* dk, int lddk, float* dv, int lddv, const float* q, int ldq, const float* k, int ldk,
+                      const float* v, int ldv, const float* dout, int ldo, int Tq, int Tk, int H, int npad, int j0, int j1) {
+    const double scale = 1.0 / sqrt(128.0);
+    const int nj = j1 - j0;
+    for (int h = 0; h < H; h++) {
+        double* P = (double*)malloc(sizeof(double) * (size_t)Tq * (size_t)(Tk > 0 ? Tk : 1));
+        double* dS = (double*)malloc(sizeof(double) * (size_t)Tq * (size_t)(Tk > 0 ? Tk : 1));
+#pragma omp parallel for schedule(static)
+        for (int t = 0; t < Tq; t++) {
+            const float* qr = q + (size_t)t * ldq + h * KO_D;
+            const float* gr = dout + (size_t)t * ldo + h * KO_D;
+            double* pr = P + (size_t)t * Tk;
+            double* dr = dS + (size_t)t * Tk;
+            double m = npad ? 0.0 : -INFINITY;
+            for (int j = 0; j < Tk; j++) {
+                const float* kr = k + (size_t)j * ldk + h * KO_D;
+                double s = 0;
+                for (int d = 0; d < KO_D; d++) s += (double)qr[d] * (double)kr[d];
+                pr[j] = s * scale;
+                if (pr[j] > m) m = pr[j];
+            }
+            double l = npad * exp(-m);
+            for (int j = 0; j < Tk; j++) { pr[j] = exp(pr[j] - m); l += pr[j]; }
+            double dot = 0;
+            for (int j = 0; j < Tk; j++) {
+                const float* vr = v + (size_t)j * ldv + h * KO_D;
+                double dp = 0;
+                for (int d = 0; d < KO_D; d++) dp += (double)gr[d] * (double)vr[d];
+                pr[j] /= l;
+                dr[j] = dp;
+                dot += pr[j] * dp;
+            }
+            double acc[KO_D] = {0};
+            for (int j = 0; j < Tk; j++) {
+                const float* kr = k + (size_t)j * ldk + h * KO_D;
+                dr[j] = pr[j] * (dr[j] - dot);
+                for (int d = 0; d < KO_D; d++) acc[d] += dr[j] * (double)kr[d];
+            }
+            if (dq) {
+                float* o = dq + (size_t)t * lddq + h * KO_D;
+                for (int d = 0; d < KO_D; d++) o[d] = (float)(acc[d] * scale);
+            }
+        }
+#pragma omp parallel for schedule(static)
+        for (int jj = 0; jj < nj; jj++) {
+            const int j = j0 + jj;
+            double ak[KO_D] = {0}, av[KO_D] = {0};
+            for (int t = 0; t < Tq; t++) {
+                const float* qr = q + (size_t)t * ldq + h * KO_D;
+                const float* gr = dout + (size_t)t * ldo + h * KO_D;
+                const double p = P[(size_t)t * Tk + j], ds = dS[(size_t)t * Tk + j];
+                for (int d = 0; d < KO_D; d++) { av[d] += p * (double)gr[d]; ak[d] += ds * (double)qr[d]; }
+            }
+            if (dk) { float* o = dk + (size_t)jj * lddk + h * KO_D; for (int d = 0; d < KO_D; d++) o[d] = (float)(ak[d] * scale); }
+            if (dv) { float* o = dv + (size_t)jj * lddv + h * KO_D; for (int d = 0; d < KO_D; d++) o[d] = (float)av[d]; }
+        }
+        free(P);
+        free(dS);
+    }
+}
+
 /* ---- RMSNorm over rows of `dim` (kernels.cu:656-666); w = bf16 bit patterns [dim] or NULL ---- */
 void ko_rmsnorm(float* y, const float* x, const uint16_t* w, size_t rows, int dim, float eps) {
 #pragma omp parallel for schedule(static)

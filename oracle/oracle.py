@@ -30,6 +30,8 @@ def lib():
         L.ko_cosmos_rope.argtypes = [vp, vp, i, i]
         L.ko_nag.argtypes = [vp, vp, i, i, f, f, f, i]
         L.ko_linear16.argtypes = [vp, i, vp, i, vp, i, i, i, i, i, vp]
+        L.ko_attention_bwd.argtypes = [vp, i, vp, i, vp, i, vp, i, vp, i, vp, i, vp, i, i, i, i, i, i, i]
+        L.ko_attention_bwd.restype = None
         L.ko_torch_randn.argtypes = [ctypes.c_uint64, ctypes.c_size_t, vp]
         L.ko_torch_randn.restype = i
         L.ko_round16.argtypes = [vp, ctypes.c_size_t, i]
@@ -79,6 +81,23 @@ def attention(q, k, v, H, npad=0, acc64=True):
     fn = lib().ko_attention_f64 if acc64 else lib().ko_attention_f32
     fn(_p(out), out.shape[1], _p(q), q.shape[1], _p(k), k.shape[1], _p(v), v.shape[1], Tq, Tk, H, npad)
     return out
+
+
+def attention_bwd(q, k, v, dout, H, npad=0, key_rows=None):
+    """Exact attention backward in double (reference: engine/src/train.cu:216-242): returns (dq [Tq, H*128], dk, dv [rows, H*128]).
+
+    key_rows = (j0, j1) restricts dk / dv to those key rows (dq is always complete for the query rows given; to sample query rows,
+    pass a subset of q and dout - but then dk / dv are meaningless)."""
+    q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
+    Tq, Tk = q.shape[0], k.shape[0]
+    j0, j1 = (0, Tk) if key_rows is None else key_rows
+    D = H * 128
+    dq = np.zeros((Tq, D), np.float32)
+    dk = np.zeros((j1 - j0, D), np.float32)
+    dv = np.zeros((j1 - j0, D), np.float32)
+    lib().ko_attention_bwd(_p(dq), D, _p(dk), D, _p(dv), D, _p(q), q.shape[1], _p(k), k.shape[1], _p(v), v.shape[1], _p(dout), dout.shape[1],
+                           Tq, Tk, H, npad, j0, j1)
+    return dq, dk, dv
 
 
 def rmsnorm(x, w_bf16_bits, H, eps=1e-6):

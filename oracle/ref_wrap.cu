@@ -101,6 +101,19 @@ void linear16(void* y, int ldy, const __half* x16, int T, const Weight& Win, Epi
 }
 #endif
 #include "dit.cu"        // k_nag<T>, cosmos_rope, Dit::forward_batch
+// The LoRA trainer's file defines the same model constants as dit.cu (each is its own translation unit in the engine): rename them
+// while it is read. Wanted from it: attention_bwd (engine/src/train.cu:216-242), the exact attention backward.
+#define D kref_train_D
+#define NH kref_train_NH
+#define DH kref_train_DH
+#define FF kref_train_FF
+#define EPS kref_train_EPS
+#include "train.cu"
+#undef D
+#undef NH
+#undef DH
+#undef FF
+#undef EPS
 
 // The symbols the included files need from the reference's Win32-only loader; never reached here.
 float st_elem_f32(const StTensor&, int64_t) { return 0.f; }
@@ -228,6 +241,14 @@ int kref_cosmos_rope(float* c, float* s, int Hp, int Wp) {
 }
 
 int kref_sync() { return (int)cudaDeviceSynchronize(); }
+
+// attention_bwd (engine/src/train.cu:216-242): q [Tq, 2048], k, v [Tk, 2048], dout [Tq, 2048] fp32 -> dq, dk, dv (16 heads of 128;
+// five cuBLAS SGEMMs per head group + k_softmax_pad / k_dsoftmax). Needs kref_engine_init (the arena holds P and dP).
+int kref_attention_bwd(float* dq, float* dk, float* dv, const float* q, const float* k, const float* v, const float* dout, int Tq, int Tk,
+                       int npad, char* err, int n) {
+    try { attention_bwd(dq, dk, dv, q, k, v, dout, Tq, Tk, npad); gpu_sync(); return 0; }
+    catch (const std::exception& e) { if (err && n > 0) snprintf(err, n, "%s", e.what()); return -1; }
+}
 
 // ------------------------------------------------------------------ the reference's DiT driver on seeded random weights
 // p[i] = bf16(bias + amp * u), u uniform in (-1, 1) from a hash of (seed, i): the same weights in every build of this file

@@ -132,3 +132,36 @@ def test_linear16_oracle_vs_reference_kernel_golden():
             bound = (2.0 ** -11 * np.sqrt(K / 32) * 4.0 + 2.0 ** -9 * np.abs(ref).max()) * scale
             assert np.abs(got - ref).max() <= bound, (name, ename, np.abs(got - ref).max(), bound)
             assert np.abs(got - ref).sum() / np.abs(ref).sum() <= 1e-3, (name, ename)
+
+
+def test_attention_bwd_oracle_vs_reference_fixture():
+    """ko_attention_bwd (fp64) against the outputs of the reference's attention_bwd (engine/src/train.cu:216-242: fp32 cuBLAS
+    SGEMMs) recorded on a B200, and against central differences of the forward oracle."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_ref_bwd_fixtures", os.path.join(os.path.dirname(__file__), "golden", "make_ref_bwd_fixtures.py"))
+    bgen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bgen)
+    path = os.path.join(os.path.dirname(__file__), "golden", "ref_bwd_fixtures.npz")
+    if not os.path.exists(path):
+        pytest.skip("tests/golden/ref_bwd_fixtures.npz has not been generated (tests/golden/make_ref_bwd_fixtures.py on a B200)")
+    golden = np.load(path)
+    n = bgen.KEEP_HEADS * 128
+    for case in bgen.BWD_CASES:
+        name, Tq, Tk, npad = case
+        q, k, v, dout = bgen.bwd_inputs(case)
+        outs = oracle.attention_bwd(q[:, :n], k[:, :n], v[:, :n], dout[:, :n], bgen.KEEP_HEADS, npad)   # heads are independent
+        for gname, o in zip(("dq", "dk", "dv"), outs):
+            g = golden[f"{name}/{gname}"]
+            assert np.abs(o - g).max() <= 2e-5 * max(1.0, float(np.abs(g).max())), f"{name}/{gname}: {np.abs(o - g).max():.3e}"
+    rng = np.random.default_rng(0)
+    q, k, v, do = (rng.standard_normal((r, 128)).astype(np.float32) for r in (5, 7, 7, 5))
+    for npad in (0, 3):
+        dq, dk, dv = oracle.attention_bwd(q, k, v, do, 1, npad)
+        f = lambda q, k, v: float((oracle.attention(q, k, v, 1, npad).astype(np.float64) * do).sum())
+        for which, arr, grad in ((0, q, dq), (1, k, dk), (2, v, dv)):
+            a, b = arr.copy(), arr.copy()
+            a[2, 17] += 1e-2
+            b[2, 17] -= 1e-2
+            args_a, args_b = [q, k, v], [q, k, v]
+            args_a[which], args_b[which] = a, b
+            assert abs((f(*args_a) - f(*args_b)) / 2e-2 - grad[2, 17]) <= 2e-4
