@@ -197,7 +197,7 @@ int launch_prep(DeviceState* st, const PrepBatch& pb, int in_dtype, int out_dtyp
 
 template <int MODE, typename OutT>
 int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
-                  const CUtensorMap& tv1, const CUtensorMap& to, const PeerMaps& tp, const AttnParams& p, int sm_count, cudaStream_t stream) {
+                  const CUtensorMap& tv1, const CUtensorMap& to, const AttnParams& p, int sm_count, cudaStream_t stream) {
     // persistent kernel: one CTA per SM (its shared memory and TMEM fill an SM) walks the work items
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(ATTN_THREADS, 1, 1);
@@ -214,7 +214,7 @@ int launch_attn_t(const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorM
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, OutT>, tq, tk0, tv0, tk1, tv1, to, tp, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<MODE, OutT>, tq, tk0, tv0, tk1, tv1, to, p);
     return e == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
@@ -222,28 +222,21 @@ template <int MODE>
 int launch_attn(int out_dtype, const CUtensorMap& tq, const CUtensorMap& tk0, const CUtensorMap& tv0, const CUtensorMap& tk1,
                 const CUtensorMap& tv1, const AttnParams& p, int sm_count, cudaStream_t stream) {
     // 16-bit outputs of single-GPU calls leave through TMA stores: [B][Tq][H*128] view of `out`, box = 64 columns x 128 rows
-    // head-split runs: the same view of every GPU's gathered buffer, beginning at this GPU's first column there
     CUtensorMap to;
-    PeerMaps tp;
     memset(&to, 0, sizeof(to));
-    memset(&tp, 0, sizeof(tp));
-    if (out_dtype != KB_F32) {
+    if (out_dtype != KB_F32 && p.n_peers == 0) {
         const cuuint64_t dims[3] = {(cuuint64_t)p.H * 128, (cuuint64_t)p.Tq, (cuuint64_t)p.B};
         const cuuint64_t strides[2] = {(cuuint64_t)p.ldo * 2, (cuuint64_t)p.Tq * (cuuint64_t)p.ldo * 2};
         const cuuint32_t box[3] = {64, 128, 1};
         const cuuint32_t estr[3] = {1, 1, 1};
-        const int n_maps = p.n_peers == 0 ? 1 : p.n_peers;
-        for (int i = 0; i < n_maps; i++) {
-            void* const base = p.n_peers == 0 ? p.out : static_cast<void*>(static_cast<char*>(p.out_peers[i]) + (size_t)p.col0 * 2);
-            if (g_encode(p.n_peers == 0 ? &to : &tp.m[i], out_dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                         base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-                return KB_ERR_CUDA;
-        }
+        if (g_encode(&to, out_dtype == KB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, p.out, dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return KB_ERR_CUDA;
     }
-    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
-    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
-    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, to, tp, p, sm_count, stream);
+    if (out_dtype == KB_F32) return launch_attn_t<MODE, float>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
+    if (out_dtype == KB_BF16) return launch_attn_t<MODE, __nv_bfloat16>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
+    return launch_attn_t<MODE, __half>(tq, tk0, tv0, tk1, tv1, to, p, sm_count, stream);
 }
 
 constexpr float SCALE_LOG2 = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)

@@ -25,11 +25,18 @@
 // adds nothing to dK / dV, a zero K row adds nothing to dQ, so ragged sizes need no masking - only finite statistics, which
 // the stats array (padded to whole query blocks) always holds.
 //
-// TMEM (512 columns): T0 [0,128) S or S^T, T1 [128,256) dP or dP^T, acc0 [256,384), acc1 [384,512). The fp16 P^T / dS^T
-// go over the first 64 columns of T0 / T1: each of the two warps that share a lane quarter first loads its 64 columns of
-// both, the pair meets at a named barrier, and only then either of them stores. One product pair in flight per thread
-// block (the S products of block i+1 wait for the dV / dK products of block i): simple and correct first, ~40 % of the
-// tensor pipe; the forward kernel's two-stream overlap is the known next step.
+// TMEM (512 columns): T0 [0,128) S or S^T, T1 [128,256) dP or dP^T, acc0 [256,384), acc1 [384,512). Measured on B200 (clock
+// stamps in a private build): the kernel is bound by the thread that issues the products - an SS product costs ~650 cycles
+// per 128x128x128 however its N is cut (the A operand is re-read from shared memory for every instruction), the softmax
+// warps need ~1100 per step. So the products keep N = 128 and the step is software-pipelined across the two products instead:
+//   softmax phase 1: S^T ready -> P^T = 2^(c S^T - L) (kept in registers), fp16 P^T stored, "P0" signalled;
+//   softmax phase 2: dP^T ready -> dS^T = P^T (dP^T - D) stored, "P1" signalled;
+//   issue order:     [P0] dV += P^T dO | S^T of the next step | [P1] dK += dS^T Q | dP^T of the next step
+// so that phase 1 of the next step runs under the dK and dP^T products and phase 2 under the dV and S^T products of the step
+// after (in-order execution of one thread's tcgen05.mma keeps a product from overwriting what the one before still reads).
+// BWD_DQ has one accumulating product: S of the next step is issued as soon as the softmax warps have read S (phase 1
+// signals that), under phase 2. Each of the eight softmax warps (lane quarter x column half) owns 64 columns of T0 / T1 and
+// writes its fp16 results over the first 32 of those same columns, so no warp overwrites what another still has to read.
 #pragma once
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -56,7 +63,7 @@ struct BwdParams {
     uint32_t* status;
 };
 
-enum { BB_RES = 0, BB_XFULL = 1, BB_XEMPTY = 3, BB_TFULL = 5, BB_PFULL = 6, BB_ACC = 7, BB_COUNT = 8 };
+enum { BB_RES = 0, BB_XFULL = 1, BB_XEMPTY = 3, BB_TFULL = 5, BB_PFULL = 7, BB_ACC = 9, BB_COUNT = 10 };   // TFULL/PFULL: [0] first product / phase 1, [1] second
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -107,7 +114,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int n_it = MODE == BWD_DKV ? nqb : (p.Tk + BN - 1) / BN;
 
     if (tid == 0) {
-        for (int i = 0; i < BB_COUNT; i++) mbar_init(bar(i), i == BB_PFULL ? 8u : 1u);
+        for (int i = 0; i < BB_COUNT; i++) mbar_init(bar(i), (i == BB_PFULL || i == BB_PFULL + 1) ? 8u : 1u);   // P: one arrival per softmax warp
         *abort_flag = 0u;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -139,7 +146,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
             const int st = it & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_TFULL), (uint32_t)it & 1u, abort_flag));
+            // ---- phase 1: P = 2^(c S - L) for this warp's 64 columns
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_TFULL + 0), (uint32_t)it & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
             const float* sStats = reinterpret_cast<const float*>(smem_raw + 2 * TILE_BYTES + st * BWD_STAGE_BYTES + 2 * TILE_BYTES);
@@ -147,44 +155,68 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_XFULL + st), ((uint32_t)it >> 1) & 1u, abort_flag));   // products read them)
                 if (!ok) break;
             }
-            uint32_t s0[32], s1[32], d0[32], d1[32];
-            tmem_ld32(tT0 + (uint32_t)(half * 64), s0);
-            tmem_ld32(tT0 + (uint32_t)(half * 64 + 32), s1);
-            tmem_ld32(tT1 + (uint32_t)(half * 64), d0);
-            tmem_ld32(tT1 + (uint32_t)(half * 64 + 32), d1);
-            tmem_wait_ld();
-            reg_fence32(s0); reg_fence32(s1); reg_fence32(d0); reg_fence32(d1);
-            // both warps of the lane quarter hold their columns: the fp16 results may now go over the first 64 columns
-            named_bar_sync(1 + quarter, 64);
-            uint32_t pk[32], dk[32];
+            float pv[64];
+            {
+                uint32_t s0[32], s1[32];
+                tmem_ld32(tT0 + (uint32_t)(half * 64), s0);
+                tmem_ld32(tT0 + (uint32_t)(half * 64 + 32), s1);
+                tmem_wait_ld();
+                reg_fence32(s0); reg_fence32(s1);
+                if (MODE == BWD_DQ) {                               // S has been read: the next step's S may be formed
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(BB_PFULL + 0));
+                }
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-#pragma unroll
-                for (int u = 0; u < 2; u++) {                       // u = 0: columns [0,32) of this warp's half, 1: [32,64)
-                    const uint32_t* sv = u ? s1 : s0;
-                    const uint32_t* dv = u ? d1 : d0;
-                    float L0 = Lr, L1 = Lr, D0 = Dr, D1 = Dr;
-                    if (MODE == BWD_DKV) {                          // per column: the query row's statistics (a broadcast read)
-                        const int col = half * 64 + u * 32 + e;
-                        const float2 l2 = *reinterpret_cast<const float2*>(sStats + col);
-                        const float2 dd = *reinterpret_cast<const float2*>(sStats + 128 + col);
-                        L0 = l2.x; L1 = l2.y; D0 = dd.x; D1 = dd.y;
+                for (int e = 0; e < 64; e += 2) {
+                    float L0 = Lr, L1 = Lr;
+                    if (MODE == BWD_DKV) {                          // per column: the query row's statistic (a broadcast read)
+                        const float2 l2 = *reinterpret_cast<const float2*>(sStats + half * 64 + e);
+                        L0 = l2.x; L1 = l2.y;
                     }
-                    const float p0 = ex2(fmaf(__uint_as_float(sv[e]), c, -L0));
-                    const float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), c, -L1));
-                    const float g0 = p0 * (__uint_as_float(dv[e]) - D0);
-                    const float g1 = p1 * (__uint_as_float(dv[e + 1]) - D1);
-                    pk[u * 16 + (e >> 1)] = pack16<DT_F16>(p0, p1);
-                    dk[u * 16 + (e >> 1)] = pack16<DT_F16>(g0, g1);
+                    const uint32_t a = e < 32 ? s0[e & 31] : s1[e & 31], bq = e < 32 ? s0[(e & 31) + 1] : s1[(e & 31) + 1];
+                    pv[e] = ex2(fmaf(__uint_as_float(a), c, -L0));
+                    pv[e + 1] = ex2(fmaf(__uint_as_float(bq), c, -L1));
                 }
             }
-            // element pair (2c, 2c+1) of the contraction index in column c: this warp's 64 elements are columns [32 half, +32)
-            if (MODE == BWD_DKV) tmem_st32(tT0 + (uint32_t)(half * 32), pk);
-            tmem_st32(tT1 + (uint32_t)(half * 32), dk);
+            if (MODE == BWD_DKV) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int e = 0; e < 32; e++) pk[e] = pack16<DT_F16>(pv[2 * e], pv[2 * e + 1]);
+                // element pair (2c, 2c+1) of this warp's contraction range in column c of its OWN columns: only what this
+                // thread has just read is overwritten
+                tmem_st32(tT0 + (uint32_t)(half * 64), pk);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BB_PFULL + 0));
+            }
+            // ---- phase 2: dS = P (dP - D)
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_TFULL + 1), (uint32_t)it & 1u, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+            {
+                uint32_t d0[32], d1[32], dk[32];
+                tmem_ld32(tT1 + (uint32_t)(half * 64), d0);
+                tmem_ld32(tT1 + (uint32_t)(half * 64 + 32), d1);
+                tmem_wait_ld();
+                reg_fence32(d0); reg_fence32(d1);
+#pragma unroll
+                for (int e = 0; e < 64; e += 2) {
+                    float D0 = Dr, D1 = Dr;
+                    if (MODE == BWD_DKV) {
+                        const float2 dd = *reinterpret_cast<const float2*>(sStats + 128 + half * 64 + e);
+                        D0 = dd.x; D1 = dd.y;
+                    }
+                    const uint32_t a = e < 32 ? d0[e & 31] : d1[e & 31], bq = e < 32 ? d0[(e & 31) + 1] : d1[(e & 31) + 1];
+                    dk[e >> 1] = pack16<DT_F16>(pv[e] * (__uint_as_float(a) - D0), pv[e + 1] * (__uint_as_float(bq) - D1));
+                }
+                tmem_st32(tT1 + (uint32_t)(half * 64), dk);
+            }
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BB_PFULL));
+            if (lane == 0) mbar_arrive(bar(BB_PFULL + 1));
         }
         // ------------------------------------------------------------------ epilogue: accumulators -> global, one row per thread
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_ACC), 0u, abort_flag));
@@ -227,35 +259,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     mma_ss_w<1>(d_tmem, alo + off, blo + off, DESC_HI, IDESC_T);
                 }
             };
-            auto issue_A = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_saddr, bool first) {
+            // the fp16 A operand sits in two pieces: contraction elements [64 hh, 64 hh + 64) at columns [64 hh, 64 hh + 32)
+            auto issue_A = [&](uint32_t d_tmem, uint32_t a_region, uint32_t b_saddr, bool first) {
                 const uint32_t blo = smem_desc_lo(b_saddr, HALF_BYTES);
-                if (first) mma_ts_w<0>(d_tmem, a_tmem, blo, DESC_HI, IDESC_A);
-                else mma_ts_w<1>(d_tmem, a_tmem, blo, DESC_HI, IDESC_A);
 #pragma unroll
-                for (int kk = 1; kk < 8; kk++) mma_ts_w<1>(d_tmem, a_tmem + (uint32_t)(kk * 8), blo + (uint32_t)(kk * 128), DESC_HI, IDESC_A);
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint32_t a_t = a_region + (uint32_t)(64 * (kk >> 2) + 8 * (kk & 3));
+                    if (kk == 0 && first) mma_ts_w<0>(d_tmem, a_t, blo, DESC_HI, IDESC_A);
+                    else mma_ts_w<1>(d_tmem, a_t, blo + (uint32_t)(kk * 128), DESC_HI, IDESC_A);
+                }
             };
+            auto xaddr = [&](int st) { return sX + (uint32_t)st * BWD_STAGE_BYTES; };
             bool good = mbar_wait(bar(BB_RES), 0u, abort_flag);
+            if (good) {
+                good = mbar_wait(bar(BB_XFULL + 0), 0u, abort_flag);
+                if (good) {
+                    tc_fence_after();
+                    issue_T(tmem_base, sR0, xaddr(0));
+                    tc_commit(bar(BB_TFULL + 0));
+                    issue_T(tmem_base + 128u, sR1, xaddr(0) + TILE_BYTES);
+                    tc_commit(bar(BB_TFULL + 1));
+                }
+            }
             for (int it = 0; it < n_it && good; ++it) {
                 const int st = it & 1;
-                const uint32_t x0 = sX + st * BWD_STAGE_BYTES, x1 = x0 + TILE_BYTES;
-                good = mbar_wait(bar(BB_XFULL + st), ((uint32_t)it >> 1) & 1u, abort_flag);
+                const uint32_t x0 = xaddr(st), x1 = x0 + TILE_BYTES;
+                const bool more = it + 1 < n_it;
+                // phase 1 of this step is over: P^T is stored (BWD_DKV) / S has been read (BWD_DQ)
+                good = mbar_wait(bar(BB_PFULL + 0), (uint32_t)it & 1u, abort_flag);
                 if (!good) break;
                 tc_fence_after();
-                // T0 and T1 are free: the products that read the fp16 data in them were issued before these (same thread, in
-                // order), and the softmax warps were done with them before they signalled those products
-                issue_T(tmem_base, sR0, x0);
-                issue_T(tmem_base + 128u, sR1, x1);
-                tc_commit(bar(BB_TFULL));
-                good = mbar_wait(bar(BB_PFULL), (uint32_t)it & 1u, abort_flag);
-                if (!good) break;
-                tc_fence_after();
-                if (MODE == BWD_DKV) {
-                    issue_A(tmem_base + 256u, tmem_base, x1, it == 0);             // dV += P^T dO_i
-                    issue_A(tmem_base + 384u, tmem_base + 128u, x0, it == 0);      // dK += dS^T Q_i
-                } else {
-                    issue_A(tmem_base + 256u, tmem_base + 128u, x0, it == 0);      // dQ += dS K_j
+                if (MODE == BWD_DKV) issue_A(tmem_base + 256u, tmem_base, x1, it == 0);               // dV += P^T dO_i
+                if (more) {
+                    good = mbar_wait(bar(BB_XFULL + (st ^ 1)), ((uint32_t)(it + 1) >> 1) & 1u, abort_flag);
+                    if (!good) break;
+                    tc_fence_after();
+                    issue_T(tmem_base, sR0, xaddr(st ^ 1));                                           // the next step's S / S^T
+                    tc_commit(bar(BB_TFULL + 0));
                 }
-                tc_commit(bar(BB_XEMPTY + st));                                    // the stage may be reloaded
+                good = mbar_wait(bar(BB_PFULL + 1), (uint32_t)it & 1u, abort_flag);
+                if (!good) break;
+                tc_fence_after();
+                if (MODE == BWD_DKV) issue_A(tmem_base + 384u, tmem_base + 128u, x0, it == 0);        // dK += dS^T Q_i
+                else issue_A(tmem_base + 256u, tmem_base + 128u, x0, it == 0);                        // dQ += dS K_j
+                tc_commit(bar(BB_XEMPTY + st));                                    // every product on this stage has been issued
+                if (more) {
+                    issue_T(tmem_base + 128u, sR1, xaddr(st ^ 1) + TILE_BYTES);                       // the next step's dP / dP^T
+                    tc_commit(bar(BB_TFULL + 1));
+                }
             }
             if (good) tc_commit(bar(BB_ACC));
         } else if (warp == 9 && lane == 0) {

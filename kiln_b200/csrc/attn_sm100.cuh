@@ -258,35 +258,11 @@ __device__ __forceinline__ int seg_entries(int mode, int jb, const int (&je)[2])
     return (je[0] > 0 ? 2 * je[0] : 0) + (je[1] > 0 ? 2 * je[1] : 0);
 }
 
-// Head-split runs: the [B][Tq][H*128] window of every GPU's gathered buffer that this GPU's heads fill (its own included),
-// laid out like tmO, so that a finished tile leaves as one pair of bulk tensor stores per GPU - over NVLink for the peers.
-struct alignas(64) PeerMaps {
-    CUtensorMap m[MAX_PEERS];
-};
-
-// One thread: count a pushed tile in on every GPU's arrival counter, after the bulk stores this thread issued have completed
-// (release at system scope once the async-proxy writes are done). Kept out of line: it runs on head-split launches only and
-// must not cost the callers registers on the others.
-__device__ __noinline__ void push_count_in(unsigned long long* const* ctr, int n_peers) {
-    tma_store_wait_all();
-    asm volatile("fence.proxy.async;" ::: "memory");
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
-    for (int pe = 0; pe < n_peers; pe++) asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(ctr[pe]), "l"(1ull) : "memory");
-}
-// One thread: a staged [128][128] 16-bit tile (two swizzled halves at `tile`) into every GPU's gathered buffer
-__device__ __noinline__ void push_tile(const PeerMaps* maps, int n_peers, uint32_t tile, int col, int row, int b) {
-    for (int pe = 0; pe < n_peers; pe++) {
-        tma_store_3d(&maps->m[pe], tile, col, row, b);
-        tma_store_3d(&maps->m[pe], tile + 16384u, col + 64, row, b);
-    }
-}
-
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK0,
                 const __grid_constant__ CUtensorMap tmV0, const __grid_constant__ CUtensorMap tmK1,
-                const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const __grid_constant__ PeerMaps tmP,
-                const __grid_constant__ AttnParams p) {
+                const __grid_constant__ CUtensorMap tmV1, const __grid_constant__ CUtensorMap tmO, const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];         // 128-byte swizzle wants 1024-byte aligned tiles
     const uint32_t base = smem_u32(smem_raw);
     uint8_t* const smem = smem_raw;
@@ -363,14 +339,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t norms_cnt = 0;                                    // parked items whose norms have been taken over so far
         float* const f_tot = fbuf + 256;                           // [2][128] norm totals of the parked item, written by warp 11
         constexpr int NORM_STRIDE = 512;                           // floats per (query tile, head) in the norm scratch
-        // Head split, MODE_PAIR: the thread that issued a tile's bulk stores to the other GPUs counts the tile in on every GPU's
-        // arrival counter once those stores have completed (release at system scope after the async-proxy writes are done).
-        bool push_pending = false;
-        auto push_signal = [&]() {
-            if (!push_pending) return;
-            push_count_in(p.ctr_peers, p.n_peers);
-            push_pending = false;
-        };
         // one thread waits (bounded) until all heads of query tile qt have published their norms; result in wg_here[0]
         auto nag_wait_norms = [&](int qt) {
             if (tid == 0) {
@@ -430,13 +398,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                     *reinterpret_cast<uint4*>(to + ((cc ^ (t & 7)) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                fence_proxy_async_smem();
+                if (p.n_peers == 0) fence_proxy_async_smem();
             }
             named_bar_sync(1, 256);                                           // the blended tile is complete, the parking tiles are read out
-            // the loader warp stores the tile (bulk tensor stores, rows past Tq clipped by the tensor map; on head-split runs
-            // one pair per GPU, into every gathered buffer) before it loads the next Q into the same space: nobody here waits
-            // for the store to read the tile
-            if (tid == 0) { sm_store[1] = (uint32_t)pend_h; sm_store[2] = (uint32_t)pend_q0; sm_store[0] = pend_go ? 1u : 0u; }
+            if (p.n_peers == 0) {
+                // the loader warp stores the tile (bulk tensor store, rows past Tq clipped by the tensor map) before it loads the
+                // next Q into the same space: nobody here waits for the store to read the tile
+                if (tid == 0) { sm_store[1] = (uint32_t)pend_h; sm_store[2] = (uint32_t)pend_q0; sm_store[0] = pend_go ? 1u : 0u; }
+            } else {
+                // head split: each of the eight warps copies 16 rows out as whole 256-byte rows to every GPU's buffer
+                if (pend_go) {
+                    const int lr0 = 16 * warp;
+                    const int row0 = pend_q0 + lr0;
+                    const int nrow = p.Tq - row0;                             // rows of this warp that exist (warp-uniform)
+                    uint2 vals[16];
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++)
+                        vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                   ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                    const size_t off = (size_t)row0 * (size_t)p.ldo + (size_t)(p.col0 + pend_h * HD) + (size_t)lane * 4;
+                    for (int pe = 0; pe < p.n_peers; pe++) {
+                        OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                        for (int rr = 0; rr < 16; rr++)
+                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
+                    }
+                    __threadfence_system();                                   // the tile is visible to every GPU before the arrival
+                }
+                named_bar_sync(1, 256);                                       // every warp is done with the parked tile
+                if (pend_go && tid < p.n_peers) atomicAdd_system(p.ctr_peers[tid], 1ull);
+                if (tid == 0) sm_store[0] = 0u;
+            }
             pend_valid = false;
         };
 
@@ -721,18 +713,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                         tma_store_wait_read();                   // the staging space may be overwritten
                                     }
                                 } else {
-                                    // head-split runs: the same pair of bulk stores into every GPU's gathered buffer. The arrival on
-                                    // a GPU's counter has to follow the COMPLETION of the stores; nobody waits for that here: the
-                                    // tile pushed last time is counted in now (its stores have had a whole item to finish)
-                                    fence_proxy_async_smem();
                                     named_bar_sync(3 + i, 128);                  // the staged tile is complete
-                                    if (t == 0) {
-                                        push_signal();
-                                        push_tile(&tmP, p.n_peers, smem_u32(stage), it.h * HD, it.q0 + i * BM, it.b);
-                                        tma_store_commit();
-                                        tma_store_wait_read();                   // the staging space may be overwritten
-                                        push_pending = true;
+                                    // head-split runs: each warp copies 32 rows out as whole 256-byte rows to every peer buffer
+                                    // (all shared-memory reads first, then the stores)
+                                    const int lr0 = 32 * (warp & 3);
+                                    const int row0 = it.q0 + i * BM + lr0;
+                                    const int nrow = p.Tq - row0;                // rows of this warp that exist (warp-uniform)
+                                    uint2 vals[32];
+#pragma unroll
+                                    for (int rr = 0; rr < 32; rr++)
+                                        vals[rr] = *reinterpret_cast<const uint2*>(stage + (lane >> 4) * HALF_BYTES + (lr0 + rr) * 128 +
+                                                                                   ((((lane >> 1) & 7) ^ ((lr0 + rr) & 7)) << 4) + (lane & 1) * 8);
+                                    const size_t off = ((size_t)it.b * p.Tq + (size_t)row0) * (size_t)p.ldo + (size_t)(p.col0 + it.h * HD) + (size_t)lane * 4;
+                                    for (int pe = 0; pe < p.n_peers; pe++) {
+                                        OutT* g = reinterpret_cast<OutT*>(p.out_peers[pe]) + off;
+#pragma unroll
+                                        for (int rr = 0; rr < 32; rr++)
+                                            if (rr < nrow) *reinterpret_cast<uint2*>(g + (size_t)rr * (size_t)p.ldo) = vals[rr];
                                     }
+                                    __threadfence_system();                      // the tile is visible to every GPU before the arrival
+                                    named_bar_sync(3 + i, 128);                  // every warp is done with the staging tile
+                                    if (t < p.n_peers) atomicAdd_system(p.ctr_peers[t], 1ull);
                                 }
                             } else {
                                 const int row = it.q0 + i * BM + t;
@@ -918,7 +919,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (tid == 0 && last) mbar_arrive(bar(BAR_QEMPTY + 0));
         }
         if (lane == 0) tma_store_wait_all();                              // bulk stores issued by this thread have landed
-        push_signal();                                                    // head split: the last tile this thread pushed
         tc_fence_before();
         cta_sync();
     } else {
@@ -1060,24 +1060,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tma_load_3d(dst + HALF_BYTES, tm, mbar, it.h * HD + 64, row0, bb);
                 };
                 // MODE_NAG, 16-bit output: the softmax threads leave the blended tile of the item before in the Q tile; store it
-                // Head split: a tile is counted in on every GPU's arrival counter once its stores have completed, which this
-                // thread only checks when it next comes by (the stores have had a whole item to finish by then) or at the end.
-                bool push_pending = false;
-                auto push_signal = [&]() {
-                    if (!push_pending) return;
-                    push_count_in(p.ctr_peers, p.n_peers);
-                    push_pending = false;
-                };
                 auto store_staged = [&]() {
                     if (MODE == MODE_NAG && sizeof(OutT) == 2 && sm_store[0]) {
-                        if (p.n_peers == 0) {
-                            tma_store_3d(&tmO, sQ, (int)sm_store[1] * HD, (int)sm_store[2], 0);
-                            tma_store_3d(&tmO, sQ + HALF_BYTES, (int)sm_store[1] * HD + 64, (int)sm_store[2], 0);
-                        } else {
-                            push_signal();
-                            push_tile(&tmP, p.n_peers, sQ, (int)sm_store[1] * HD, (int)sm_store[2], 0);
-                            push_pending = true;
-                        }
+                        tma_store_3d(&tmO, sQ, (int)sm_store[1] * HD, (int)sm_store[2], 0);
+                        tma_store_3d(&tmO, sQ + HALF_BYTES, (int)sm_store[1] * HD + 64, (int)sm_store[2], 0);
                         tma_store_commit();
                         tma_store_wait_read();                                // the tile has been read: Q may land on it
                     }
@@ -1140,7 +1126,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         if (good) store_staged();
                     }
                     tma_store_wait_all();
-                    push_signal();
                 }
                 // on failure, let the copies already requested land before the CTA's shared memory goes away: a bounded wait on
                 // the FULL barrier of every ring slot and Q tile that still has a request outstanding

@@ -145,4 +145,5 @@ def test_reference_attention_bwd_reproduces_fixture_and_matches_oracle_and_ours(
         for gname, lv, oc, mine in zip(("dq", "dk", "dv"), live, orc, outs):
             np.testing.assert_allclose(lv[:, :n], golden[f"{name}/{gname}"], rtol=0, atol=1e-5)
             np.testing.assert_allclose(oc, lv, rtol=0, atol=2e-5 * max(1.0, float(np.abs(lv).max())))
-            assert_close(mine.cpu().numpy(), lv, f"{name}/{gname}: kb_attn_bwd vs live attention_bwd")
+            # relative to the gradient's scale: the reference reads unrounded fp32 inputs (tests/test_attn_bwd_gpu.py explains)
+            assert_close(mine.cpu().numpy(), lv, f"{name}/{gname}: kb_attn_bwd vs live attention_bwd", max_abs=2e-3 * max(1.0, float(np.abs(lv).max())))

@@ -83,3 +83,35 @@ def test_attention16_vs_reference_flash(kb, ref, Tq, Tk, npad):
           f"activations (staging pass included), reference tfa::k_flash {theirs:.1f} us; {fl / ours / 1e6:.0f} vs {fl / theirs / 1e6:.0f} TFLOP/s")
     if Tk >= 1024:
         assert theirs > 2.0 * ours32
+
+
+@pytest.mark.parametrize("Tq,Tk,npad", [(4096, 4096, 0), (1536, 1536, 0), (4096, 77, 435)], ids=["self_4096", "self_1536", "cross_77_of_512"])
+def test_attention_bwd_vs_reference(kb, ref, Tq, Tk, npad):
+    """kb_attn_bwd (all its launches, fp32 inputs as the trainer holds them) beside the reference's attention_bwd
+    (engine/src/train.cu:216-242: fp32 cuBLAS SGEMMs with P and dP in the arena) on the same GPU."""
+    H, D = 16, 2048
+    ref.kref_engine_init.argtypes = [ctypes.c_size_t, ctypes.c_char_p, ctypes.c_int]
+    ref.kref_attention_bwd.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3 + [ctypes.c_char_p, ctypes.c_int]
+    err = ctypes.create_string_buffer(512)
+    assert ref.kref_engine_init(3 << 30, err, 512) == 0, err.value
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    rn = lambda r: torch.randn(r, D, device="cuda", generator=g)
+    q, k, v, do = rn(Tq), rn(Tk), rn(Tk), rn(Tq)
+    mine = [torch.empty(Tq, D, device="cuda"), torch.empty(Tk, D, device="cuda"), torch.empty(Tk, D, device="cuda")]
+    theirs = [torch.empty_like(t) for t in mine]
+    ws = torch.empty(kb.lib().kb_attn_bwd_workspace_bytes(1, Tq, Tk, H, kb.KB_F32), dtype=torch.uint8, device="cuda")
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def run_ref():
+        assert ref.kref_attention_bwd(P(theirs[0]), P(theirs[1]), P(theirs[2]), P(q), P(k), P(v), P(do), Tq, Tk, npad, err, 512) == 0, err.value
+
+    t_ours = _timed(lambda: kb.attn_bwd(mine[0], mine[1], mine[2], q, k, v, do, 1, Tq, Tk, npad, H, workspace=ws))
+    t_ref = _timed(run_ref, warm=1, reps=3)
+    assert kb.check_status() == 0
+    flop = 10.0 * Tq * Tk * 128 * H
+    worst = max(float((a - b).abs().max() / b.abs().max().clamp_min(1.0)) for a, b in zip(mine, theirs))
+    print(f"\nattention backward {Tq}x{Tk} (npad {npad}): ours {t_ours:.1f} us ({flop / t_ours / 1e6:.0f} TFLOP/s of the five products), "
+          f"reference {t_ref:.1f} us, {t_ref / t_ours:.1f}x; worst difference relative to the gradient's scale {worst:.2e}")
+    assert t_ours < t_ref
+    assert worst <= 2e-3
