@@ -175,6 +175,14 @@ void cross_kv16(__half* k16, __half* v16, int ldy, const float* ctx, int L, cons
           "cross_kv16");
 }
 
+void attention_bwd(float* dq, float* dk, float* dv, const float* q, const float* k, const float* v, const float* dout, int Tq, int Tk, int npad,
+                   int H) {
+    const int D = H * 128;
+    check(kb_attn_bwd(dq, dk, dv, q, k, v, dout, 1, Tq, Tk, npad, H, D, D, D, D, D, D, D, KB_F32, g_ctx.workspace, g_ctx.workspace_bytes,
+                      g_ctx.stream),
+          "attention_bwd");
+}
+
 }  // namespace kiln_b200
 
 // C trampolines so the shim can be exercised from the test-suite without a C++ test runner:
@@ -300,6 +308,12 @@ int kbh_cross_kv16(void* k16, void* v16, int ldy, const float* ctx, int L, const
         Wk.p = (const __half*)a.wk; Wv.p = (const __half*)a.wv; Wk.rows = Wv.rows = a.rows; Wk.cols = Wv.cols = a.cols;
         kiln_b200::cross_kv16((__half*)a.k, (__half*)a.v, a.ldy, a.ctx, a.L, Wk, Wv, a.kw, a.eps);
     }, &a);
+}
+struct AB { float *dq, *dk, *dv; const float *q, *k, *v, *g; int Tq, Tk, npad, H; };
+int kbh_attention_bwd(float* dq, float* dk, float* dv, const float* q, const float* k, const float* v, const float* dout, int Tq, int Tk, int npad,
+                      int H, char* err, int n) {
+    AB a{dq, dk, dv, q, k, v, dout, Tq, Tk, npad, H};
+    return guard(err, n, [](void* p) { AB& a = *(AB*)p; kiln_b200::attention_bwd(a.dq, a.dk, a.dv, a.q, a.k, a.v, a.g, a.Tq, a.Tk, a.npad, a.H); }, &a);
 }
 // the exact-path hook: a stand-in "engine path" that only records that it was reached
 static int g_exact_calls = 0;

@@ -102,4 +102,10 @@ void linear16_qkv(__half* q, __half* k, __half* v, int ldy, const __half* x16, i
 void cross_kv16(__half* k16, __half* v16, int ldy, const float* ctx, int L, const Weight16& Wk, const Weight16& Wv, const uint16_t* kn_w_bf16,
                 float eps);
 
+// The trainer's exact attention backward (attention_bwd, engine/src/train.cu:216-242; an anonymous-namespace function there, with
+// D = 2048 fixed): q, dout [Tq, H*128], k, v [Tk, H*128] fp32 rows -> dq, dk, dv (written). npad zero keys of score 0 join the
+// softmax. Nothing of size Tq x Tk is materialised; scratch comes from the context's workspace (kb_attn_bwd_workspace_bytes).
+void attention_bwd(float* dq, float* dk, float* dv, const float* q, const float* k, const float* v, const float* dout, int Tq, int Tk, int npad,
+                   int H = 16);
+
 }  // namespace kiln_b200

@@ -282,3 +282,17 @@ def test_cross_kv16_then_nag_attention_on_the_cache(shim):
     v_ref = oracle.linear16(x16, wv, 1)
     assert np.all(np.abs(k16.float().cpu().numpy() - k_ref) <= 2.0 ** -10 * np.abs(k_ref) + 1e-4)
     assert np.all(np.abs(v16.float().cpu().numpy() - v_ref) <= 2.0 ** -10 * np.abs(v_ref) + 1e-4)
+
+
+def test_attention_bwd_through_the_shim(shim):
+    """attention_bwd with the trainer's signature (engine/src/train.cu:216): fp32 rows in and out, scratch from the context."""
+    Tq, Tk, npad, H = 150, 26, 486, 2
+    D = H * 128
+    q, k = (oracle.round16(oracle.randn(940 + i, r * D) * np.float32(1.5), 0).reshape(r, D) for i, r in enumerate((Tq, Tk)))
+    v, do = (oracle.round16(oracle.randn(942 + i, r * D), 0).reshape(r, D) for i, r in enumerate((Tk, Tq)))
+    outs = [torch.full((r, D), float("nan"), device="cuda") for r in (Tq, Tk, Tk)]
+    err = ctypes.create_string_buffer(256)
+    assert shim.kbh_attention_bwd(P(outs[0]), P(outs[1]), P(outs[2]), P(dev(q)), P(dev(k)), P(dev(v)), P(dev(do)), Tq, Tk, npad, H, err, 256) == 0, err.value
+    torch.cuda.synchronize()
+    for name, o, r in zip(("dq", "dk", "dv"), outs, oracle.attention_bwd(q, k, v, do, H, npad)):
+        assert_close(o.cpu().numpy(), r, f"shim attention_bwd {name}")
