@@ -742,6 +742,27 @@ def linear_cases(a):
                 torch.matmul(xs[it[0]], wts[it[0]].T, out=c)
             us = _timed_us(mm, a.warm, a.reps)
             print(f"  cuBLAS (torch.matmul) fp16: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
+        if a.lora_rank > 0:                                 # the engine's unmerged LoRA path: t = x A_cat^T, then the layer with the second product
+            R = a.lora_rank
+            acat, bcat = rn(R, K, 0.02), rn(N, R, 0.02)
+            t = torch.empty(M, R, device="cuda", dtype=torch.float16)
+
+            def with_lora():
+                it[0] = (it[0] + 1) % nset
+                ops.linear16(t, xs[it[0]], acat, ops.EPI_F16)
+                ops.linear16(c, xs[it[0]], wts[it[0]], epi, lora=(t, bcat), **kw)
+            us = _timed_us(with_lora, a.warm, a.reps)
+            ops.linear16(t, xs[0], acat, ops.EPI_F16)
+            us_down = _timed_us(lambda: ops.linear16(t, xs[0], acat, ops.EPI_F16), a.warm, a.reps)
+            print(f"  with a stacked LoRA rank of {R} (down-projection launch + second product): {us:.1f} us/call; the down-projection alone {us_down:.1f} us")
+        if a.ctx > 0 and a.cross_kv:                        # the cross-attention K/V producer on a [ctx, 1024] fp32 context
+            ctx = torch.randn(a.ctx, 1024, device="cuda", generator=g)
+            wk, wv = rn(2048, 1024, 0.03), rn(2048, 1024, 0.03)
+            k16 = torch.empty(a.ctx, 2048, device="cuda", dtype=torch.float16)
+            v16 = torch.empty_like(k16)
+            wsx = torch.empty(a.ctx * 1024 * 2, dtype=torch.uint8, device="cuda")
+            us = _timed_us(lambda: ops.cross_kv(k16, v16, ctx, wk, wv, kn_w=hw, workspace=wsx), a.warm, a.reps)
+            print(f"  cross-attention K/V producer, {a.ctx} x 1024 fp32 context -> fp16 K (normalised), V [{a.ctx}, 2048]: {us:.1f} us/call (two launches)")
         return
     D = H * 128
     x = rn(T, D)
@@ -799,6 +820,8 @@ def main():
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16", "f32"])
     ap.add_argument("--norm", action="store_true", help="Q/K RMSNorm (+ RoPE for self) through the staging pre-pass")
     ap.add_argument("--cublas", action="store_true", help="linear: also time torch.matmul on the same operands")
+    ap.add_argument("--lora-rank", type=int, default=0, help="linear: also time the layer with a stacked LoRA of this rank")
+    ap.add_argument("--cross-kv", action="store_true", help="linear: also time kb_cross_kv on a [--ctx, 1024] context")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--warm", type=int, default=2)
     args = ap.parse_args()

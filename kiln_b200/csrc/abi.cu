@@ -93,8 +93,7 @@ int init_device(DeviceState& st, int dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     int rc;
-    if ((rc = set_smem(attn_bwd_kernel<BWD_DKV>, BWD_SMEM))) return rc;
-    if ((rc = set_smem(attn_bwd_kernel<BWD_DQ>, BWD_SMEM))) return rc;
+    if ((rc = set_smem(attn_bwd_kernel, BWD_SMEM))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __half>, ATTN_SMEM_PAIR))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, __nv_bfloat16>, ATTN_SMEM_PAIR))) return rc;
     if ((rc = set_smem(attn_fwd_kernel<MODE_PAIR, float>, ATTN_SMEM_PAIR))) return rc;
@@ -796,11 +795,12 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
     p.stats = stats; p.scale_log2 = SCALE_LOG2; p.scale = 0.08838834764831845f;
     p.status = st->status;
     ProfScope ps(st, KB_PROF_ATTENTION, stream);
+    BwdParams pq = p;
     p.out0 = static_cast<float*>(dv); p.ld0 = ld_dv; p.out1 = static_cast<float*>(dk); p.ld1 = ld_dk;
-    attn_bwd_kernel<BWD_DKV><<<dim3((unsigned)((Tk + 127) / 128), (unsigned)H, (unsigned)B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
-    if (cudaGetLastError() != cudaSuccess) return KB_ERR_CUDA;
-    p.out0 = static_cast<float*>(dq); p.ld0 = ld_dq; p.out1 = nullptr; p.ld1 = 0;
-    attn_bwd_kernel<BWD_DQ><<<dim3((unsigned)((Tq + 127) / 128), (unsigned)H, (unsigned)B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
+    pq.out0 = static_cast<float*>(dq); pq.ld0 = ld_dq; pq.out1 = nullptr; pq.ld1 = 0;
+    const long long n_dkv = (long long)B * H * ((Tk + 127) / 128), n_dq = (long long)B * H * ((Tq + 127) / 128);
+    if (n_dkv + n_dq > 0x7fffffffLL) return KB_ERR_SHAPE;
+    attn_bwd_kernel<<<(unsigned)(n_dkv + n_dq), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p, pq, (int)n_dkv);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 
