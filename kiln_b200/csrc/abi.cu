@@ -732,7 +732,7 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
 namespace {
 size_t bwd_stats_bytes(int B, int Tq, int H) { return align256((size_t)B * H * ((Tq + 127) / 128) * 256 * sizeof(float)); }
 size_t bwd_fixed_bytes(int B, int Tq, int Tk, int H, int dtype) {
-    size_t n = bwd_stats_bytes(B, Tq, H) + align256((size_t)B * Tq * H * 128 * sizeof(float));             // statistics, O (fp32)
+    size_t n = bwd_stats_bytes(B, Tq, H) + align256((size_t)B * Tq * H * 128 * 2);                         // statistics, O (fp16)
     if (dtype != KB_F16) n += 2 * align256((size_t)B * Tq * H * 128 * 2) + 2 * align256((size_t)B * Tk * H * 128 * 2);   // fp16 Q, dO, K, V
     return n;
 }
@@ -761,7 +761,7 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
     if ((rc = get_state(&st))) return rc;
     Stage sg{static_cast<char*>(workspace), workspace_bytes};
     float* stats = static_cast<float*>(sg.take_bytes(bwd_stats_bytes(B, Tq, H)));
-    float* o32 = static_cast<float*>(sg.take_bytes((size_t)B * Tq * H * 128 * sizeof(float)));
+    __half* o16 = static_cast<__half*>(sg.take_bytes((size_t)B * Tq * H * 128 * 2));
     const void *qq = q, *kk = k, *vv = v, *gg = dout;
     int ldq = ld_q, ldk = ld_k, ldv = ld_v, ldg = ld_do;
     PrepBatch pb;
@@ -775,15 +775,15 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
     }
     if (sg.overflow) return KB_ERR_WORKSPACE;
     if ((rc = launch_prep(st, pb, dtype, KB_F16, stream))) return rc;
-    // forward on the fp16 operands: O (fp32) for D, and L into the statistics
-    if ((rc = attn_pair(o32, qq, kk, vv, nullptr, nullptr, nullptr, nullptr, B, Tq, Tk, npad, H, ldq, ldk, ldv, H * 128, KB_F16, KB_F32, 0.f,
+    // forward on the fp16 operands: O for D, and L into the statistics
+    if ((rc = attn_pair(o16, qq, kk, vv, nullptr, nullptr, nullptr, nullptr, B, Tq, Tk, npad, H, ldq, ldk, ldv, H * 128, KB_F16, KB_F16, 0.f,
                         sg.ws, sg.left, stream, nullptr, stats)))
         return rc;
     {
         const long long warps = (long long)B * H * ((Tq + 127) / 128) * 128;
         const unsigned grid = (unsigned)((warps + 7) / 8);
         // dO as the tensor cores see it (fp16), so that the rows of dS sum to zero as exactly as the products allow
-        bwd_delta_kernel<<<grid, 256, 0, stream>>>(stats, static_cast<const __half*>(gg), ldg, o32, H * 128, B, Tq, H);
+        bwd_delta_kernel<<<grid, 256, 0, stream>>>(stats, static_cast<const __half*>(gg), ldg, o16, H * 128, B, Tq, H);
         if (cudaGetLastError() != cudaSuccess) return KB_ERR_CUDA;
     }
     CUtensorMap tq, tk, tv, tg;

@@ -8,7 +8,8 @@
 //
 // Four launches (kb_attn_bwd): the staging pre-pass (Q, K, V, dO -> fp16), the forward kernel, which also leaves
 // L_i = log2 of the softmax denominator of row i (npad zero keys included) in the "stats" array, a small kernel for
-// D_i = sum_d dO[i, d] O[i, d] (= sum_j P_ij dP_ij, what k_dsoftmax sums), and this file's kernel twice:
+// D_i = sum_d dO[i, d] O[i, d] (= sum_j P_ij dP_ij, what k_dsoftmax sums), and this file's kernel, whose thread blocks
+// play one of two roles:
 //
 //   BWD_DKV  one thread block per (key block j, head, image), query blocks i streamed through a two-stage ring:
 //              S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                      (two SS products into TMEM)
@@ -71,8 +72,9 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 }
 
 // D_i = sum_d dO[i, d] * O[i, d] per (row, head) into the stats array; one warp per (row, head), rows of whole query blocks
-// (rows past Tq get 0). dO fp16 as staged for the tensor cores, O fp32 from the forward pass.
-__global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, const float* o, int ld_o, int B, int Tq, int H) {
+// (rows past Tq get 0). dO fp16 as staged for the tensor cores, O fp16 from the forward pass (its 16-bit output path: bulk
+// tensor stores instead of per-thread fp32 row stores; the rounding moves D by ~1e-4 of the dP it is subtracted from).
+__global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, const __half* o, int ld_o, int B, int Tq, int H) {
     const int nqb = (Tq + BM - 1) / BM;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -82,9 +84,10 @@ __global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, co
     float s = 0.f;
     if (r < Tq) {
         const uint2 gv = *reinterpret_cast<const uint2*>(dout + ((size_t)b * Tq + r) * (size_t)ld_do + (size_t)h * HD + lane * 4);
-        const float4 ov = *reinterpret_cast<const float4*>(o + ((size_t)b * Tq + r) * (size_t)ld_o + (size_t)h * HD + lane * 4);
+        const uint2 ow = *reinterpret_cast<const uint2*>(o + ((size_t)b * Tq + r) * (size_t)ld_o + (size_t)h * HD + lane * 4);
         const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&gv.x)), gb = __half22float2(*reinterpret_cast<const __half2*>(&gv.y));
-        s = ga.x * ov.x + ga.y * ov.y + gb.x * ov.z + gb.y * ov.w;
+        const float2 oa = __half22float2(*reinterpret_cast<const __half2*>(&ow.x)), ob = __half22float2(*reinterpret_cast<const __half2*>(&ow.y));
+        s = ga.x * oa.x + ga.y * oa.y + gb.x * ob.x + gb.y * ob.y;
     }
     for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
     if (lane == 0) stats[(((size_t)b * H + h) * nqb + r / BM) * 256 + 128 + (r % BM)] = s;
