@@ -227,7 +227,8 @@ def run_ours(args):
             cap_stream = torch.cuda.Stream()
             cap_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(cap_stream):
-                with torch.cuda.graph(cg, stream=cap_stream):
+                # thread-local capture mode: the process group's watchdog thread may query its events meanwhile
+                with torch.cuda.graph(cg, stream=cap_stream, capture_error_mode="thread_local"):
                     eager_step()
             torch.cuda.current_stream().wait_stream(cap_stream)
             cg.replay()
