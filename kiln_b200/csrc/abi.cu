@@ -795,12 +795,23 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
     p.stats = stats; p.scale_log2 = SCALE_LOG2; p.scale = 0.08838834764831845f;
     p.status = st->status;
     ProfScope ps(st, KB_PROF_ATTENTION, stream);
-    BwdParams pq = p;
-    p.out0 = static_cast<float*>(dv); p.ld0 = ld_dv; p.out1 = static_cast<float*>(dk); p.ld1 = ld_dk;
-    pq.out0 = static_cast<float*>(dq); pq.ld0 = ld_dq; pq.out1 = nullptr; pq.ld1 = 0;
+    // fp32 [B][T][H*128] views of the three outputs, 32 columns x 32 rows per box (128-byte rows, 128-byte swizzle)
+    CUtensorMap tdq, tdk, tdv;
+    {
+        struct { CUtensorMap* tm; void* ptr; int T, ld; } outs[3] = {{&tdq, dq, Tq, ld_dq}, {&tdk, dk, Tk, ld_dk}, {&tdv, dv, Tk, ld_dv}};
+        for (auto& o : outs) {
+            const cuuint64_t dims[3] = {(cuuint64_t)H * 128, (cuuint64_t)o.T, (cuuint64_t)B};
+            const cuuint64_t strides[2] = {(cuuint64_t)o.ld * 4, (cuuint64_t)o.T * (cuuint64_t)o.ld * 4};
+            const cuuint32_t box[3] = {32, 32, 1};
+            const cuuint32_t estr[3] = {1, 1, 1};
+            if (g_encode(o.tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, o.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return KB_ERR_CUDA;
+        }
+    }
     const long long n_dkv = (long long)B * H * ((Tk + 127) / 128), n_dq = (long long)B * H * ((Tq + 127) / 128);
     if (n_dkv + n_dq > 0x7fffffffLL) return KB_ERR_SHAPE;
-    attn_bwd_kernel<<<(unsigned)(n_dkv + n_dq), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p, pq, (int)n_dkv);
+    attn_bwd_kernel<<<(unsigned)(n_dkv + n_dq), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, tdk, tdv, p, (int)n_dkv);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 

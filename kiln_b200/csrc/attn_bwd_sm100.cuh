@@ -54,9 +54,6 @@ constexpr int BWD_STAGE_BYTES = 2 * TILE_BYTES + 1024;        // two streamed ti
 constexpr int BWD_SMEM = 2 * TILE_BYTES + 2 * BWD_STAGE_BYTES + 1024;   // resident pair, two stages, control block
 
 struct BwdParams {
-    float* out0;            // BWD_DKV: dV [B*Tk, ld0]; BWD_DQ: dQ [B*Tq, ld0]
-    float* out1;            // BWD_DKV: dK [B*Tk, ld1]
-    int ld0, ld1;
     int B, H, Tq, Tk;
     const float* stats;     // [B][H][ceil(Tq/128)][2][128]: L (log2 of the softmax denominator, in units of c * score), then D
     float scale_log2;       // c = log2(e) / sqrt(128)
@@ -96,7 +93,8 @@ __global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, co
 // One thread block's work in either role: (blk, h, b) = (key block, head, image) for BWD_DKV, (query block, head, image) for BWD_DQ.
 template <int MODE>
 __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmdO,
-                                              const BwdParams& p, const int blk, const int h, const int b) {
+                                              const CUtensorMap& tmOut0, const CUtensorMap& tmOut1, const BwdParams& p, const int blk, const int h,
+                                              const int b) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                                           // never seen; without it every tile would be garbage
@@ -220,29 +218,45 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(BB_PFULL + 1));
         }
-        // ------------------------------------------------------------------ epilogue: accumulators -> global, one row per thread
+        // ------------------------------------------------------------------ epilogue: accumulators -> global
+        // Each warp turns its 32 rows x 64 columns of an accumulator into two 32 x 32 fp32 boxes (128-byte rows, 128-byte
+        // swizzle) in the stage area, which is free now, and one lane hands them to bulk tensor stores: rows past the end are
+        // clipped by the tensor map. (Per-thread row stores, 32 scattered 16-byte pieces per instruction, took ~4 us per
+        // thread block here, as they did in the projection GEMM.)
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(BB_ACC), 0u, abort_flag));
         if (ok) {
             tc_fence_after();
-            const int T = MODE == BWD_DKV ? p.Tk : p.Tq;
-            const int row = blk * BM + r;
+            uint8_t* const my_stage = smem_raw + 2 * TILE_BYTES + warp * 16384;          // four 4 KiB boxes per warp
 #pragma unroll
             for (int a = 0; a < (MODE == BWD_DKV ? 2 : 1); a++) {
-                float* const out = a ? p.out1 : p.out0;
-                const int ld = a ? p.ld1 : p.ld0;
                 const float k = (MODE == BWD_DKV && a == 0) ? 1.f : p.scale;   // dV unscaled; dK and dQ carry 1/sqrt(128)
-                float* dst = out + ((size_t)b * T + (size_t)row) * (size_t)ld + (size_t)h * HD + half * 64;
 #pragma unroll
                 for (int q = 0; q < 2; q++) {
                     uint32_t o[32];
-                    float v[32];
                     tmem_ld32(tmem_base + lane_base + 256u + (uint32_t)(a * 128 + half * 64 + 32 * q), o);
                     tmem_wait_ld();
                     reg_fence32(o);
+                    uint8_t* const box = my_stage + (a * 2 + q) * 4096 + lane * 128;
 #pragma unroll
-                    for (int e = 0; e < 32; e++) v[e] = __uint_as_float(o[e]) * k;
-                    if (row < T) store32<float>(dst + 32 * q, v);
+                    for (int cc = 0; cc < 8; cc++)
+                        *reinterpret_cast<float4*>(box + ((cc ^ (lane & 7)) << 4)) =
+                            make_float4(__uint_as_float(o[4 * cc]) * k, __uint_as_float(o[4 * cc + 1]) * k, __uint_as_float(o[4 * cc + 2]) * k,
+                                        __uint_as_float(o[4 * cc + 3]) * k);
                 }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                const int row0 = blk * BM + quarter * 32;
+                if (row0 < (MODE == BWD_DKV ? p.Tk : p.Tq)) {
+#pragma unroll
+                    for (int a = 0; a < (MODE == BWD_DKV ? 2 : 1); a++)
+#pragma unroll
+                        for (int q = 0; q < 2; q++)
+                            tma_store_3d(a ? &tmOut1 : &tmOut0, smem_u32(my_stage + (a * 2 + q) * 4096), h * HD + half * 64 + 32 * q, row0, b);
+                    tma_store_commit();
+                }
+                tma_store_wait_all();                                       // the stage area goes away with the thread block
             }
         }
     } else {
@@ -354,15 +368,15 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
 // dK/dV blocks leaves idle: 2 x 512 blocks at the DiT size are 6.9 rounds on 148 SMs instead of 3.46 rounds twice, each rounded up.
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ BwdParams p_dkv, const __grid_constant__ BwdParams p_dq,
-                const int n_dkv) {
-    const int nkb = (p_dkv.Tk + BN - 1) / BN, nqb = (p_dkv.Tq + BM - 1) / BM;
+                const __grid_constant__ CUtensorMap tmdO, const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+                const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ BwdParams p, const int n_dkv) {
+    const int nkb = (p.Tk + BN - 1) / BN, nqb = (p.Tq + BM - 1) / BM;
     int idx = (int)blockIdx.x;
     if (idx < n_dkv) {
-        attn_bwd_body<BWD_DKV>(tmQ, tmK, tmV, tmdO, p_dkv, idx % nkb, (idx / nkb) % p_dkv.H, idx / (nkb * p_dkv.H));
+        attn_bwd_body<BWD_DKV>(tmQ, tmK, tmV, tmdO, tmDV, tmDK, p, idx % nkb, (idx / nkb) % p.H, idx / (nkb * p.H));
     } else {
         idx -= n_dkv;
-        attn_bwd_body<BWD_DQ>(tmQ, tmK, tmV, tmdO, p_dq, idx % nqb, (idx / nqb) % p_dq.H, idx / (nqb * p_dq.H));
+        attn_bwd_body<BWD_DQ>(tmQ, tmK, tmV, tmdO, tmDQ, tmDQ, p, idx % nqb, (idx / nqb) % p.H, idx / (nqb * p.H));
     }
 }
 
