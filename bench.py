@@ -154,13 +154,81 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 4.0 * rows * T * 128 * H / dt / 1e12
     sample = f"per step: self-attention of {rows} of 4096 query tokens x 4096 keys x 16 heads of one block (fp32, two-pass, OpenMP); ms_per_step extrapolates to the full 4.81 TFLOP step"
+    gpu_ref = reference_kernels_on_gpu(args)
     line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": FLOP_STEP / (tflops * 1e12) * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD},
             "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": oracle.max_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    if gpu_ref is not None:
+        line["reference_kernels_on_this_gpu"] = gpu_ref
     print(json.dumps(line), flush=True)
+
+
+def reference_kernels_on_gpu(args):
+    """The reference has no CPU attention: its implementation of this path IS its CUDA kernels. Where those were compiled from the
+    reference tree (oracle/_ref/libkiln_ref.so) and a GPU is present, time them on this GPU in the engine's own order for one DiT
+    block (engine/src/dit.cu:464-487: rmsnorm(Q), rmsnorm(K), rope_half(Q), rope_half(K), attention16; rmsnorm(Q), attention16 to
+    the positive and to the negative context, k_nag) on the engine's fp32 activations, and report the step as 28 such blocks. An
+    extra field beside the CPU arm, not the arm's value. Returns None when the library or a GPU is missing."""
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libkiln_ref.so")
+    if not os.path.exists(ref_path):
+        return None
+    try:
+        import ctypes
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        R = ctypes.CDLL(ref_path)
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(11)
+        rn = lambda r: torch.randn(r, D, device=dev, generator=g)
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        cf = ctypes.c_float
+        nset = 6                                                   # rotating fp32 operand sets: 6 x 3 x 33.5 MB, more than L2
+        sets = [(rn(T), rn(T), rn(T), rn(T)) for _ in range(nset)]
+        ctx = [rn(L) for _ in range(4)]
+        w = (torch.ones(128, device=dev) * 1.0).to(torch.bfloat16)
+        cos_h, sin_h = cosmos_rope_table(64, 64)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+        a16 = torch.empty(T, D, device=dev, dtype=torch.float16)
+        n16 = torch.empty(T, D, device=dev, dtype=torch.float16)
+
+        def block(i):
+            q, k, v, q2 = sets[i % nset]
+            R.kref_rmsnorm(P(q), P(q), P(w), T * H, 128, cf(1e-6))
+            R.kref_rmsnorm(P(k), P(k), P(w), T * H, 128, cf(1e-6))
+            R.kref_rope_half(P(q), T, H, 128, P(cos), P(sin))
+            R.kref_rope_half(P(k), T, H, 128, P(cos), P(sin))
+            R.kref_tfa_f16(P(a16), D, P(q), D, P(k), D, P(v), D, T, T, H, 0)
+            R.kref_rmsnorm(P(q2), P(q2), P(w), T * H, 128, cf(1e-6))
+            R.kref_tfa_f16(P(a16), D, P(q2), D, P(ctx[0]), D, P(ctx[1]), D, T, L, H, 0)
+            R.kref_tfa_f16(P(n16), D, P(q2), D, P(ctx[2]), D, P(ctx[3]), D, T, L, H, 0)
+            R.kref_nag_f16(P(a16), P(n16), T, D, cf(5.0), cf(2.5), cf(0.25))
+
+        for i in range(3):
+            block(i)
+        torch.cuda.synchronize()
+        nblk = 12
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(nblk):
+            block(i)
+        e1.record()
+        torch.cuda.synchronize()
+        if R.kref_sync() != 0:
+            return None
+        ms_block = e0.elapsed_time(e1) / nblk
+        return {"kind": "reference", "ms_per_step": ms_block * BLOCKS, "value": FLOP_STEP / (ms_block * BLOCKS * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "what": "the reference's own CUDA kernels (tfa::k_flash, k_rmsnorm_warp, k_rope_half, k_nag<half>; engine/src/tcflash.cuh, "
+                        "kernels.cu, dit.cu) compiled for sm_100a, run in the engine's order on fp32 activations: %d blocks timed with CUDA "
+                        "events on the legacy stream, the step taken as %d blocks" % (nblk, BLOCKS)}
+    except Exception as e:                                          # an extra: never let it take the arm down
+        print(f"# reference kernels on the GPU: skipped ({type(e).__name__}: {e})", file=sys.stderr)
+        return None
 
 
 # ------------------------------------------------------------------------------------------------ our arm

@@ -405,11 +405,12 @@ def test_nag_benchmark_variant_qnorm_16bit_out(kb, kind, Tq, Tp, Tn, s):
             assert_close(o[rows], ref, what)
 
 
-@pytest.mark.parametrize("T,H,B,kind", [(1536, 16, 1, "f16"), (2000, 3, 1, "bf16"), (4096, 2, 1, "bf16"), (900, 5, 3, "f16")])
+@pytest.mark.parametrize("T,H,B,kind", [(2560, 16, 1, "f16"), (2000, 3, 1, "bf16"), (4096, 2, 1, "bf16"), (2000, 2, 2, "f16")])
 def test_balanced_schedule_equals_whole_items(kb, T, H, B, kind):
     """The balanced (item, key block) schedule, taken when the workspace has room for partial results, against the
     whole-items schedule of the same call without that room, and against the oracle: items cut across two or more SMs
-    (2 heads x 4096 tokens: an item spans five SMs), ragged token counts, a batch."""
+    (2 heads x 4096 tokens: an item spans five SMs), ragged token counts, a batch. (The library takes the balanced schedule
+    only when it saves more than eight key-block steps on the slowest SM: all four cases do.)"""
     q, k, v = (seeded(s, B * T, H * 128, kind) for s in (41, 42, 43))
     dq, dk, dv = dev(q, kind), dev(k, kind), dev(v, kind)
     full = torch.empty(kb.workspace_bytes(B * T, B * T, H, DT[kind]), dtype=torch.uint8, device="cuda")
