@@ -265,7 +265,7 @@ struct PeerSpec {
 };
 
 #ifndef KB_SPLIT_MARGIN
-#define KB_SPLIT_MARGIN 8
+#define KB_SPLIT_MARGIN 7
 #endif
 constexpr int MAX_HEADS = 4096;   // keeps every byte count below in range
 constexpr size_t NAG_NORM_FLOATS = 512;   // per (query tile, head): [2 column halves][|Z+|_1, |g|_1][128 rows]
@@ -283,8 +283,9 @@ size_t staging_bytes(size_t rows_q, size_t rows_k, int n_ctx, int H, int dtype, 
 // Balanced (item, key block) ranges per SM against whole items per SM, in key-block steps on the slowest SM. Measured on B200
 // (4096 / 3456 / 2560 / 2048 / 1536 / 1024 tokens x 16 heads, device time inside a CUDA graph): a key-block step costs ~1.86 us
 // and the balanced schedule a fixed ~15 us on top (one more segment to fill and drain per SM, the partial results written and
-// merged, the cooperative launch): it wins at 2560 and 3456 tokens (63.8 vs 83.5 us, 97.6 vs 111.7 us), ties at 4096 and 2048,
-// and loses at 1536 and 1024 (36.8 vs 29.3 us, 28.7 vs 21.3 us). So it is taken when it saves more than eight steps.
+// merged; the cooperative launch itself measured free): it wins at 2560 and 3456 tokens (63.8 vs 83.5 us, 97.6 vs 111.7 us), ties
+// or wins at 4096 (128.2 vs 127.4 us on one GPU, 126.9 vs 140.0 us on another), ties at 2048 and loses at 1536 and 1024 (36.8 vs
+// 29.3 us, 28.7 vs 21.3 us). So it is taken when it saves at least eight steps.
 bool split_pays(int n_items, int nb, int sm_count) {
     const long long steps = (long long)n_items * nb;
     if (nb < 2 || steps < 2LL * sm_count) return false;

@@ -593,8 +593,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     ok = (warp_ok[w0] & warp_ok[w0 + 1] & warp_ok[w0 + 2] & warp_ok[w0 + 3]) != 0u;
                     const float M = row_m * c;                                 // running maximum in log2 units
                     if (jb > 0) {
-                        // later blocks of a cut item: the unnormalised result goes to this CTA's scratch slot,
-                        // column-major (coalesced over rows), and the stream's flag is raised
+                        // later blocks of a cut item: the unnormalised result goes to this CTA's scratch slot, four columns of a
+                        // row together and rows adjacent (16-byte stores, coalesced over rows), and the stream's flag is raised
                         float* const slot = p.part + (size_t)blockIdx.x * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS;
                         if (ok) {
                             slot[HD * BM + t] = M;
@@ -606,7 +606,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 tmem_wait_ld();
                                 reg_fence32(o);
 #pragma unroll
-                                for (int e = 0; e < 32; e++) slot[(size_t)(q * 32 + e) * BM + t] = __uint_as_float(o[e]);
+                                for (int e4 = 0; e4 < 8; e4++)                 // [column / 4][row][4]: a warp writes 512 contiguous bytes
+                                    reinterpret_cast<float4*>(slot)[(size_t)(q * 8 + e4) * BM + t] =
+                                        make_float4(__uint_as_float(o[4 * e4]), __uint_as_float(o[4 * e4 + 1]), __uint_as_float(o[4 * e4 + 2]),
+                                                    __uint_as_float(o[4 * e4 + 3]));
                             }
                             tc_fence_before();
                             __syncwarp();
@@ -676,7 +679,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                     const float* slot = p.part + (size_t)(blockIdx.x + r) * (2 * PART_STREAM_FLOATS) + (size_t)i * PART_STREAM_FLOATS;
                                     const float k_r = ex2(__ldcg(slot + HD * BM + t) - Mf) * inv;
 #pragma unroll
-                                    for (int e = 0; e < 32; e++) v[e] += __ldcg(slot + (size_t)(q * 32 + e) * BM + t) * k_r;
+                                    for (int e4 = 0; e4 < 8; e4++) {
+                                        const float4 pv = __ldcg(reinterpret_cast<const float4*>(slot) + (size_t)(q * 8 + e4) * BM + t);
+                                        v[4 * e4] += pv.x * k_r; v[4 * e4 + 1] += pv.y * k_r; v[4 * e4 + 2] += pv.z * k_r; v[4 * e4 + 3] += pv.w * k_r;
+                                    }
                                 }
                             };
                             if constexpr (sizeof(OutT) == 2) {
