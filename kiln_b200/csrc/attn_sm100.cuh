@@ -85,12 +85,13 @@ constexpr int ATTN_THREADS = 384;
 #endif
 constexpr int SOFTMAX_REGS = KB_SOFTMAX_REGS, OTHER_REGS = (ATTN_THREADS * 168 - 256 * SOFTMAX_REGS) / 128;
 static_assert(256 * SOFTMAX_REGS + 128 * OTHER_REGS == ATTN_THREADS * 168 && OTHER_REGS % 8 == 0 && OTHER_REGS >= 24, "register split");
-// Shared memory (dynamic, 1024-byte aligned): MODE_PAIR: Q0, Q1 (each doubles as the output staging of its stream), K/V ring,
-// 1 KB of barriers and shared words. MODE_NAG: Q, two tiles holding the previous item's unblended g and Z+ as fp16 (see the
+// Shared memory (dynamic, 1024-byte aligned): MODE_PAIR: Q0, Q1, K/V ring, one tile of output staging (a 64-column half per
+// stream, so that a Q tile is free for the next segment's Q as soon as the segment's last S product is done - head-split
+// runs still stage in the Q tile), 1 KB of barriers and shared words. MODE_NAG: Q, two tiles holding the previous item's unblended g and Z+ as fp16 (see the
 // NAG epilogue), K/V ring, 3 KB control block (barriers, words, 2.5 KB of epilogue scratch): exactly the 227 KB a thread
 // block may have.
 constexpr int CTRL_BYTES_PAIR = 1024, CTRL_BYTES_NAG = 3072;
-constexpr int ATTN_TILES_PAIR = 2 + NSTAGE, ATTN_TILES_NAG = 3 + NSTAGE;
+constexpr int ATTN_TILES_PAIR = 3 + NSTAGE, ATTN_TILES_NAG = 3 + NSTAGE;
 constexpr int ATTN_SMEM_PAIR = ATTN_TILES_PAIR * TILE_BYTES + CTRL_BYTES_PAIR;
 constexpr int ATTN_SMEM_NAG = ATTN_TILES_NAG * TILE_BYTES + CTRL_BYTES_NAG;
 static_assert(ATTN_SMEM_NAG <= 232448, "shared memory per thread block on sm_100");
@@ -273,8 +274,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     constexpr int N_FRONT = MODE == MODE_NAG ? 3 : 2;             // tiles in front of the K/V ring
     const uint32_t sQ = base;
     const uint32_t sKV = base + N_FRONT * TILE_BYTES;             // NSTAGE tiles
-    uint8_t* const ctrl = smem + (N_FRONT + NSTAGE) * TILE_BYTES;
-    const uint32_t bars = sKV + NSTAGE * TILE_BYTES;              // BAR_COUNT x 8 bytes
+    constexpr int N_BACK = MODE == MODE_PAIR ? 1 : 0;             // MODE_PAIR: the output staging tile behind the ring
+    uint8_t* const ctrl = smem + (N_FRONT + NSTAGE + N_BACK) * TILE_BYTES;
+    const uint32_t bars = sKV + (NSTAGE + N_BACK) * TILE_BYTES;   // BAR_COUNT x 8 bytes
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(ctrl + 260);
     volatile uint32_t* const warp_ok = reinterpret_cast<volatile uint32_t*>(ctrl + 264);   // [8] per softmax warp
@@ -457,6 +459,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 ++sf_cnt;
                 if (!ok) break;
                 tc_fence_after();
+                // the segment's last S product is done: nothing reads this stream's Q tile any more, the next segment's Q may
+                // load under the rest of this one (head-split runs stage their output in the Q tile and release it later)
+                if (MODE == MODE_PAIR && j == je - 1 && t == 0 && (sizeof(OutT) == 4 || p.n_peers == 0)) mbar_arrive(bar(BAR_QEMPTY + i));
                 uint32_t s[4][32];
 #pragma unroll
                 for (int q = 0; q < 4; q++) tmem_ld32(tR + 32u * q, s[q]);
@@ -614,7 +619,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
-                            if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
+                            if (t == 0 && sizeof(OutT) == 2 && p.n_peers != 0) mbar_arrive(bar(BAR_QEMPTY + i));
                         }
                         __threadfence();
                         named_bar_sync(3 + i, 128);                            // every thread's stores are ordered before the flag
@@ -686,41 +691,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 }
                             };
                             if constexpr (sizeof(OutT) == 2) {
-                                // 16-bit output: stage the 128 x 128 tile in this stream's Q tile (dead: every S MMA of the stream
-                                // has completed), then write whole 256-byte rows, to every peer buffer on head-split runs.
                                 constexpr int ODT = std::is_same<OutT, __nv_bfloat16>::value ? DT_BF16 : DT_F16;
-                                uint8_t* const stage = smem + i * TILE_BYTES;
-#pragma unroll
-                                for (int q = 0; q < 4; q++) {
-                                    float v[32];
-                                    chunk(q, v);
-#pragma unroll
-                                    for (int cc = 0; cc < 4; cc++) {           // 16-byte chunk 4q + cc of the row, XOR-swizzled against bank conflicts
-                                        uint4 pk;
-                                        pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
-                                        pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
-                                        pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
-                                        pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
-                                        // the tile's own layout: two 128-byte-swizzled [128][64] halves (what TMA stores)
-                                        *reinterpret_cast<uint4*>(stage + (q >> 1) * HALF_BYTES + t * 128 + ((((4 * q + cc) & 7) ^ (t & 7)) << 4)) = pk;
-                                    }
-                                }
-                                tc_fence_before();
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));  // O_i is read out: the next segment's P*V may start
                                 if (p.n_peers == 0) {
-                                    // one bulk tensor store per half; rows past Tq are clipped by the tensor map
-                                    fence_proxy_async_smem();
-                                    named_bar_sync(3 + i, 128);                  // the staged tile is complete
-                                    if (t == 0) {
-                                        tma_store_3d(&tmO, smem_u32(stage), it.h * HD, it.q0 + i * BM, it.b);
-                                        tma_store_3d(&tmO, smem_u32(stage) + HALF_BYTES, it.h * HD + 64, it.q0 + i * BM, it.b);
-                                        tma_store_commit();
-                                        tma_store_wait_read();                   // the staging space may be overwritten
+                                    // 16-bit output: the tile leaves in two rounds of 64 columns through this stream's own
+                                    // [128][64] staging half (128-byte rows, 128-byte swizzle: what a bulk tensor store reads);
+                                    // rows past Tq are clipped by the tensor map
+                                    uint8_t* const half_stage = smem + (2 + NSTAGE) * TILE_BYTES + i * HALF_BYTES;
+#pragma unroll
+                                    for (int hh = 0; hh < 2; hh++) {
+#pragma unroll
+                                        for (int q2 = 0; q2 < 2; q2++) {
+                                            float v[32];
+                                            chunk(2 * hh + q2, v);
+#pragma unroll
+                                            for (int cc = 0; cc < 4; cc++) {
+                                                uint4 pk;
+                                                pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
+                                                pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
+                                                pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
+                                                pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
+                                                *reinterpret_cast<uint4*>(half_stage + t * 128 + (((4 * q2 + cc) ^ (t & 7)) << 4)) = pk;
+                                            }
+                                        }
+                                        if (hh == 1) {
+                                            tc_fence_before();
+                                            __syncwarp();
+                                            if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));   // O_i is read out: the next segment's P*V may start
+                                        }
+                                        fence_proxy_async_smem();
+                                        named_bar_sync(3 + i, 128);              // the staged half is complete
+                                        if (t == 0) {
+                                            tma_store_3d(&tmO, smem_u32(half_stage), it.h * HD + 64 * hh, it.q0 + i * BM, it.b);
+                                            tma_store_commit();
+                                            tma_store_wait_read();               // the half may be overwritten
+                                        }
+                                        if (hh == 0) named_bar_sync(3 + i, 128);
                                     }
                                 } else {
+                                    // head-split runs: the tile is staged in this stream's Q tile (dead: every S product of the
+                                    // stream has completed), then written as whole 256-byte rows to every peer buffer
+                                    uint8_t* const stage = smem + i * TILE_BYTES;
+#pragma unroll
+                                    for (int q = 0; q < 4; q++) {
+                                        float v[32];
+                                        chunk(q, v);
+#pragma unroll
+                                        for (int cc = 0; cc < 4; cc++) {
+                                            uint4 pk;
+                                            pk.x = pack16<ODT>(v[8 * cc + 0], v[8 * cc + 1]);
+                                            pk.y = pack16<ODT>(v[8 * cc + 2], v[8 * cc + 3]);
+                                            pk.z = pack16<ODT>(v[8 * cc + 4], v[8 * cc + 5]);
+                                            pk.w = pack16<ODT>(v[8 * cc + 6], v[8 * cc + 7]);
+                                            *reinterpret_cast<uint4*>(stage + (q >> 1) * HALF_BYTES + t * 128 + ((((4 * q + cc) & 7) ^ (t & 7)) << 4)) = pk;
+                                        }
+                                    }
+                                    tc_fence_before();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
                                     named_bar_sync(3 + i, 128);                  // the staged tile is complete
-                                    // head-split runs: each warp copies 32 rows out as whole 256-byte rows to every peer buffer
+                                    // each warp copies 32 rows out as whole 256-byte rows to every peer buffer
                                     // (all shared-memory reads first, then the stores)
                                     const int lr0 = 32 * (warp & 3);
                                     const int row0 = it.q0 + i * BM + lr0;
@@ -754,8 +783,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 __syncwarp();
                                 if (lane == 0) mbar_arrive(bar(BAR_OFREE + i));
                             }
-                            // the Q tile (and the staging space in it) may be overwritten by the next segment's Q
-                            if (t == 0) mbar_arrive(bar(BAR_QEMPTY + i));
+                            // head-split runs: the Q tile (the staging space in it) may now be overwritten by the next segment's Q
+                            if (t == 0 && sizeof(OutT) == 2 && p.n_peers != 0) mbar_arrive(bar(BAR_QEMPTY + i));
                         }
                     }
                 }
