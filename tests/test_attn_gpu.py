@@ -295,6 +295,9 @@ def test_nag(kb, Tq, H, Tp, Tn, kind, s):
     ref, _ = _nag_ref(q, kp, vp, Tp, L - Tp, kn, vn, Tn, L - Tn, s, 2.5, 0.25, H)
     out = _nag(kb, q, kp, vp, Tp, L - Tp, kn, vn, Tn, L - Tn, s, 2.5, 0.25, Tq, H, kind)
     assert_close(out, ref, f"NAG Tq={Tq} H={H} Tp={Tp} Tn={Tn} {kind} s={s}")
+    # 16-bit output takes the other kernel form (two query tiles per item, positive then negative context)
+    out16 = _nag(kb, q, kp, vp, Tp, L - Tp, kn, vn, Tn, L - Tn, s, 2.5, 0.25, Tq, H, kind, out_kind=kind)
+    (assert_close if kind == "f16" else assert_close_bf16_storage)(out16, ref, f"NAG 16-bit out Tq={Tq} H={H} Tp={Tp} Tn={Tn} {kind} s={s}")
 
 
 def test_nag_identities_and_clamp(kb):
