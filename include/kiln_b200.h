@@ -255,7 +255,7 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
  * the tensor cores (fp16 operands, fp32 accumulation; the engine's is fp32 throughout), nothing of size Tq x Tk is stored,
  * and every output element is written once in a fixed order (bit-identical from run to run). Launches: staging pre-pass
  * (unless dtype is KB_F16), the forward kernel (for the per-row softmax statistics and O), a reduction for
- * sum_d dout * O, the dK/dV kernel and the dQ kernel. The workspace (kb_attn_bwd_workspace_bytes) is always required. */
+ * sum_d dout * O, and one launch whose thread blocks form dK/dV (one per key block) or dQ (one per query block). The workspace (kb_attn_bwd_workspace_bytes) is always required. */
 size_t kb_attn_bwd_workspace_bytes(int B, int Tq, int Tk, int H, int dtype);
 int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, const void* v, const void* dout, int B, int Tq, int Tk,
                 int npad, int H, int ld_q, int ld_k, int ld_v, int ld_do, int ld_dq, int ld_dk, int ld_dv, int dtype, void* workspace,
