@@ -739,6 +739,18 @@ int kb_linear16_qkv_lora(void* const* C3, int ldc, const void* A, int lda, const
 // ------------------------------------------------------------------------------------------- attention backward
 namespace {
 size_t bwd_stats_bytes(int B, int Tq, int H) { return align256((size_t)B * H * ((Tq + 127) / 128) * 256 * sizeof(float)); }
+// How the dK/dV role cuts its query blocks when there are too few (key block, head, image) triples to fill the GPU
+// (cross-attention to a short context): parts of q_per query blocks each; 1 part = no cut.
+void bwd_qsplit(int B, int Tq, int Tk, int H, int sm_count, int* qsplit, int* q_per) {
+    const long long triples = (long long)B * H * ((Tk + 127) / 128);
+    const int nqb = (Tq + 127) / 128;
+    int want = (int)(sm_count / (triples > 0 ? triples : 1));
+    if (want > nqb) want = nqb;
+    if (want < 2) { *qsplit = 1; *q_per = nqb; return; }
+    *q_per = (nqb + want - 1) / want;
+    *qsplit = (nqb + *q_per - 1) / *q_per;
+}
+size_t bwd_partial_bytes(int B, int Tk, int H, int qsplit) { return qsplit > 1 ? 2 * align256((size_t)qsplit * B * Tk * H * 128 * sizeof(float)) : 0; }
 size_t bwd_fixed_bytes(int B, int Tq, int Tk, int H, int dtype) {
     size_t n = bwd_stats_bytes(B, Tq, H) + align256((size_t)B * Tq * H * 128 * 2);                         // statistics, O (fp16)
     if (dtype != KB_F16) n += 2 * align256((size_t)B * Tq * H * 128 * 2) + 2 * align256((size_t)B * Tk * H * 128 * 2);   // fp16 Q, dO, K, V
@@ -748,8 +760,13 @@ size_t bwd_fixed_bytes(int B, int Tq, int Tk, int H, int dtype) {
 
 size_t kb_attn_bwd_workspace_bytes(int B, int Tq, int Tk, int H, int dtype) {
     if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || H > MAX_HEADS || !valid_in_dtype(dtype)) return 0;
-    // + what the forward pass inside wants for its balanced schedule (it runs on fp16 operands: no staging of its own)
-    return bwd_fixed_bytes(B, Tq, Tk, H, dtype) + kb_attn_workspace_bytes(B * Tq, B * Tk, 1, H, KB_F16, 0, 0);
+    // + the partial dK / dV of a cut query range, + what the forward pass inside wants for its balanced schedule (it runs on
+    // fp16 operands: no staging of its own)
+    int sms = 148, qsplit, q_per;
+    DeviceState* st;
+    if (get_state(&st) == KB_OK) sms = st->sm_count;
+    bwd_qsplit(B, Tq, Tk, H, sms, &qsplit, &q_per);
+    return bwd_fixed_bytes(B, Tq, Tk, H, dtype) + bwd_partial_bytes(B, Tk, H, qsplit) + kb_attn_workspace_bytes(B * Tq, B * Tk, 1, H, KB_F16, 0, 0);
 }
 
 int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, const void* v, const void* dout, int B, int Tq, int Tk,
@@ -770,6 +787,14 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
     Stage sg{static_cast<char*>(workspace), workspace_bytes};
     float* stats = static_cast<float*>(sg.take_bytes(bwd_stats_bytes(B, Tq, H)));
     __half* o16 = static_cast<__half*>(sg.take_bytes((size_t)B * Tq * H * 128 * 2));
+    int qsplit, q_per;
+    bwd_qsplit(B, Tq, Tk, H, st->sm_count, &qsplit, &q_per);
+    float* part_dk = nullptr;
+    float* part_dv = nullptr;
+    if (qsplit > 1) {
+        part_dk = static_cast<float*>(sg.take_bytes((size_t)qsplit * B * Tk * H * 128 * sizeof(float)));
+        part_dv = static_cast<float*>(sg.take_bytes((size_t)qsplit * B * Tk * H * 128 * sizeof(float)));
+    }
     const void *qq = q, *kk = k, *vv = v, *gg = dout;
     int ldq = ld_q, ldk = ld_k, ldv = ld_v, ldg = ld_do;
     PrepBatch pb;
@@ -800,15 +825,19 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
         return rc;
     BwdParams p = {};
     p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
+    p.qsplit = qsplit; p.q_per = q_per;
     p.stats = stats; p.scale_log2 = SCALE_LOG2; p.scale = 0.08838834764831845f;
     p.status = st->status;
     ProfScope ps(st, KB_PROF_ATTENTION, stream);
     // fp32 [B][T][H*128] views of the three outputs, 32 columns x 32 rows per box (128-byte rows, 128-byte swizzle)
     CUtensorMap tdq, tdk, tdv;
     {
-        struct { CUtensorMap* tm; void* ptr; int T, ld; } outs[3] = {{&tdq, dq, Tq, ld_dq}, {&tdk, dk, Tk, ld_dk}, {&tdv, dv, Tk, ld_dv}};
+        // a cut query range writes its dK / dV parts to scratch: dense [qsplit * B][Tk][H*128]
+        struct { CUtensorMap* tm; void* ptr; int T, ld, nb; } outs[3] = {{&tdq, dq, Tq, ld_dq, B},
+                                                                         {&tdk, qsplit > 1 ? (void*)part_dk : dk, Tk, qsplit > 1 ? H * 128 : ld_dk, qsplit * B},
+                                                                         {&tdv, qsplit > 1 ? (void*)part_dv : dv, Tk, qsplit > 1 ? H * 128 : ld_dv, qsplit * B}};
         for (auto& o : outs) {
-            const cuuint64_t dims[3] = {(cuuint64_t)H * 128, (cuuint64_t)o.T, (cuuint64_t)B};
+            const cuuint64_t dims[3] = {(cuuint64_t)H * 128, (cuuint64_t)o.T, (cuuint64_t)o.nb};
             const cuuint64_t strides[2] = {(cuuint64_t)o.ld * 4, (cuuint64_t)o.T * (cuuint64_t)o.ld * 4};
             const cuuint32_t box[3] = {32, 32, 1};
             const cuuint32_t estr[3] = {1, 1, 1};
@@ -817,9 +846,15 @@ int kb_attn_bwd(void* dq, void* dk, void* dv, const void* q, const void* k, cons
                 return KB_ERR_CUDA;
         }
     }
-    const long long n_dkv = (long long)B * H * ((Tk + 127) / 128), n_dq = (long long)B * H * ((Tq + 127) / 128);
+    const long long n_dkv = (long long)B * H * ((Tk + 127) / 128) * qsplit, n_dq = (long long)B * H * ((Tq + 127) / 128);
     if (n_dkv + n_dq > 0x7fffffffLL) return KB_ERR_SHAPE;
     attn_bwd_kernel<<<(unsigned)(n_dkv + n_dq), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, tdk, tdv, p, (int)n_dkv);
+    if (cudaGetLastError() != cudaSuccess) return KB_ERR_CUDA;
+    if (qsplit > 1) {
+        const size_t n = (size_t)B * Tk * H * 32;                 // one thread per four columns
+        bwd_reduce_kernel<<<dim3((unsigned)((n + 255) / 256), 2), 256, 0, stream>>>(static_cast<float*>(dk), ld_dk, static_cast<float*>(dv), ld_dv, part_dk,
+                                                                                   part_dv, B * Tk, H * 128, qsplit);
+    }
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_CUDA;
 }
 

@@ -55,6 +55,10 @@ constexpr int BWD_SMEM = 2 * TILE_BYTES + 2 * BWD_STAGE_BYTES + 1024;   // resid
 
 struct BwdParams {
     int B, H, Tq, Tk;
+    // BWD_DKV with few key blocks (cross-attention to a short context): the query blocks of a (key block, head, image) are cut
+    // into qsplit ranges of q_per blocks, one thread block each, whose partial dK / dV go to scratch (image index s * B + b of
+    // the output tensor maps) and are summed in a fixed order by bwd_reduce_kernel. qsplit = 1: no cut, outputs written directly.
+    int qsplit, q_per;
     const float* stats;     // [B][H][ceil(Tq/128)][2][128]: L (log2 of the softmax denominator, in units of c * score), then D
     float scale_log2;       // c = log2(e) / sqrt(128)
     float scale;            // 1 / sqrt(128)
@@ -94,7 +98,7 @@ __global__ void bwd_delta_kernel(float* stats, const __half* dout, int ld_do, co
 template <int MODE>
 __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmdO,
                                               const CUtensorMap& tmOut0, const CUtensorMap& tmOut1, const BwdParams& p, const int blk, const int h,
-                                              const int b) {
+                                              const int b, const int part) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                                           // never seen; without it every tile would be garbage
@@ -111,7 +115,8 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nqb = (p.Tq + BM - 1) / BM;
-    const int n_it = MODE == BWD_DKV ? nqb : (p.Tk + BN - 1) / BN;
+    const int i0 = MODE == BWD_DKV ? part * p.q_per : 0;           // first streamed block of this thread block
+    const int n_it = MODE == BWD_DKV ? min(nqb - i0, p.q_per) : (p.Tk + BN - 1) / BN;
 
     if (tid == 0) {
         for (int i = 0; i < BB_COUNT; i++) mbar_init(bar(i), (i == BB_PFULL || i == BB_PFULL + 1) ? 8u : 1u);   // P: one arrival per softmax warp
@@ -253,7 +258,8 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
                     for (int a = 0; a < (MODE == BWD_DKV ? 2 : 1); a++)
 #pragma unroll
                         for (int q = 0; q < 2; q++)
-                            tma_store_3d(a ? &tmOut1 : &tmOut0, smem_u32(my_stage + (a * 2 + q) * 4096), h * HD + half * 64 + 32 * q, row0, b);
+                            tma_store_3d(a ? &tmOut1 : &tmOut0, smem_u32(my_stage + (a * 2 + q) * 4096), h * HD + half * 64 + 32 * q, row0,
+                                         MODE == BWD_DKV ? part * p.B + b : b);
                     tma_store_commit();
                 }
                 tma_store_wait_all();                                       // the stage area goes away with the thread block
@@ -343,9 +349,9 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
                 issued = it + 1;
                 const uint32_t x0 = sX + st * BWD_STAGE_BYTES, x1 = x0 + TILE_BYTES;
                 mbar_expect_tx(bar(BB_XFULL + st), 2 * TILE_BYTES + (MODE == BWD_DKV ? 1024 : 0));
-                load_tile(x0, MODE == BWD_DKV ? &tmQ : &tmK, bar(BB_XFULL + st), it * BM);
-                load_tile(x1, MODE == BWD_DKV ? &tmdO : &tmV, bar(BB_XFULL + st), it * BM);
-                if (MODE == BWD_DKV) bulk_load_1d(x1 + TILE_BYTES, p.stats + (((size_t)b * p.H + h) * nqb + it) * 256, 1024, bar(BB_XFULL + st));
+                load_tile(x0, MODE == BWD_DKV ? &tmQ : &tmK, bar(BB_XFULL + st), (i0 + it) * BM);
+                load_tile(x1, MODE == BWD_DKV ? &tmdO : &tmV, bar(BB_XFULL + st), (i0 + it) * BM);
+                if (MODE == BWD_DKV) bulk_load_1d(x1 + TILE_BYTES, p.stats + (((size_t)b * p.H + h) * nqb + (i0 + it)) * 256, 1024, bar(BB_XFULL + st));
             }
             if (!good || *abort_flag) {                               // let the copies already requested land before the memory goes away
                 drain_wait(bar(BB_RES), 0u);
@@ -363,6 +369,23 @@ __device__ __forceinline__ void attn_bwd_body(const CUtensorMap& tmQ, const CUte
     }
 }
 
+// dk / dv [B*Tk, ld] = sum over the qsplit partial results [qsplit][B*Tk][cols] in scratch, in the order of the parts
+// (bit-identical from run to run); one thread per four columns of a row, both tensors in one launch (blockIdx.y).
+__global__ void bwd_reduce_kernel(float* dk, int ld_dk, float* dv, int ld_dv, const float* part_dk, const float* part_dv, int rows, int cols, int qsplit) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t per_row = (size_t)cols / 4;
+    if (i >= (size_t)rows * per_row) return;
+    const size_t r = i / per_row, c4 = i % per_row;
+    const float* src = blockIdx.y ? part_dv : part_dk;
+    float* dst = blockIdx.y ? dv + r * (size_t)ld_dv + c4 * 4 : dk + r * (size_t)ld_dk + c4 * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < qsplit; s++) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + ((size_t)s * rows + r) * (size_t)cols) + c4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(dst) = acc;
+}
+
 // Both roles in ONE launch: thread blocks [0, n_dkv) are the dK/dV blocks, the rest the dQ blocks. The two halves are independent
 // (disjoint outputs, common read-only inputs); launched together, the dQ blocks start on the SMs that the last, partial round of
 // dK/dV blocks leaves idle: 2 x 512 blocks at the DiT size are 6.9 rounds on 148 SMs instead of 3.46 rounds twice, each rounded up.
@@ -373,10 +396,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int nkb = (p.Tk + BN - 1) / BN, nqb = (p.Tq + BM - 1) / BM;
     int idx = (int)blockIdx.x;
     if (idx < n_dkv) {
-        attn_bwd_body<BWD_DKV>(tmQ, tmK, tmV, tmdO, tmDV, tmDK, p, idx % nkb, (idx / nkb) % p.H, idx / (nkb * p.H));
+        const int part = idx % p.qsplit;
+        idx /= p.qsplit;
+        attn_bwd_body<BWD_DKV>(tmQ, tmK, tmV, tmdO, tmDV, tmDK, p, idx % nkb, (idx / nkb) % p.H, idx / (nkb * p.H), part);
     } else {
         idx -= n_dkv;
-        attn_bwd_body<BWD_DQ>(tmQ, tmK, tmV, tmdO, tmDQ, tmDQ, p, idx % nqb, (idx / nqb) % p.H, idx / (nqb * p.H));
+        attn_bwd_body<BWD_DQ>(tmQ, tmK, tmV, tmdO, tmDQ, tmDQ, p, idx % nqb, (idx / nqb) % p.H, idx / (nqb * p.H), 0);
     }
 }
 
