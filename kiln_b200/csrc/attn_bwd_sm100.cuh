@@ -19,7 +19,7 @@
 //   BWD_DQ   one thread block per (query block i, head, image), key blocks j streamed:
 //              S = Q_i K_j^T,  dP = dO_i V_j^T,  dS = 2^(c S - L_i) (dP - D_i),  dQ_i += dS K_j
 //
-// Two kernels instead of one with atomics: every output element is written once by one thread block, in a fixed order, so
+// Two roles instead of one with atomics: every output element is written once by one thread block, in a fixed order, so
 // results are bit-identical from run to run (the reference's are too). The price is that S and dP are formed twice.
 // The npad zero keys only enter through L_i: their dP is 0 and their K is 0, so they add nothing to any gradient
 // (train.cu:124 says the same of the reference). Rows past Tq or Tk are zero-filled by TMA; a zero Q/dO row has dS = 0 and

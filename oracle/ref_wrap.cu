@@ -39,66 +39,7 @@
 #undef rmsnorm
 #undef rope_half
 #undef linear16
-#include "gpu_ops.h"
-#include "kiln_b200.h"
-
-// ---- the binding: the reference's signatures (engine/src/gpu.h:133,145,152-156 and linear16 there), the library underneath ----
-static void bind_context() {
-    // the library's staging area for fp32 operands: sized once for the largest call this wrapper makes, outside the arena
-    static void* ws = nullptr;
-    static size_t ws_bytes = 0;
-    if (!ws) {
-        ws_bytes = kb_attn_workspace_bytes(8192, 8192, 2, 16, KB_F32, 1, 1) + ((size_t)64 << 20);   // + room for LoRA down-projections
-        if (cudaMalloc(&ws, ws_bytes) != cudaSuccess) throw std::runtime_error("workspace allocation failed");
-        kiln_b200::set_exact_attention([](float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-                                          int Tq, int Tk, int H, int Dh, bool causal, int npad) {
-            ref_own_attention(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, causal, npad);
-        });
-    }
-    kiln_b200::OpContext c;
-    c.stream = G.stream; c.workspace = ws; c.workspace_bytes = ws_bytes;
-    kiln_b200::set_context(c);
-}
-void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-               int Tq, int Tk, int H, int Dh, bool causal, int npad = 0) {
-    bind_context();
-    kiln_b200::attention(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, causal, npad);   // falls through to ref_own_attention when not eligible
-}
-void attention16(__half* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-                 int Tq, int Tk, int H, int Dh, int npad = 0) {
-    bind_context();
-    kiln_b200::attention16(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, npad);
-}
-void rmsnorm(float* y, const float* x, const Weight* w, int rows, int dim, float eps) {
-    if (dim != 128) { ref_own_rmsnorm(y, x, w, rows, dim, eps); return; }                   // the 2048- and 1024-wide norms are not on the path
-    bind_context();
-    kiln_b200::rmsnorm(y, x, w ? w->p : nullptr, rows, dim, eps);
-}
-void rope_half(float* x, int T, int H, int Dh, const float* cos_t, const float* sin_t) {
-    if (Dh != 128) { ref_own_rope_half(x, T, H, Dh, cos_t, sin_t); return; }
-    bind_context();
-    kiln_b200::rope_half(x, T, H, Dh, cos_t, sin_t);
-}
-void linear16(void* y, int ldy, const __half* x16, int T, const Weight& Win, Epi16 epi, const float* gate = nullptr) {
-    if (!Win.f16 || Win.on_host || Win.cols % 64) { ref_own_linear16(y, ldy, x16, T, Win, epi, gate); return; }
-    bind_context();
-    kiln_b200::Weight16 W;
-    W.p = (const __half*)Win.p; W.rows = (int)Win.rows; W.cols = (int)Win.cols;
-    kiln_b200::Lora16 L;
-    const size_t m = G.arena.mark();
-    if (Win.lora && !Win.lora->empty()) {                          // stacked per call into the arena, as engine/src/kernels.cu:578-590 does
-        std::vector<kiln_b200::LoraAdd16> adds;
-        for (auto& l : *Win.lora) adds.push_back({l.A.p, (int)l.A.rows, l.B.p, l.scale});
-        const int rank = kiln_b200::lora_rank_padded(adds.data(), (int)adds.size());
-        __half* ac = (__half*)G.arena.f(((size_t)rank * W.cols + 1) / 2);
-        __half* bc = (__half*)G.arena.f(((size_t)W.rows * rank + 1) / 2);
-        kiln_b200::pack_lora(ac, bc, W.rows, W.cols, adds.data(), (int)adds.size());
-        L.a_cat = ac; L.b_cat = bc; L.rank = rank;
-        W.lora = &L;
-    }
-    kiln_b200::linear16(y, ldy, x16, T, W, (kiln_b200::Epi16)(int)epi, gate);
-    G.arena.release(m);
-}
+#include "ref_ops_binding.h"
 #endif
 #include "dit.cu"        // k_nag<T>, cosmos_rope, Dit::forward_batch
 // The LoRA trainer's file defines the same model constants as dit.cu (each is its own translation unit in the engine): rename them
