@@ -11,7 +11,7 @@ weights:
   anima-base-v1.0.safetensors   the DiT the loader expects (engine/src/dit.cu:11-96: 28 blocks, 2048 wide, adaLN-LoRA
                                 rank 256, 6-block LLM adapter, 1024 wide), bf16, about 4 GB
   qwen_3_06b_base.safetensors   the text encoder's layout (engine/src/te.cu:6-28; the loader counts the layers it finds
-                                and reads the MLP width from the file: two layers, a short vocabulary)
+                                and reads the MLP width from the file: two layers, a shortened vocabulary)
   loras/style_a, style_b        two LoRA files in the naming the engine's loader pairs up (engine/src/engine.h:136-170)
   qwen_image_vae.safetensors    the VAE's layout (engine/src/vae.cu:38-112: channel counts are read from the file; the
                                 real ones are used: 96/192/384/384, 16 latent channels)
@@ -27,7 +27,7 @@ import sys
 import numpy as np
 
 D, AD, FF = 2048, 1024, 8192
-TE_VOCAB, T5_VOCAB = 4096, 4096          # token ids in test requests stay below these
+TE_VOCAB, T5_VOCAB = 65536, 32768        # token ids in test requests and in the engine's --bench prompt (main.cpp:79-80) stay below these
 POOL = 1 << 24
 
 

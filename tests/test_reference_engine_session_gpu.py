@@ -254,3 +254,39 @@ def test_graph_request_with_stacked_loras(models, tmp_path):
     assert len(pv_r) == len(pv_s) == len(pv_x) == 3
     for a, b, x in zip(pv_r, pv_s, pv_x):
         assert np.abs(b - x).mean() <= FACTOR * np.abs(a - x).mean() + FLOOR_LEVELS
+
+
+def test_engine_bench_mode(models):
+    """--bench WxH (main.cpp:77-152): the engine's own DiT-step benchmark - warm forward passes of all 28 blocks with the
+    cross-attention K/V cached, its fp16-activation path against its fp32-input path, a batched CFG step and its per-category
+    profile - at the three image sizes of the headline metric (1536 / 3456 / 4096 image tokens), in both builds. Wall-clock
+    milliseconds as the engine prints them (whole milliseconds); the build over the library must not be slower."""
+    import re
+    rows = []
+    for size in ("512x768", "768x1152", "1024x1024"):
+        got = {}
+        for tag, engine in (("reference", ENGINE_REF), ("library", ENGINE_SHIM)):
+            rc, events, err = _run(engine, models, extra_args=["--bench", size])
+            assert rc == 0, (events[-3:], err[-2000:])
+            logs = [e["msg"] for e in events if e.get("ev") == "log"]
+            assert not [e for e in events if e.get("ev") in ("error", "fatal")]
+            step = [m for m in logs if "ms/step (avg of" in m]
+            paths = [m for m in logs if m.startswith("fp32-input tensor-core path")]
+            cfg = [m for m in logs if m.startswith("CFG step")]
+            assert len(step) == 1 and len(paths) == 1 and len(cfg) == 1, logs
+            got[tag] = dict(step=float(re.search(r": (\d+) ms/step", step[0]).group(1)),
+                            f16=float(re.search(r"fp16-activation path (\d+) ms/step", paths[0]).group(1)),
+                            rel=float(re.search(r"rel_l2 ([0-9.e+-]+)", paths[0]).group(1)),
+                            cfg=float(re.search(r"batched (\d+) ms", cfg[0]).group(1)))
+            print("--bench %s, %s build:" % (size, tag))
+            for m in logs[logs.index(step[0]):]:
+                print("    " + m)
+        rows.append((size, got))
+    print("size        DiT step ms (reference / library)   batched CFG step ms   fp16 path vs fp32-input path rel_l2")
+    for size, g in rows:
+        print("%-10s  %5.0f / %-5.0f                       %5.0f / %-5.0f         %.2e / %.2e"
+              % (size, g["reference"]["step"], g["library"]["step"], g["reference"]["cfg"], g["library"]["cfg"],
+                 g["reference"]["rel"], g["library"]["rel"]))
+        assert g["library"]["step"] <= g["reference"]["step"]
+        assert g["library"]["cfg"] <= g["reference"]["cfg"]
+        assert g["library"]["rel"] <= FACTOR * g["reference"]["rel"] + FLOOR_REL
