@@ -22,7 +22,7 @@ REF_ENGINE_SHIM = os.path.join(REF_DIR, "kiln-engine-shim")      # the same engi
 # POSIX ones behind the same headers) and without the optional face-detector / upscaler modules
 ENGINE_UNITS = ["main.cpp", "graph.cpp", "kernels.cu", "te.cu", "dit.cu", "train.cu", "tagger.cu", "vae.cu", "pipeline.cu",
                 "sdops.cu", "sdxl.cu", "clip.cu", "sdvae.cu", "sdpipe.cu"]
-OP_RENAMES = ["-D%s=ref_own_%s" % (n, n) for n in ("attention", "attention16", "rmsnorm", "rope_half", "linear16")]
+OP_RENAMES = ["-D%s=ref_own_%s" % (n, n) for n in ("attention", "attention16", "rmsnorm", "rope_half", "linear16", "gpu_alloc_scratch")]
 
 
 def _gomp_dir():
@@ -110,7 +110,7 @@ def build_ref_engine(ref_root, force=False):
     posix = os.path.join(HERE, "posix")
     lib = os.path.join(root, "kiln_b200", "lib")
     own = [os.path.join(posix, f) for f in ("windows.h", "io.h", "safetensors_posix.cpp", "image_io_posix.cpp")] + \
-          [os.path.join(HERE, f) for f in ("ref_engine_bind.cu", "ref_ops_binding.h")] + \
+          [os.path.join(HERE, f) for f in ("ref_engine_bind.cu", "ref_engine_train_bind.cu", "ref_ops_binding.h")] + \
           [os.path.join(root, "kiln_b200", "host", "gpu_ops.h"), os.path.join(root, "include", "kiln_b200.h")]
     if not force and _newer(REF_ENGINE, *own) and _newer(REF_ENGINE_SHIM, *own):
         return REF_ENGINE, REF_ENGINE_SHIM
@@ -121,6 +121,7 @@ def build_ref_engine(ref_root, force=False):
     jobs.append((os.path.join(src_dir, "kernels.cu"), os.path.join(obj, "kernels_renamed.o"), OP_RENAMES))
     jobs.append((os.path.join(HERE, "ref_engine_bind.cu"), os.path.join(obj, "bind.o"),
                  ["-I" + HERE, "-I" + os.path.join(root, "kiln_b200", "host"), "-I" + os.path.join(root, "include")]))
+    jobs.append((os.path.join(HERE, "ref_engine_train_bind.cu"), os.path.join(obj, "train_bound.o"), []))
     jobs.append((os.path.join(posix, "safetensors_posix.cpp"), os.path.join(obj, "safetensors_posix.o"), []))
     jobs.append((os.path.join(posix, "image_io_posix.cpp"), os.path.join(obj, "image_io_posix.o"), []))
 
@@ -132,12 +133,12 @@ def build_ref_engine(ref_root, force=False):
         for job, r in zip(jobs, pool.map(compile_one, jobs)):
             if r.returncode != 0:
                 raise RuntimeError("reference engine: %s failed to compile:\n%s" % (job[0], r.stderr[-4000:]))
-    common = [os.path.join(obj, u.rsplit(".", 1)[0] + ".o") for u in ENGINE_UNITS if u != "kernels.cu"] + \
+    common = [os.path.join(obj, u.rsplit(".", 1)[0] + ".o") for u in ENGINE_UNITS if u not in ("kernels.cu", "train.cu")] + \
              [os.path.join(obj, "safetensors_posix.o"), os.path.join(obj, "image_io_posix.o")]
-    r = subprocess.run(["nvcc", "-o", REF_ENGINE] + common + [os.path.join(obj, "kernels.o"), "-lcublas"], capture_output=True, text=True)
+    r = subprocess.run(["nvcc", "-o", REF_ENGINE] + common + [os.path.join(obj, "kernels.o"), os.path.join(obj, "train.o"), "-lcublas"], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("reference engine: link failed:\n" + r.stderr[-4000:])
-    r = subprocess.run(["nvcc", "-o", REF_ENGINE_SHIM] + common + [os.path.join(obj, "kernels_renamed.o"), os.path.join(obj, "bind.o"),
+    r = subprocess.run(["nvcc", "-o", REF_ENGINE_SHIM] + common + [os.path.join(obj, "kernels_renamed.o"), os.path.join(obj, "train_bound.o"), os.path.join(obj, "bind.o"),
                         "-L" + lib, "-lkiln_engine_ops", "-lkiln_b200", "-lcublas", "-Xlinker", "-rpath=$ORIGIN/../../kiln_b200/lib"],
                        capture_output=True, text=True)
     if r.returncode != 0:

@@ -12,20 +12,28 @@
 #include "kiln_b200.h"
 
 // ---- the binding: the reference's signatures (engine/src/gpu.h:133,145,152-156 and linear16 there), the library underneath ----
+// The library's staging area (fp16 copies of fp32 operands, LoRA down-projections, the backward's scratch): one block outside
+// the engine's arena, sized for the largest call the engine makes (8192 image tokens). Taken at the first bound call, or
+// earlier by whoever sizes the engine's scratch (oracle/ref_engine_bind.cu does, so that the arena leaves room for it).
+static void* g_bind_ws = nullptr;
+static size_t g_bind_ws_bytes = 0;
+static size_t bind_workspace_bytes() {
+    const size_t fwd = kb_attn_workspace_bytes(8192, 8192, 2, 16, KB_F32, 1, 1), bwd = kb_attn_bwd_workspace_bytes(1, 8192, 8192, 16, KB_F32);
+    return (fwd > bwd ? fwd : bwd) + ((size_t)64 << 20);   // + room for LoRA down-projections
+}
+static void bind_workspace_reserve() {
+    if (g_bind_ws) return;
+    g_bind_ws_bytes = bind_workspace_bytes();
+    if (cudaMalloc(&g_bind_ws, g_bind_ws_bytes) != cudaSuccess) { g_bind_ws = nullptr; throw std::runtime_error("workspace allocation failed"); }
+    kiln_b200::set_exact_attention([](float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                      int Tq, int Tk, int H, int Dh, bool causal, int npad) {
+        ref_own_attention(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, causal, npad);
+    });
+}
 static void bind_context() {
-    // the library's staging area for fp32 operands: sized once for the largest call this wrapper makes, outside the arena
-    static void* ws = nullptr;
-    static size_t ws_bytes = 0;
-    if (!ws) {
-        ws_bytes = kb_attn_workspace_bytes(8192, 8192, 2, 16, KB_F32, 1, 1) + ((size_t)64 << 20);   // + room for LoRA down-projections
-        if (cudaMalloc(&ws, ws_bytes) != cudaSuccess) throw std::runtime_error("workspace allocation failed");
-        kiln_b200::set_exact_attention([](float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
-                                          int Tq, int Tk, int H, int Dh, bool causal, int npad) {
-            ref_own_attention(out, ldo, q, ldq, k, ldk, v, ldv, Tq, Tk, H, Dh, causal, npad);
-        });
-    }
+    bind_workspace_reserve();
     kiln_b200::OpContext c;
-    c.stream = G.stream; c.workspace = ws; c.workspace_bytes = ws_bytes;
+    c.stream = G.stream; c.workspace = g_bind_ws; c.workspace_bytes = g_bind_ws_bytes;
     kiln_b200::set_context(c);
 }
 void attention(float* out, int ldo, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,

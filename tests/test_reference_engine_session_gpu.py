@@ -63,9 +63,9 @@ def _job(job_id, out, **extra):
     return j
 
 
-def _run(engine, models, lines=None, extra_args=(), timeout=900):
+def _run(engine, models, lines=None, extra_args=(), timeout=900, engine_args=ENGINE_ARGS):
     env = dict(os.environ, KILN_TC16="1")     # the fp16-activation path on in both builds, not decided by a timing race
-    p = subprocess.run([engine, "--models", models, *ENGINE_ARGS, *extra_args],
+    p = subprocess.run([engine, "--models", models, *engine_args, *extra_args],
                        input=("\n".join(json.dumps(l) for l in lines) + "\n").encode() if lines is not None else b"",
                        stdout=subprocess.PIPE, stderr=subprocess.PIPE, env=env, timeout=timeout)
     events = [json.loads(l) for l in p.stdout.decode().splitlines() if l.strip()]
@@ -290,3 +290,36 @@ def test_engine_bench_mode(models):
         assert g["library"]["step"] <= g["reference"]["step"]
         assert g["library"]["cfg"] <= g["reference"]["cfg"]
         assert g["library"]["rel"] <= FACTOR * g["reference"]["rel"] + FLOOR_REL
+
+
+def test_engine_train_bench_mode(models):
+    """--train-bench WxH (main.cpp:330-367): three LoRA training steps (rank 32 on every linear of the 28 blocks; forward,
+    backward through every block, the engine's exact attention backward of train.cu:216-242) with its loss and per-category
+    profile. In the build over the library the trainer's attention_bwd goes to kb_attn_bwd (oracle/ref_engine_train_bind.cu)
+    and its forward attention calls to the library as everywhere else. 512 x 512 (1024 tokens): the largest size whose step
+    scratch (train.h:40-42) fits the 800 MB arena the engine keeps when it shares the card; without --vram-budget the arena
+    takes all memory and the trainer's own allocations (train.cu:384) fail in the reference's build as well."""
+    import re
+    got = {}
+    for tag, engine in (("reference", ENGINE_REF), ("library", ENGINE_SHIM)):
+        rc, events, err = _run(engine, models, extra_args=["--train-bench", "512x512"])
+        logs = [e["msg"] for e in events if e.get("ev") == "log"]
+        assert rc == 0 and not [e for e in events if e.get("ev") in ("error", "fatal")], (logs[-6:], err[-2000:])
+        steps = [re.search(r"step (\d) ([0-9.]+) s, loss ([0-9.eE+-]+)", m) for m in logs if "tokens): step" in m]
+        assert len(steps) == 3, logs
+        bwd = [m for m in logs if m.strip().startswith("bwd_attention")]
+        assert len(bwd) == 1, logs
+        got[tag] = dict(sec=[float(s.group(2)) for s in steps], loss=[float(s.group(3)) for s in steps],
+                        bwd_ms=float(re.search(r"([0-9.]+) ms", bwd[0]).group(1)))
+        print("--train-bench 512x512, %s build:" % tag)
+        for m in logs[[i for i, m in enumerate(logs) if "tokens): step" in m][0]:]:
+            print("    " + m)
+    r, l = got["reference"], got["library"]
+    print("train step seconds (reference / library): %s / %s; attention backward in the profiled step: %.1f / %.1f ms; losses %s / %s"
+          % (r["sec"], l["sec"], r["bwd_ms"], l["bwd_ms"], r["loss"], l["loss"]))
+    assert all(np.isfinite(r["loss"])) and all(np.isfinite(l["loss"]))
+    # the first step's loss depends on the forward pass only, the later ones on the updates the gradients produced
+    assert abs(l["loss"][0] - r["loss"][0]) <= 2e-3 * abs(r["loss"][0]) + 1e-4
+    for a, b in zip(r["loss"][1:], l["loss"][1:]):
+        assert abs(a - b) <= 2e-2 * abs(a) + 1e-3, (r["loss"], l["loss"])
+    assert l["bwd_ms"] < r["bwd_ms"] and l["sec"][2] <= r["sec"][2]
