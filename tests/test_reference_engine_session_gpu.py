@@ -263,10 +263,11 @@ def test_engine_bench_mode(models):
     milliseconds as the engine prints them (whole milliseconds); the build over the library must not be slower."""
     import re
     rows = []
-    for size in ("512x768", "768x1152", "1024x1024"):
+    lora = os.path.join(models, "loras", "style_a.safetensors")      # rank 16 on eight linears of every block, left unmerged
+    for size, extra in (("512x768", []), ("768x1152", []), ("1024x1024", []), ("1024x1024", ["--lora", lora])):
         got = {}
         for tag, engine in (("reference", ENGINE_REF), ("library", ENGINE_SHIM)):
-            rc, events, err = _run(engine, models, extra_args=["--bench", size])
+            rc, events, err = _run(engine, models, extra_args=["--bench", size, *extra])
             assert rc == 0, (events[-3:], err[-2000:])
             logs = [e["msg"] for e in events if e.get("ev") == "log"]
             assert not [e for e in events if e.get("ev") in ("error", "fatal")]
@@ -278,13 +279,15 @@ def test_engine_bench_mode(models):
                             f16=float(re.search(r"fp16-activation path (\d+) ms/step", paths[0]).group(1)),
                             rel=float(re.search(r"rel_l2 ([0-9.e+-]+)", paths[0]).group(1)),
                             cfg=float(re.search(r"batched (\d+) ms", cfg[0]).group(1)))
-            print("--bench %s, %s build:" % (size, tag))
+            if extra:
+                assert any(m.startswith("LoRA style_a.safetensors: 224 layers") for m in logs), logs[:12]
+            print("--bench %s%s, %s build:" % (size, " with a LoRA" if extra else "", tag))
             for m in logs[logs.index(step[0]):]:
                 print("    " + m)
-        rows.append((size, got))
+        rows.append((size + (" +LoRA" if extra else ""), got))
     print("size        DiT step ms (reference / library)   batched CFG step ms   fp16 path vs fp32-input path rel_l2")
     for size, g in rows:
-        print("%-10s  %5.0f / %-5.0f                       %5.0f / %-5.0f         %.2e / %.2e"
+        print("%-15s  %5.0f / %-5.0f                       %5.0f / %-5.0f         %.2e / %.2e"
               % (size, g["reference"]["step"], g["library"]["step"], g["reference"]["cfg"], g["library"]["cfg"],
                  g["reference"]["rel"], g["library"]["rel"]))
         assert g["library"]["step"] <= g["reference"]["step"]
