@@ -40,6 +40,8 @@ def _bf16(x):
 class _Writer:
     """One .safetensors file: 8-byte header length, JSON header, tensors back to back (bf16)."""
 
+    layout_only = False     # True (set by write_all(..., layout_only=True)): headers and sizes only, for loader checks on the CPU
+
     def __init__(self, seed):
         rng = np.random.default_rng(seed)
         self.unit = rng.uniform(-1.0, 1.0, POOL).astype(np.float32)   # the pool, unit scale
@@ -48,6 +50,8 @@ class _Writer:
         self.entries = []
 
     def _take(self, n, scale, offset=0.0):
+        if self.layout_only:
+            return 2 * n                                  # bytes only
         key = (round(float(scale), 9), offset)
         if key not in self.scaled:
             self.scaled[key] = _bf16(self.unit * np.float32(scale) + np.float32(offset))
@@ -77,15 +81,19 @@ class _Writer:
     def save(self, path):
         header, off = {}, 0
         for name, shape, data in self.entries:
-            header[name] = {"dtype": "BF16", "shape": shape, "data_offsets": [off, off + data.nbytes]}
-            off += data.nbytes
+            nbytes = data if isinstance(data, int) else data.nbytes
+            header[name] = {"dtype": "BF16", "shape": shape, "data_offsets": [off, off + nbytes]}
+            off += nbytes
         blob = json.dumps(header, separators=(",", ":")).encode()
         blob += b" " * (-len(blob) % 8)
         with open(path, "wb") as f:
             f.write(struct.pack("<Q", len(blob)))
             f.write(blob)
-            for _, _, data in self.entries:
-                f.write(data.tobytes())
+            if self.layout_only:
+                f.truncate(8 + len(blob) + off)          # a sparse file: the right names, shapes and size, all-zero values
+            else:
+                for _, _, data in self.entries:
+                    f.write(data.tobytes())
         return off
 
 
@@ -237,11 +245,21 @@ def write_lora(path, seed=4, rank=16, alpha=8.0, blocks=range(28),
             p = "diffusion_model.blocks.%d.%s" % (i, m)
             w.weight(p + ".lora_down.weight", (rank, inp))
             w.weight(p + ".lora_up.weight", (out, rank))
-            w.entries.append((p + ".alpha", [], _bf16(np.array([alpha], dtype=np.float32))))
+            w.entries.append((p + ".alpha", [], 2 if w.layout_only else _bf16(np.array([alpha], dtype=np.float32))))
     return w.save(path)
 
 
-def write_all(directory, seed=0):
+def write_all(directory, seed=0, layout_only=False):
+    """All files into `directory`. layout_only: sparse files with the real headers and sizes but zero values (instant; enough
+    for a loader to walk them)."""
+    _Writer.layout_only = bool(layout_only)
+    try:
+        return _write_all(directory, seed)
+    finally:
+        _Writer.layout_only = False
+
+
+def _write_all(directory, seed):
     os.makedirs(directory, exist_ok=True)
     sizes = {
         "anima-base-v1.0.safetensors": write_dit(os.path.join(directory, "anima-base-v1.0.safetensors"), seed + 1),

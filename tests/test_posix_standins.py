@@ -138,3 +138,39 @@ def test_win32_calls(harness, tmp_path):
     (d / "x.bin").write_bytes(b"1")
     assert harness("files", str(tmp_path) + "\\sub\\x.bin") == ["exists 1", "icmp 0", "deleted 1", "exists 0"]
     assert not (d / "x.bin").exists()
+
+
+def test_reference_loaders_accept_the_synthetic_model_files(tmp_path):
+    """The reference's own Dit::load / TextEncoder::load / Vae::load (engine/src/dit.cu:11-96, te.cu:6-28, vae.cu:38-130) walk
+    the files oracle/synthetic_models.py writes - here as sparse layout-only files - with the weight upload stubbed, and
+    see the shapes their forward passes expect. Uses the engine objects oracle/build.py left in oracle/_ref/engine_obj."""
+    import shutil
+    import synthetic_models
+    src = _reference_src()
+    obj = os.path.join(ROOT, "oracle", "_ref", "engine_obj")
+    need = [os.path.join(obj, f) for f in ("kernels.o", "te.o", "dit.o", "vae.o", "sdops.o", "safetensors_posix.o")]
+    if not src or not all(os.path.exists(f) for f in need) or not shutil.which("nvcc"):
+        pytest.skip("needs the reference's headers and the engine objects of oracle/build.py --ref")
+    exe = str(tmp_path / "loader_check")
+    o = str(tmp_path / "loader_check.o")
+    r = subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-I" + os.path.join(ROOT, "oracle", "posix"),
+                        "-I" + src, "-c", os.path.join(ROOT, "tests", "posix_harness", "loader_check.cu"), "-o", o], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run(["nvcc", "-o", exe, o, *need, "-lcublas", "-Xlinker", "--allow-multiple-definition"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    models = str(tmp_path / "models")
+    sizes = synthetic_models.write_all(models, layout_only=True)
+    assert sizes["anima-base-v1.0.safetensors"] > 4e9 and os.path.getsize(os.path.join(models, "anima-base-v1.0.safetensors")) > 4e9
+    r = subprocess.run([exe, models], capture_output=True, text=True, timeout=120)
+    out = r.stdout.splitlines()
+    assert r.returncode == 0 and not [l for l in out if l.startswith(("FAILED", "bad "))], out[-5:]
+    assert "vae top 384 stages 4 4 fp16 1" in out                          # every conv of the real architecture is on its fp16 path
+    assert "up 384: 192>384s 384>384 384>384 rs 192x3456" in out and "up 96: 96>96 96>96 96>96 rs 0x0" in out
+    assert "down 192: 96>192s 192>192 ds 192x1728" in out and "vae head 3x864 ehead 32x3456 q 32x32" in out
+    assert "dit named 685 prefix net. blocks 28 adapter 6" in out
+    w = dict(l.split()[1:] for l in out if l.startswith("w "))
+    assert w["blocks.0.self_attn.q_proj.weight"] == "2048x2048" and w["blocks.0.cross_attn.k_proj.weight"] == "2048x1024"
+    assert w["blocks.0.mlp.layer1.weight"] == "8192x2048" and w["blocks.0.adaln_modulation_mlp.2.weight"] == "6144x256"
+    assert w["x_embedder.proj.1.weight"] == "2048x68" and w["final_layer.linear.weight"] == "64x2048" and w["t_embedder.1.linear_2.weight"] == "6144x2048"
+    assert w["llm_adapter.blocks.0.mlp.0.weight"] == "4096x1024" and w["llm_adapter.embed.weight"] == "32768x1024"
+    assert "te layers 2 ff 3072 vocab 65536 q 2048x1024 k 1024x1024 o 1024x2048" in out
