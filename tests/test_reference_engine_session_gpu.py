@@ -103,7 +103,8 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
         return [{"cmd": "info", "id": "i1"},
                 _job("nag", outs[tag + "_nag"], nag={"enabled": True, "scale": 5.0, "tau": 2.5, "alpha": 0.25}),   # NAG cross-attention
                 {"cmd": "no-such-command", "id": "x"},
-                _job("cfg", outs[tag + "_cfg"], cfg=3.0, steps=3),                                                 # two contexts per step
+                # two contexts per step, then the hires pass: resize to 768 x 1152, VAE encode, two more steps at 3456 image tokens
+                _job("cfg", outs[tag + "_cfg"], cfg=3.0, steps=3, hires={"scale": 1.5, "denoise": 0.5, "steps": 2}),
                 _job("dropped", outs[tag + "_nag"] + ".never", nag={"enabled": True}),
                 {"cmd": "cancel", "id": "not-queued"},
                 {"cmd": "cancel", "id": "dropped"},
@@ -136,9 +137,14 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
     assert [e["ev"] for e in st_r["i1"]] == ["info"] and [e["ev"] for e in st_r["i2"]] == ["info"]
     assert st_r["dropped"] == [{"id": "dropped", "ev": "cancelled"}]          # cancelled while queued: never rendered
     for job, n in (("nag", STEPS), ("cfg", 3), ("exact", STEPS)):
-        assert [e["ev"] for e in st_r[job]] == ["encoded"] + ["step"] * n + ["decoded", "done"], st_r[job]
-        assert [(e["step"], e["of"]) for e in st_r[job] if e["ev"] == "step"] == [(i + 1, n) for i in range(n)]
-        assert st_r[job][-1]["w"] == W and st_r[job][-1]["h"] == H
+        hires = [(i + 1, 1) for i in range(1)] if job == "cfg" else []     # denoise 0.5 of 2 steps: one step of the truncated schedule
+        base = [e for e in st_r[job] if e.get("stage", "base") == "base"]
+        assert [e["ev"] for e in base] == ["encoded"] + ["step"] * n + ["decoded", "done"], st_r[job]
+        assert [(e["step"], e["of"]) for e in base if e["ev"] == "step"] == [(i + 1, n) for i in range(n)]
+        hs = [(e["step"], e["of"]) for e in st_r[job] if e["ev"] == "step" and e.get("stage") == "hires"]
+        assert (len(hs) >= 1 and hs == [(i + 1, len(hs)) for i in range(len(hs))]) if job == "cfg" else hs == [], hs
+        scale = 1.5 if job == "cfg" else 1.0
+        assert st_r[job][-1]["w"] == int(W * scale) and st_r[job][-1]["h"] == int(H * scale)
     info = [e for e in ev_s if e["ev"] == "info"][0]
     assert info["family"] == "anima" and info["tc"] is True and info["features"]["ext"] is True
 
@@ -159,7 +165,7 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
         e_shim = np.abs(_previews(ev_s, "nag")[i] - pv_exact[i]).mean()
         assert e_shim <= FACTOR * e_ref + FLOOR_LEVELS, (i, e_ref, e_shim)
     # the CFG job has no exact twin in the session: the two fp16 builds against each other, in the same units
-    d_cfg = np.abs(_image(outs["ref_cfg"]) - _image(outs["shim_cfg"])).mean()
+    d_cfg = np.abs(_image(outs["ref_cfg"], 768, 1152) - _image(outs["shim_cfg"], 768, 1152)).mean()
     print("image, CFG job, mean |reference - library| in 8-bit levels: %.3f (NAG job, same measure: %.3f)"
           % (d_cfg, np.abs(_image(outs["ref_nag"]) - _image(outs["shim_nag"])).mean()))
     assert d_cfg <= 2.0 * FACTOR * err_ref + 2 * FLOOR_LEVELS
