@@ -137,11 +137,11 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
     assert [e["ev"] for e in st_r["i1"]] == ["info"] and [e["ev"] for e in st_r["i2"]] == ["info"]
     assert st_r["dropped"] == [{"id": "dropped", "ev": "cancelled"}]          # cancelled while queued: never rendered
     for job, n in (("nag", STEPS), ("cfg", 3), ("exact", STEPS)):
-        hires = [(i + 1, 1) for i in range(1)] if job == "cfg" else []     # denoise 0.5 of 2 steps: one step of the truncated schedule
         base = [e for e in st_r[job] if e.get("stage", "base") == "base"]
         assert [e["ev"] for e in base] == ["encoded"] + ["step"] * n + ["decoded", "done"], st_r[job]
         assert [(e["step"], e["of"]) for e in base if e["ev"] == "step"] == [(i + 1, n) for i in range(n)]
         hs = [(e["step"], e["of"]) for e in st_r[job] if e["ev"] == "step" and e.get("stage") == "hires"]
+        # the hires pass runs a truncated schedule (denoise 0.5): at least one step, numbered 1..n of n
         assert (len(hs) >= 1 and hs == [(i + 1, len(hs)) for i in range(len(hs))]) if job == "cfg" else hs == [], hs
         scale = 1.5 if job == "cfg" else 1.0
         assert st_r[job][-1]["w"] == int(W * scale) and st_r[job][-1]["h"] == int(H * scale)
@@ -158,8 +158,7 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
     print("image, mean |fp16 - exact| in 8-bit levels: reference %.3f, over the library %.3f" % (err_ref, err_shim))
     assert err_shim <= FACTOR * err_ref + FLOOR_LEVELS
     pv_exact = _previews(ev_r, "exact")
-    for name, ev in (("reference", ev_r), ("library", ev_s)):
-        assert len(_previews(ev, "nag")) == STEPS
+    assert len(_previews(ev_r, "nag")) == len(_previews(ev_s, "nag")) == len(pv_exact) == STEPS
     for i in range(STEPS):
         e_ref = np.abs(_previews(ev_r, "nag")[i] - pv_exact[i]).mean()
         e_shim = np.abs(_previews(ev_s, "nag")[i] - pv_exact[i]).mean()
@@ -173,8 +172,8 @@ def test_scripted_session_matches_the_reference_engine(models, tmp_path):
 
 def test_engine_latent_comparison_tool(models, tmp_path):
     """--repeat FILE (main.cpp:493-531): the engine runs the jobs of a file and logs each latent's relative L2 distance from
-    the first job's. First job exact, then the fp16 NAG job and the fp16 CFG-free plain job: the distances of the build over
-    the library against those of the reference's own build."""
+    the first job's. First job exact, then the fp16 NAG job, then the exact job again: the distances of the build over the
+    library against those of the reference's own build."""
     jobs = tmp_path / "jobs.jsonl"
     base = dict(skip_decode=True, preview=False)
     lines = [_job("exact", "", nag={"enabled": True}, precision="fp32", **base),
